@@ -1,0 +1,107 @@
+"""The batch of one step: a packed list of rows, each row the next tokens of one request.
+
+Rows may be portions of prompts (of any length, cut anywhere) beside single decoded tokens, in
+any order.  The reference has three separate forward modes chosen by the cache object's type
+(src/scratch_llm/model.py:290-325, 493-498) and never mixes them; here one descriptor covers
+all of them:
+
+=============  ======================  ==================================================
+token_ids      int32 [n_tokens]        all rows' new tokens, row after row
+positions      int32 [n_tokens]        absolute position of each token in its request
+token_row      int32 [n_tokens]        row of each token
+row_start      int32 [n_rows + 1]      offset of each row's first token (cu_seqlens)
+row_pos0       int32 [n_rows]          position of each row's first new token
+row_slot       int32 [n_rows]          the request's state slot
+block_tables   int32 [n_rows, P] each  per cache group: physical page of each logical page
+logit_index    int32 [n_out]           flat token indices whose logits are wanted
+=============  ======================  ==================================================
+
+All of it is packed on the host into one pinned buffer and reaches the device in one copy.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Hashable, Sequence
+
+import numpy as np
+import torch
+
+
+@dataclass
+class RowInput:
+    """The next tokens of one request and the places among them whose logits are wanted."""
+
+    request_id: Hashable
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+@dataclass
+class StepBatch:
+    n_tokens: int
+    n_rows: int
+    n_out: int
+    max_new: int
+    max_context: int
+    token_ids: torch.Tensor
+    positions: torch.Tensor
+    token_row: torch.Tensor
+    row_start: torch.Tensor
+    row_pos0: torch.Tensor
+    row_slot: torch.Tensor
+    logit_index: torch.Tensor
+    block_tables: list[torch.Tensor] = field(default_factory=list)
+    # host copies, for parts that plan their launches from them
+    host_row_new: list[int] = field(default_factory=list)
+    host_row_pos0: list[int] = field(default_factory=list)
+
+
+class BatchStager:
+    """Packs step descriptors on the host and copies them to the device in one transfer.
+    Two pinned buffers alternate, each guarded by an event, so that packing step n+1 never
+    overwrites bytes that step n's copy is still reading."""
+
+    def __init__(self, device: torch.device, capacity_ints: int = 1 << 16) -> None:
+        self.device = device
+        self._host = [self._pinned(capacity_ints) for _ in range(2)]
+        self._events: list[torch.cuda.Event | None] = [None, None]
+        self._dev = torch.empty(capacity_ints, dtype=torch.int32, device=device)
+        self._turn = 0
+
+    @staticmethod
+    def _pinned(n: int) -> torch.Tensor:
+        return torch.empty(n, dtype=torch.int32, pin_memory=True)
+
+    def _grow(self, n: int) -> None:
+        cap = self._dev.numel()
+        while cap < n:
+            cap *= 2
+        torch.cuda.current_stream().synchronize()
+        self._host = [self._pinned(cap) for _ in range(2)]
+        self._events = [None, None]
+        self._dev = torch.empty(cap, dtype=torch.int32, device=self.device)
+
+    def upload(self, parts: Sequence[np.ndarray]) -> list[torch.Tensor]:
+        """Copy the int32 arrays to the device; returns one device view per array (each view
+        starts on a 16-byte boundary)."""
+        offsets, total = [], 0
+        for a in parts:
+            offsets.append(total)
+            total += (a.size + 3) // 4 * 4
+        if total > self._dev.numel():
+            self._grow(total)
+        turn = self._turn
+        self._turn ^= 1
+        if self._events[turn] is not None:
+            self._events[turn].synchronize()
+        host = self._host[turn]
+        hnp = host.numpy()
+        for a, o in zip(parts, offsets):
+            hnp[o:o + a.size] = a.reshape(-1)
+        if total:
+            self._dev[:total].copy_(host[:total], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._events[turn] = ev
+        return [self._dev[o:o + a.size].view(a.shape) for a, o in zip(parts, offsets)]

@@ -1,0 +1,272 @@
+"""Python bindings of the engine's CUDA kernels: one function per launcher of ``csrc/``.
+
+Each function checks devices, dtypes and layouts, passes raw pointers and the current CUDA
+stream through ctypes, and raises :class:`KernelError` on a non-zero return code.  There is no
+other implementation behind these functions: if a library cannot be compiled or loaded, the
+call fails.
+
+The reference reaches its compiled kernels through one pybind module (csrc/pybind.cpp:89-127)
+and a lazy dispatch table (src/scratch_llm/kernels/attention/dispatch.py:68-90).
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_int64, c_void_p
+from typing import Sequence
+
+import torch
+
+from . import build
+
+_DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+# library name -> (sources, defines)
+CORE_LIBRARIES: dict[str, tuple[tuple[str, ...], tuple[str, ...]]] = {
+    "sllm_elementwise": (("elementwise.cu",), ()),
+    "sllm_rope_cache": (("rope_cache.cu",), ()),
+    "sllm_gemm_simt": (("gemm_simt.cu",), ()),
+    "sllm_sampling": (("sampling.cu",), ()),
+}
+
+
+def attention_library(head_dim: int) -> tuple[str, tuple[str, ...], tuple[str, ...]]:
+    return (f"sllm_attention_simt_hd{head_dim}", ("attention_simt.cu",),
+            (f"SLLM_HEAD_DIM={head_dim}",))
+
+
+_loaded: dict[str, ctypes.CDLL] = {}
+
+
+def _load(name: str, sources: Sequence[str], defines: Sequence[str]) -> ctypes.CDLL:
+    lib = _loaded.get(name)
+    if lib is None:
+        path = build.compile_library(name, sources, defines)
+        try:
+            lib = ctypes.CDLL(str(path))
+        except OSError as exc:
+            raise KernelError(f"cannot load {path}: {exc}") from None
+        _loaded[name] = lib
+    return lib
+
+
+def _core(name: str) -> ctypes.CDLL:
+    return _load(name, *CORE_LIBRARIES[name])
+
+
+def prepare(head_dims: Sequence[int] = (), verbose: bool = True) -> None:
+    """Compile (in parallel) and load everything a model with these head sizes needs."""
+    jobs = [(n, s, d) for n, (s, d) in CORE_LIBRARIES.items()]
+    jobs += [attention_library(hd) for hd in sorted(set(head_dims))]
+    build.compile_many(jobs, verbose=verbose)
+    for n, s, d in jobs:
+        _load(n, s, d)
+
+
+def _check(code: int, what: str) -> None:
+    if code != 0:
+        raise KernelError(f"{what} failed with CUDA error {code} "
+                          f"({'invalid value: a size this kernel does not take' if code == 1 else 'see cudaError_t'})")
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t: torch.Tensor | None) -> c_void_p:
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+def _need(t: torch.Tensor, dtype: torch.dtype | None, name: str, contiguous: bool = True) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor: the engine has no CPU path")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
+    if contiguous and not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+
+
+def _code(dtype: torch.dtype) -> int:
+    try:
+        return _DTYPE_CODE[dtype]
+    except KeyError:
+        raise KernelError(f"unsupported dtype {dtype}: kernels take float32 and bfloat16") from None
+
+
+# ------------------------------------------------------------------------------ elementwise
+
+def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[n] = table[ids[n]] widened to 32-bit.  ids int32 [N]; table [V, d]; out f32 [N, d]."""
+    _need(ids, torch.int32, "ids")
+    _need(table, None, "table")
+    _need(out, torch.float32, "out")
+    n, d = ids.numel(), table.shape[1]
+    if out.shape != (n, d):
+        raise KernelError(f"out must be [{n}, {d}], got {list(out.shape)}")
+    _check(_core("sllm_elementwise").sllm_embed(
+        _ptr(ids), _ptr(table), _ptr(out), c_int(n), c_int(d), c_int(_code(table.dtype)),
+        _stream()), "embed")
+    return out
+
+
+def add_rmsnorm(resid: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor,
+                eps: float, out: torch.Tensor, index: torch.Tensor | None = None) -> torch.Tensor:
+    """resid += delta (if given), out = rmsnorm(resid) * weight.  With ``index`` only the rows
+    ``index`` are normed into out[0..len(index)) and resid is left as it was."""
+    _need(resid, torch.float32, "resid")
+    _need(weight, torch.float32, "weight")
+    _need(out, None, "out")
+    d = resid.shape[-1]
+    if delta is not None:
+        _need(delta, out.dtype, "delta")
+        if delta.shape != resid.shape:
+            raise KernelError("delta and resid differ in shape")
+    if weight.numel() != d or out.shape[-1] != d:
+        raise KernelError("norm width mismatch")
+    if index is not None:
+        _need(index, torch.int32, "index")
+        n_out = index.numel()
+    else:
+        n_out = resid.shape[0]
+    if out.shape[0] != n_out:
+        raise KernelError("out has the wrong number of rows")
+    _check(_core("sllm_elementwise").sllm_add_rmsnorm(
+        _ptr(resid), _ptr(delta), _ptr(index), _ptr(weight), c_float(eps), _ptr(out),
+        c_int(n_out), c_int(d), c_int(_code(out.dtype)), _stream()), "add_rmsnorm")
+    return out
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[n, f] = silu(gate_up[n, f]) * gate_up[n, F + f]."""
+    _need(gate_up, None, "gate_up")
+    _need(out, gate_up.dtype, "out")
+    n, two_f = gate_up.shape
+    if two_f % 2 or out.shape != (n, two_f // 2):
+        raise KernelError("swiglu shapes")
+    _check(_core("sllm_elementwise").sllm_swiglu(
+        _ptr(gate_up), _ptr(out), c_int(n), c_int(two_f // 2), c_int(_code(out.dtype)),
+        _stream()), "swiglu")
+    return out
+
+
+# ------------------------------------------------------------------------------------ gemm
+
+def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[M, N] = x[M, K] @ w[N, K]^T with 32-bit fused multiply-adds on the CUDA cores."""
+    _need(x, None, "x", contiguous=False)
+    _need(w, x.dtype, "w", contiguous=False)
+    _need(out, None, "out", contiguous=False)
+    (m, k), (n, k2) = x.shape, w.shape
+    if k != k2 or out.shape != (m, n) or x.stride(1) != 1 or w.stride(1) != 1 \
+            or out.stride(1) != 1:
+        raise KernelError(f"gemm shapes/strides: x {list(x.shape)}, w {list(w.shape)}, "
+                          f"out {list(out.shape)}")
+    _check(_core("sllm_gemm_simt").sllm_gemm_simt(
+        _ptr(x), _ptr(w), _ptr(out), c_int(m), c_int(n), c_int(k), c_int64(x.stride(0)),
+        c_int64(w.stride(0)), c_int64(out.stride(0)), c_int(_code(x.dtype)),
+        c_int(_code(out.dtype)), _stream()), "gemm_simt")
+    return out
+
+
+# --------------------------------------------------------------------------- rope and cache
+
+def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, token_row: torch.Tensor,
+                  cos: torch.Tensor | None, sin: torch.Tensor | None, pages: torch.Tensor,
+                  block_table: torch.Tensor, page_size: int, n_heads: int, n_kv_heads: int,
+                  head_dim: int, interleaved: bool, write: bool) -> None:
+    """Rotate q (in place) and k by their positions' angles; store k and v into the pages.
+    ``cos``/``sin`` None stores k as it is (the position encoding was applied before)."""
+    _need(qkv, None, "qkv")
+    _need(positions, torch.int32, "positions")
+    _need(token_row, torch.int32, "token_row")
+    _need(pages, qkv.dtype, "pages")
+    _need(block_table, torch.int32, "block_table", contiguous=False)
+    n = qkv.shape[0]
+    if qkv.shape[1] != (n_heads + 2 * n_kv_heads) * head_dim:
+        raise KernelError("qkv width does not match the head counts")
+    if pages.shape[1:] != (2, n_kv_heads, page_size, head_dim):
+        raise KernelError(f"pages must be [n_pages, 2, {n_kv_heads}, {page_size}, {head_dim}], "
+                          f"got {list(pages.shape)}")
+    rotate = cos is not None
+    if rotate:
+        _need(cos, torch.float32, "cos")
+        _need(sin, torch.float32, "sin")
+        if cos.shape[1] != head_dim // 2 or sin.shape != cos.shape:
+            raise KernelError("rotary table width")
+    if block_table.stride(1) != 1:
+        raise KernelError("block_table rows must be contiguous")
+    _check(_core("sllm_rope_cache").sllm_rope_kv_write(
+        _ptr(qkv), _ptr(positions), _ptr(token_row), _ptr(cos), _ptr(sin), _ptr(pages),
+        _ptr(block_table), c_int(block_table.stride(0)), c_int(page_size), c_int(n),
+        c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), c_int(int(rotate)),
+        c_int(int(interleaved)), c_int(int(write)), c_int(_code(qkv.dtype)), _stream()),
+        "rope_kv_write")
+
+
+# -------------------------------------------------------------------------------- attention
+
+def attention_simt(q: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor,
+                   page_size: int, row_start: torch.Tensor, row_pos0: torch.Tensor,
+                   out: torch.Tensor, n_rows: int, max_new: int, n_heads: int, n_kv_heads: int,
+                   head_dim: int, scale: float, window: int | None) -> torch.Tensor:
+    """Causal attention of the packed batch over the paged cache (CUDA cores, 32-bit math).
+    ``q`` may be a column slice of a wider buffer (the fused qkv)."""
+    _need(q, None, "q", contiguous=False)
+    _need(pages, q.dtype, "pages")
+    _need(out, q.dtype, "out", contiguous=False)
+    _need(block_table, torch.int32, "block_table", contiguous=False)
+    _need(row_start, torch.int32, "row_start")
+    _need(row_pos0, torch.int32, "row_pos0")
+    if q.stride(1) != 1 or out.stride(1) != 1 or q.shape[1] != n_heads * head_dim \
+            or out.shape != q.shape:
+        raise KernelError("attention q/out layout")
+    if pages.shape[1:] != (2, n_kv_heads, page_size, head_dim):
+        raise KernelError(f"pages must be [n_pages, 2, {n_kv_heads}, {page_size}, {head_dim}], "
+                          f"got {list(pages.shape)}")
+    if head_dim % 16 or not 16 <= head_dim <= 512:
+        raise KernelError(f"head size {head_dim}: the attention kernels take multiples of 16 "
+                          "from 16 to 512")
+    lib = _load(*attention_library(head_dim))
+    _check(lib.sllm_attn_simt(
+        _ptr(q), c_int64(q.stride(0)), _ptr(pages), _ptr(block_table),
+        c_int(block_table.stride(0)), c_int(page_size), _ptr(row_start), _ptr(row_pos0),
+        _ptr(out), c_int64(out.stride(0)), c_int(n_rows), c_int(max_new), c_int(n_heads),
+        c_int(n_kv_heads), c_float(scale), c_int(window or 0), c_int(_code(q.dtype)),
+        _stream()), "attention_simt")
+    return out
+
+
+# --------------------------------------------------------------------------------- sampling
+
+def sample(logits: torch.Tensor, out: torch.Tensor, temperature: torch.Tensor | None = None,
+           top_p: torch.Tensor | None = None, seed: torch.Tensor | None = None,
+           counter: torch.Tensor | None = None, logprob_out: torch.Tensor | None = None,
+           probs_out: torch.Tensor | None = None) -> torch.Tensor:
+    """Choose one token per row of ``logits`` [n, V] (32-bit).  Rows whose temperature is 0
+    (or all rows when ``temperature`` is None) take the argmax.  seed/counter: int64 [n]."""
+    _need(logits, torch.float32, "logits", contiguous=False)
+    _need(out, torch.int32, "out")
+    n, v = logits.shape
+    if logits.stride(1) != 1 or out.numel() != n:
+        raise KernelError("sample shapes")
+    for t, dt, name in ((temperature, torch.float32, "temperature"), (top_p, torch.float32, "top_p"),
+                        (seed, torch.int64, "seed"), (counter, torch.int64, "counter"),
+                        (logprob_out, torch.float32, "logprob_out")):
+        if t is not None:
+            _need(t, dt, name)
+            if t.numel() != n:
+                raise KernelError(f"{name} must have one entry per row")
+    if probs_out is not None:
+        _need(probs_out, torch.float32, "probs_out")
+        if probs_out.shape != (n, v):
+            raise KernelError("probs_out shape")
+    _check(_core("sllm_sampling").sllm_sample(
+        _ptr(logits), c_int64(logits.stride(0)), c_int(n), c_int(v), _ptr(temperature),
+        _ptr(top_p), _ptr(seed), _ptr(counter), _ptr(out), _ptr(logprob_out), _ptr(probs_out),
+        _stream()), "sample")
+    return out

@@ -1,0 +1,76 @@
+"""Grouped-query attention over the paged cache.
+
+q, k, v projections without bias (fused into one matrix at load), position encoding on q and
+k, the new keys and values stored into the request's pages, causal attention in which query
+head h reads kv head ``h // (n_heads / n_kv_heads)``, and the output projection:
+src/scratch_llm/model.py:265-366 of the reference.  ``scale`` multiplies the scores
+(``1/sqrt(head_dim)`` for this architecture, src/scratch_llm/model.py:177); ``window`` None
+attends to every earlier key, a number to the last ``window`` of them.
+"""
+
+from __future__ import annotations
+
+from typing import Mapping
+
+import torch
+
+from ..kernels import ops
+from ..weights.loader import ParamSpec
+from .base import BuildContext, CacheView, KVSpec, Mixer, PositionEncoding
+from .linear import Linear
+from .registry import register_mixer
+
+
+@register_mixer("gqa_attention")
+class GQAttention(Mixer):
+    def __init__(self, hidden_size: int, n_heads: int, n_kv_heads: int, head_dim: int,
+                 scale: float, window: int | None = None,
+                 names: Mapping[str, str] | None = None) -> None:
+        if n_heads % n_kv_heads:
+            raise ValueError(f"{n_heads} query heads do not group evenly over {n_kv_heads} "
+                             "kv heads")
+        if head_dim % 16 or not 16 <= head_dim <= 512:
+            raise ValueError(f"head size {head_dim}: the attention kernels take multiples of "
+                             "16 from 16 to 512")
+        self.hidden_size, self.n_heads, self.n_kv_heads = hidden_size, n_heads, n_kv_heads
+        self.head_dim, self.scale, self.window = head_dim, float(scale), window
+        self.names = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight",
+                      "o": "o_proj.weight", **(names or {})}
+        self.qkv: Linear | None = None
+        self.o: Linear | None = None
+
+    def kv_spec(self) -> KVSpec:
+        return KVSpec(self.n_kv_heads, self.head_dim, self.window)
+
+    def param_specs(self) -> dict[str, ParamSpec]:
+        hq, hk = self.n_heads * self.head_dim, self.n_kv_heads * self.head_dim
+        return {self.names["q"]: ParamSpec((hq, self.hidden_size)),
+                self.names["k"]: ParamSpec((hk, self.hidden_size)),
+                self.names["v"]: ParamSpec((hk, self.hidden_size)),
+                self.names["o"]: ParamSpec((self.hidden_size, hq))}
+
+    def load(self, tensors: Mapping[str, torch.Tensor], ctx: BuildContext) -> None:
+        put = lambda t: t.to(device=ctx.device, dtype=ctx.dtype)  # noqa: E731
+        self.qkv = Linear(torch.cat([put(tensors[self.names[n]]) for n in "qkv"], 0).contiguous())
+        self.o = Linear(put(tensors[self.names["o"]]).contiguous())
+
+    def forward(self, x: torch.Tensor, batch, cache: CacheView, write: bool,
+                position: PositionEncoding) -> torch.Tensor:
+        H, G, hd = self.n_heads, self.n_kv_heads, self.head_dim
+        qkv = self.qkv(x)
+        if position.rotary_tables:
+            cos, sin, interleaved = position.cos, position.sin, position.interleaved
+        else:
+            n = qkv.shape[0]
+            position.apply(qkv[:, :H * hd].view(n, H, hd), qkv[:, H * hd:(H + G) * hd].view(n, G, hd),
+                           batch.positions)
+            cos = sin = None
+            interleaved = True
+        ops.rope_kv_write(qkv, batch.positions, batch.token_row, cos, sin, cache.pages,
+                          cache.block_table, cache.page_size, H, G, hd, interleaved, write)
+        q = qkv[:, :H * hd]
+        out = torch.empty((qkv.shape[0], H * hd), dtype=qkv.dtype, device=qkv.device)
+        ops.attention_simt(q, cache.pages, cache.block_table, cache.page_size, batch.row_start,
+                           batch.row_pos0, out, batch.n_rows, batch.max_new, H, G, hd,
+                           self.scale, self.window)
+        return self.o(out)

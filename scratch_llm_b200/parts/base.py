@@ -1,0 +1,113 @@
+"""Interfaces of the parts a layer is put together from.
+
+A part is built from explicit sizes and constants (never from a model's configuration
+object), states which tensors it wants (:meth:`Part.param_specs`, names relative to its own
+prefix), receives them once (:meth:`Part.load`) and is then called by a block inside the step
+function.  No part knows which model it is in.
+
+=================  ==========================================================================
+part               call
+=================  ==========================================================================
+Norm               ``forward(resid, delta, out_rows=None) -> normed``: add the pending
+                   ``delta`` into the 32-bit residual stream, return norm(resid) in the compute
+                   dtype; with ``out_rows`` only those rows are normed and resid is not written
+PositionEncoding   ``apply(q, k, positions)`` in place on [N, heads, head_dim] views, or, for
+                   the rotary encoding, its tables handed to the fused rotate-and-store kernel
+Mixer              ``forward(x, batch, cache, write, position) -> [N, hidden]``; states what it
+                   caches through ``kv_spec()`` (paged keys and values) and ``state_spec()``
+                   (fixed-size state per request)
+FeedForward        ``forward(x) -> [N, hidden]``
+Block              ``forward(resid, pending, batch, cache, write) -> pending``: the arrangement
+                   of the four parts around the residual stream
+=================  ==========================================================================
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import TYPE_CHECKING, Mapping
+
+import torch
+
+from ..weights.loader import ParamSpec
+
+if TYPE_CHECKING:
+    from ..engine.batch import StepBatch
+
+
+@dataclass(frozen=True)
+class BuildContext:
+    """Where and in which precision a model is built.  ``dtype`` is the dtype of matrix-product
+    operands and of the cache: ``torch.bfloat16`` (serving) or ``torch.float32`` (everything in
+    true 32-bit)."""
+
+    dtype: torch.dtype
+    device: torch.device
+
+
+@dataclass(frozen=True)
+class KVSpec:
+    """Paged keys and values one cache entry needs per token.  ``window`` None keeps every key;
+    a number keeps the last ``window`` keys and lets older pages be given back."""
+
+    n_kv_heads: int
+    head_dim: int
+    window: int | None = None
+
+
+@dataclass(frozen=True)
+class StateSpec:
+    """State of fixed size that one cache entry keeps per live request."""
+
+    shape: tuple[int, ...]
+    dtype: torch.dtype
+
+
+@dataclass
+class CacheView:
+    """What one run of a layer sees of the cache in this step."""
+
+    pages: torch.Tensor | None = None        # [n_pages, 2, n_kv_heads, page_size, head_dim]
+    block_table: torch.Tensor | None = None  # int32 [rows, max_pages]; -1 where no page is held
+    page_size: int = 0
+    state: torch.Tensor | None = None        # [n_slots, *StateSpec.shape]
+
+
+class Part:
+    def param_specs(self) -> dict[str, ParamSpec]:
+        return {}
+
+    def load(self, tensors: Mapping[str, torch.Tensor], ctx: BuildContext) -> None:
+        """Take the part's tensors (CPU or device, as stored) onto the device in the dtype the
+        part computes in."""
+
+
+class Norm(Part):
+    def forward(self, resid: torch.Tensor, delta: torch.Tensor | None,
+                out_rows: torch.Tensor | None = None) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    #: True if the attention mixer may hand cos/sin tables to its fused rotate-and-store kernel
+    rotary_tables = False
+
+    def apply(self, q: torch.Tensor, k: torch.Tensor, positions: torch.Tensor) -> None:
+        raise NotImplementedError
+
+
+class Mixer(Part):
+    def kv_spec(self) -> KVSpec | None:
+        return None
+
+    def state_spec(self) -> StateSpec | None:
+        return None
+
+    def forward(self, x: torch.Tensor, batch: "StepBatch", cache: CacheView, write: bool,
+                position: PositionEncoding) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError
