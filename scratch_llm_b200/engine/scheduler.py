@@ -1,0 +1,275 @@
+"""Continuous batching: admits requests, cuts prompts into portions under a token budget,
+decodes, finishes and frees, and decides what happens when pages run out.
+
+The reference's scheduler (src/scratch_llm/serving/continuous.py:91-409) runs admission
+prefills and lockstep decodes as separate forwards, prefills one chunk of one request per
+iteration in its chunked mode (:335-369), finishes on the budget only (:276-279), and cannot
+run out of pages because it admits only what fits whole (:289-293).  Here every step is one
+mixed batch:
+
+1. every running request that is decoding gets its one token;
+2. requests that are still reading their prompt get portions, oldest first, each
+   ``min(rest of the prompt, chunk_size, budget left)``;
+3. queued requests are admitted, first come first served, while a state slot, budget and
+   pages for their first portion are there (``admission="reserve_full"`` instead admits only if
+   the pool can hold every live request up to its full budget, the reference's guard).
+
+**When pages run out** (only under ``admission="optimistic"``): a decoding request that cannot
+get the page for its next token sets back the most recently admitted live request (possibly
+itself): that request's pages and slot are freed, it returns to the front of the queue and is
+later recomputed from its prompt plus the tokens it had generated, then goes on.  A prompt
+portion that cannot get its pages is cut to what fits, or waits for a later step.  A request
+that alone could never fit the pool is refused when it is submitted.
+
+The scheduler is host-side logic over a :class:`CacheManager`; it runs without a GPU.
+"""
+
+from __future__ import annotations
+
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Hashable, Sequence
+
+from ..cache import CacheManager
+from ..sampling.params import SamplingParams
+
+
+@dataclass
+class Request:
+    """One generation job (src/scratch_llm/serving/continuous.py:44-50 of the reference, plus
+    sampling parameters; ``params.max_tokens`` is its max_new_tokens)."""
+
+    request_id: Hashable
+    prompt_ids: Sequence[int]
+    params: SamplingParams = field(default_factory=lambda: SamplingParams(temperature=0.0))
+
+
+@dataclass
+class Sequence_:
+    request: Request
+    tokens: list[int]                 # prompt + generated so far
+    n_prompt: int
+    order: int = -1                   # admission counter; larger = admitted later
+    logprobs: list[float] = field(default_factory=list)
+    n_preempted: int = 0
+    finish_reason: str | None = None
+    admitted_at_step: int = -1
+
+    @property
+    def generated(self) -> list[int]:
+        return self.tokens[self.n_prompt:]
+
+
+@dataclass
+class PlannedRow:
+    seq: Sequence_
+    start: int        # index of the first token fed (= tokens cached before the step)
+    n: int            # how many tokens are fed
+    samples: bool     # True if the row's last token is the sequence's last: logits wanted
+
+
+@dataclass
+class SchedulerStats:
+    steps: int = 0
+    prefill_tokens: int = 0
+    decode_tokens: int = 0
+    preemptions: int = 0
+    stalled_portions: int = 0
+    peak_live: int = 0
+    rows_per_step: list[int] = field(default_factory=list)
+    tokens_per_step: list[int] = field(default_factory=list)
+    page_occupancy: list[float] = field(default_factory=list)
+
+
+class Scheduler:
+    def __init__(self, cache: CacheManager, max_position: int, max_batch_tokens: int = 2048,
+                 chunk_size: int | None = None, admission: str = "optimistic",
+                 vocab_size: int | None = None) -> None:
+        if admission not in ("optimistic", "reserve_full"):
+            raise ValueError("admission is 'optimistic' or 'reserve_full'")
+        if max_batch_tokens < 1 or (chunk_size is not None and chunk_size < 1):
+            raise ValueError("max_batch_tokens and chunk_size must be positive")
+        self.cache, self.max_position = cache, max_position
+        self.max_batch_tokens, self.chunk_size = max_batch_tokens, chunk_size
+        self.admission, self.vocab_size = admission, vocab_size
+        self.queue: deque[Sequence_] = deque()
+        self.running: list[Sequence_] = []      # in admission order
+        self.finished: dict[Hashable, Sequence_] = {}
+        self.stats = SchedulerStats()
+        self._admissions = 0
+        self._known: set[Hashable] = set()
+
+    # ---------------------------------------------------------------------------- submit
+
+    def _pool_pages(self) -> int:
+        return min(g.pool.n_pages for g in self.cache.groups) if self.cache.groups else 1 << 60
+
+    def submit(self, request: Request) -> None:
+        prompt = list(request.prompt_ids)
+        p = request.params
+        if request.request_id in self._known:
+            raise ValueError(f"request id {request.request_id!r} was already submitted")
+        if not prompt:
+            raise ValueError("prompt_ids must be non-empty")
+        if self.vocab_size is not None and not all(0 <= t < self.vocab_size for t in prompt):
+            raise ValueError(f"prompt token out of range [0, {self.vocab_size})")
+        if len(prompt) + p.max_tokens > self.max_position:
+            raise ValueError(f"prompt ({len(prompt)}) + max_tokens ({p.max_tokens}) exceeds "
+                             f"max_position {self.max_position}")
+        need = -(-(len(prompt) + p.max_tokens - 1) // self.cache.page_size)
+        if need > self._pool_pages():
+            raise ValueError(f"request {request.request_id!r} needs {need} pages by its last "
+                             f"token but the pool has {self._pool_pages()}: it could never "
+                             "finish")
+        self._known.add(request.request_id)
+        self.queue.append(Sequence_(request, prompt, len(prompt)))
+
+    @property
+    def has_work(self) -> bool:
+        return bool(self.queue or self.running)
+
+    # ------------------------------------------------------------------------------ plan
+
+    def _cached(self, seq: Sequence_) -> int:
+        return self.cache.requests[seq.request.request_id].n_tokens
+
+    def _preempt(self, seq: Sequence_) -> None:
+        self.cache.release(seq.request.request_id)
+        self.running.remove(seq)
+        seq.n_preempted += 1
+        self.queue.appendleft(seq)
+        self.stats.preemptions += 1
+
+    def _fits(self, seq: Sequence_, n: int) -> int:
+        """The largest m <= n for which pages can be reserved now (0 if none)."""
+        rid = seq.request.request_id
+        if self.cache.reserve(rid, n):
+            return n
+        rc = self.cache.requests[rid]
+        ps = self.cache.page_size
+        room = min((len(t) + g.pool.n_free) * ps for t, g in zip(rc.tables, self.cache.groups))
+        m = min(n, room - rc.n_tokens)
+        if m >= 1 and self.cache.reserve(rid, m):
+            return m
+        return 0
+
+    def _committed_pages(self) -> int:
+        ps = self.cache.page_size
+        return sum(-(-(s.n_prompt + s.request.params.max_tokens - 1) // ps) for s in self.running)
+
+    def plan(self) -> list[PlannedRow]:
+        """Decide the next step's batch.  Reserves the pages its rows need."""
+        budget = self.max_batch_tokens
+        rows: list[PlannedRow] = []
+        # 1. decoding requests, oldest first; a page shortage sets back the newest request
+        for seq in list(self.running):
+            if seq not in self.running:      # set back while serving an older one
+                continue
+            cached = self._cached(seq)
+            if cached != len(seq.tokens) - 1 or budget < 1:
+                continue
+            rid = seq.request.request_id
+            while not self.cache.reserve(rid, 1):
+                victim = max(self.running, key=lambda s: s.order)
+                planned = [r for r in rows if r.seq is victim]
+                for r in planned:
+                    rows.remove(r)
+                    budget += r.n
+                self._preempt(victim)
+                if victim is seq:
+                    break
+            else:
+                rows.append(PlannedRow(seq, cached, 1, True))
+                budget -= 1
+        # 2. prompts in progress, oldest first
+        for seq in self.running:
+            cached = self._cached(seq)
+            rest = len(seq.tokens) - cached
+            if rest <= 1 and any(r.seq is seq for r in rows):
+                continue
+            if rest < 1 or budget < 1 or any(r.seq is seq for r in rows):
+                continue
+            n = min(rest, budget, self.chunk_size or rest)
+            m = self._fits(seq, n)
+            if m == 0:
+                self.stats.stalled_portions += 1
+                continue
+            rows.append(PlannedRow(seq, cached, m, cached + m == len(seq.tokens)))
+            budget -= m
+        # 3. admissions, first come first served, no skipping ahead
+        while self.queue and budget >= 1 and self.cache.n_free_slots > 0:
+            seq = self.queue[0]
+            if self.admission == "reserve_full":
+                ps = self.cache.page_size
+                need = -(-(seq.n_prompt + seq.request.params.max_tokens - 1) // ps)
+                if self._committed_pages() + need > self._pool_pages():
+                    break
+            n = min(len(seq.tokens), budget, self.chunk_size or len(seq.tokens))
+            rid = seq.request.request_id
+            assert self.cache.admit(rid) is not None
+            m = self._fits(seq, n)
+            if m == 0:
+                self.cache.release(rid)
+                break
+            self.queue.popleft()
+            seq.order = self._admissions
+            self._admissions += 1
+            if seq.admitted_at_step < 0:
+                seq.admitted_at_step = self.stats.steps
+            self.running.append(seq)
+            rows.append(PlannedRow(seq, 0, m, m == len(seq.tokens)))
+            budget -= m
+        # nothing can move although requests are live: the pool is full of half-read prompts
+        if not rows and self.running:
+            victim = max(self.running, key=lambda s: s.order)
+            if len(self.running) == 1:
+                raise RuntimeError("a single live request cannot get pages: the pool is too "
+                                   "small for it")
+            self._preempt(victim)
+            return self.plan()
+        return rows
+
+    # -------------------------------------------------------------------------- complete
+
+    def complete(self, rows: Sequence[PlannedRow], sampled: Sequence[int],
+                 logprobs: Sequence[float] | None = None) -> list[Sequence_]:
+        """The step ran: ``sampled`` holds one token for every row with ``samples`` set, in
+        order.  Returns the sequences that finished."""
+        done: list[Sequence_] = []
+        k = 0
+        st = self.stats
+        st.steps += 1
+        st.rows_per_step.append(len(rows))
+        st.tokens_per_step.append(sum(r.n for r in rows))
+        st.peak_live = max(st.peak_live, len(self.running))
+        for r in rows:
+            rid = r.seq.request.request_id
+            self.cache.commit(rid, r.n)
+            if r.n == 1 and r.start >= r.seq.n_prompt:
+                st.decode_tokens += 1
+            else:
+                st.prefill_tokens += r.n
+            if not r.samples:
+                continue
+            token = int(sampled[k])
+            if logprobs is not None:
+                r.seq.logprobs.append(float(logprobs[k]))
+            k += 1
+            seq = r.seq
+            seq.tokens.append(token)
+            p = seq.request.params
+            if token in p.stop_ids:
+                seq.finish_reason = "stop"       # the stop token is kept in the output
+            elif len(seq.generated) >= p.max_tokens:
+                seq.finish_reason = "length"
+            elif len(seq.tokens) >= self.max_position:
+                seq.finish_reason = "max_position"
+            if seq.finish_reason:
+                self.cache.release(rid)
+                self.running.remove(seq)
+                self.finished[rid] = seq
+                done.append(seq)
+        if self.cache.groups:
+            g = self.cache.groups[0]
+            st.page_occupancy.append(1.0 - g.pool.n_free / g.pool.n_pages)
+        return done

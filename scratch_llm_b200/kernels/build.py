@@ -50,7 +50,18 @@ def find_nvcc() -> str:
                      "engine's CUDA kernels cannot be compiled, and there is no fallback")
 
 
+_build_dir: Path | None = None
+
+
 def build_dir() -> Path:
+    global _build_dir
+    with _lock:
+        if _build_dir is None:
+            _build_dir = _pick_build_dir()
+        return _build_dir
+
+
+def _pick_build_dir() -> Path:
     override = os.environ.get("SCRATCH_LLM_B200_BUILD_DIR")
     candidates = [Path(override)] if override else []
     candidates.append(Path(__file__).resolve().parent.parent / "_build")

@@ -1,0 +1,6 @@
+"""Greedy, temperature and nucleus sampling."""
+
+from .params import SamplingParams
+from .sampler import Sampler
+
+__all__ = ["Sampler", "SamplingParams"]

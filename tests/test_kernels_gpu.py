@@ -1,0 +1,244 @@
+"""Each CUDA kernel alone against its plain reference, at sizes other than the engine's."""
+
+import math
+
+import pytest
+import torch
+
+from plain import llama_plain as P
+
+pytestmark = pytest.mark.gpu
+
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+TOL = {"float32": dict(rtol=1e-5, atol=1e-6), "bfloat16": dict(rtol=1.6e-2, atol=1e-2)}
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from scratch_llm_b200.kernels import ops
+    ops.prepare([16, 48, 80, 128], verbose=False)
+    return ops
+
+
+def rand(*shape, dtype=torch.float32, seed=0, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_embed(ops, dtype):
+    table = rand(1000, 200, dtype=DT[dtype])
+    ids = torch.tensor([0, 999, 5, 5, 123], dtype=torch.int32)
+    out = torch.empty(5, 200, dtype=torch.float32, device="cuda")
+    ops.embed(ids.cuda(), table.cuda(), out)
+    assert torch.equal(out.cpu(), P.embed(ids.long(), table).float())
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("d, eps", [(4096, 1e-5), (120, 1e-6), (7, 1e-3), (5000, 1e-5)])
+def test_add_rmsnorm(ops, dtype, d, eps):
+    n = 9
+    resid, delta = rand(n, d, seed=1), rand(n, d, dtype=DT[dtype], seed=2)
+    w = rand(d, seed=3) + 1.0
+    want_resid = resid + delta.float()
+    want = P.rmsnorm(want_resid, w, eps)
+    r = resid.cuda()
+    out = torch.empty(n, d, dtype=DT[dtype], device="cuda")
+    ops.add_rmsnorm(r, delta.cuda(), w.cuda(), eps, out)
+    torch.testing.assert_close(r.cpu(), want_resid, rtol=0, atol=0)
+    torch.testing.assert_close(out.cpu().float(), want, **TOL[dtype])
+    # without a delta the stream is left alone
+    r2 = resid.cuda()
+    ops.add_rmsnorm(r2, None, w.cuda(), eps, out)
+    assert torch.equal(r2.cpu(), resid)
+    torch.testing.assert_close(out.cpu().float(), P.rmsnorm(resid, w, eps), **TOL[dtype])
+    # gathered rows: only those rows, delta added on the fly, stream untouched
+    idx = torch.tensor([7, 0, 7, 3], dtype=torch.int32)
+    r3 = resid.cuda()
+    out4 = torch.empty(4, d, dtype=DT[dtype], device="cuda")
+    ops.add_rmsnorm(r3, delta.cuda(), w.cuda(), eps, out4, idx.cuda())
+    assert torch.equal(r3.cpu(), resid)
+    torch.testing.assert_close(out4.cpu().float(), want[idx.long()], **TOL[dtype])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_swiglu(ops, dtype):
+    gu = rand(13, 2 * 301, dtype=DT[dtype], scale=3.0)
+    out = torch.empty(13, 301, dtype=DT[dtype], device="cuda")
+    ops.swiglu(gu.cuda(), out)
+    g, u = gu.float()[:, :301], gu.float()[:, 301:]
+    torch.testing.assert_close(out.cpu().float(), g * torch.sigmoid(g) * u, **TOL[dtype])
+
+
+@pytest.mark.parametrize("m, n, k", [(1, 100, 64), (70, 130, 200), (64, 64, 16), (3, 5, 7),
+                                     (129, 257, 33)])
+def test_gemm_simt_is_true_32_bit(ops, m, n, k):
+    x, w = rand(m, k, seed=1), rand(n, k, seed=2)
+    out = torch.empty(m, n, dtype=torch.float32, device="cuda")
+    ops.gemm_simt(x.cuda(), w.cuda(), out)
+    want = (x.double() @ w.double().T)
+    # a tf32 product would be wrong by ~1e-3 relative; 32-bit accumulation by ~1e-6
+    torch.testing.assert_close(out.cpu().double(), want, rtol=1e-5, atol=1e-5 * math.sqrt(k))
+    # a row's result does not depend on the other rows of the batch: bitwise
+    one = torch.empty(1, n, dtype=torch.float32, device="cuda")
+    ops.gemm_simt(x[m // 2:m // 2 + 1].cuda(), w.cuda(), one)
+    assert torch.equal(one.cpu()[0], out.cpu()[m // 2])
+
+
+def test_gemm_simt_bfloat16_inputs(ops):
+    x, w = rand(17, 96, dtype=torch.bfloat16, seed=1), rand(50, 96, dtype=torch.bfloat16, seed=2)
+    out = torch.empty(17, 50, dtype=torch.float32, device="cuda")
+    ops.gemm_simt(x.cuda(), w.cuda(), out)
+    torch.testing.assert_close(out.cpu(), x.float() @ w.float().T, rtol=1e-5, atol=1e-5)
+
+
+def paged_cache(k, v, page_size, n_pages, seed, dtype):
+    """Scatter k, v [G, T, hd] of several rows into shuffled pages.  Returns pages, tables."""
+    g = torch.Generator().manual_seed(seed)
+    G, hd = k[0].shape[0], k[0].shape[2]
+    pages = torch.full((n_pages, 2, G, page_size, hd), float("nan")).to(dtype)
+    order = torch.randperm(n_pages, generator=g).tolist()
+    width = max(-(-kk.shape[1] // page_size) for kk in k)
+    table = torch.full((len(k), width), -1, dtype=torch.int32)
+    for r, (kk, vv) in enumerate(zip(k, v)):
+        for p in range(-(-kk.shape[1] // page_size)):
+            phys = order.pop()
+            table[r, p] = phys
+            n = min(page_size, kk.shape[1] - p * page_size)
+            pages[phys, 0, :, :n] = kk[:, p * page_size:p * page_size + n].to(dtype)
+            pages[phys, 1, :, :n] = vv[:, p * page_size:p * page_size + n].to(dtype)
+    return pages, table
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H, G, hd, page, window", [(4, 2, 16, 16, None), (6, 3, 48, 8, None),
+                                                    (8, 1, 128, 32, None), (5, 5, 80, 4, None),
+                                                    (4, 2, 16, 16, 37), (6, 2, 48, 8, 5)])
+def test_attention_over_pages(ops, dtype, H, G, hd, page, window):
+    # rows: (cached before this step, new tokens): a whole prompt, portions, single tokens
+    rows = [(0, 70), (33, 1), (64, 18), (100, 2), (0, 1), (255, 1), (17, 47)]
+    dt = DT[dtype]
+    ks = [rand(G, a + n, hd, seed=10 + i).to(dt).float() for i, (a, n) in enumerate(rows)]
+    vs = [rand(G, a + n, hd, seed=50 + i).to(dt).float() for i, (a, n) in enumerate(rows)]
+    qs = [rand(H, n, hd, seed=90 + i).to(dt).float() for i, (a, n) in enumerate(rows)]
+    # a far key among hundreds: in the row with 255 cached keys, key 3 of kv head 0 points
+    # along the query and is scaled so that its score stands out
+    far = 5
+    ks[far][0, 3] = qs[far][0, 0] / qs[far][0, 0].norm() * 12.0
+    ks[far] = ks[far].to(dt).float()
+    n_pages = sum(-(-(a + n) // page) for a, n in rows) + 3
+    pages, table = paged_cache(ks, vs, page, n_pages, seed=7, dtype=dt)
+    scale = 1.0 / math.sqrt(hd)
+    q_flat = torch.cat([q.transpose(0, 1).reshape(q.shape[1], H * hd) for q in qs]).to(dt)
+    # q lives inside a wider buffer, as in the fused qkv
+    wide = torch.zeros(q_flat.shape[0], H * hd + 64, dtype=dt)
+    wide[:, :H * hd] = q_flat
+    wide = wide.cuda()
+    row_start = torch.tensor([0] + list(torch.tensor([n for _, n in rows]).cumsum(0)), dtype=torch.int32)
+    row_pos0 = torch.tensor([a for a, _ in rows], dtype=torch.int32)
+    out = torch.empty(q_flat.shape[0], H * hd, dtype=dt, device="cuda")
+    ops.attention_simt(wide[:, :H * hd], pages.cuda(), table.cuda(), page, row_start.cuda(),
+                       row_pos0.cuda(), out, len(rows), max(n for _, n in rows), H, G, hd, scale,
+                       window)
+    got = out.cpu().float()
+    t = 0
+    for i, (a, n) in enumerate(rows):
+        want = P.attention(qs[i], ks[i], vs[i], torch.arange(a, a + n), torch.arange(a + n),
+                           scale, window)
+        want = want.transpose(0, 1).reshape(n, H * hd)
+        torch.testing.assert_close(got[t:t + n], want, **TOL[dtype],
+                                   msg=lambda m: f"row {i} {rows[i]}: {m}")
+        t += n
+    if window is None:
+        # the far key took nearly all the weight of head 0 in its row
+        t_far = int(row_start[far])
+        torch.testing.assert_close(got[t_far, :hd], vs[far][0, 3], rtol=0.05, atol=0.05)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("interleaved", [True, False])
+def test_rope_and_cache_write(ops, dtype, interleaved):
+    H, G, hd, page, theta, max_pos = 3, 2, 48, 8, 50000.0, 300
+    dt = DT[dtype]
+    pos = torch.tensor([0, 1, 2, 250, 7, 8, 9, 10, 299], dtype=torch.int32)
+    row = torch.tensor([0, 0, 0, 1, 2, 2, 2, 2, 3], dtype=torch.int32)
+    n = len(pos)
+    qkv = rand(n, (H + 2 * G) * hd, dtype=dt, seed=4)
+    cos, sin = P.rope_tables(hd, max_pos, theta)
+    table = torch.full((4, 38), -1, dtype=torch.int32)
+    table[0, 0], table[1, 31], table[2, 0], table[2, 1], table[3, 37] = 5, 2, 9, 0, 7
+    pages = torch.zeros(10, 2, G, page, hd, dtype=dt).cuda()
+    buf = qkv.clone().cuda()
+    ops.rope_kv_write(buf, pos.cuda(), row.cuda(), cos.cuda(), sin.cuda(), pages, table.cuda(),
+                      page, H, G, hd, interleaved, True)
+    q = qkv[:, :H * hd].float().view(n, H, hd).transpose(0, 1)
+    k = qkv[:, H * hd:(H + G) * hd].float().view(n, G, hd).transpose(0, 1)
+    v = qkv[:, (H + G) * hd:].float().view(n, G, hd)
+    q_want = P.apply_rope(q, pos.long(), cos, sin, interleaved).transpose(0, 1).reshape(n, H * hd)
+    k_want = P.apply_rope(k, pos.long(), cos, sin, interleaved).transpose(0, 1)
+    got = buf.cpu().float()
+    torch.testing.assert_close(got[:, :H * hd], q_want, **TOL[dtype])
+    assert torch.equal(got[:, H * hd:], qkv[:, H * hd:].float())  # k, v of the buffer untouched
+    pg = pages.cpu().float()
+    for i in range(n):
+        phys, off = int(table[row[i], pos[i] // page]), int(pos[i]) % page
+        torch.testing.assert_close(pg[phys, 0, :, off], k_want[i], **TOL[dtype])
+        assert torch.equal(pg[phys, 1, :, off], v[i])
+    assert int((pg != 0).any(dim=-1).sum()) == n * 2 * G  # nothing else was written
+    # write=False rotates q only
+    pages2 = torch.zeros_like(pages)
+    ops.rope_kv_write(qkv.clone().cuda(), pos.cuda(), row.cuda(), cos.cuda(), sin.cuda(), pages2,
+                      table.cuda(), page, H, G, hd, interleaved, False)
+    assert not pages2.any()
+
+
+def test_sampling_greedy_ties_and_logprob(ops):
+    V = 1000
+    logits = rand(4, V, seed=5)
+    logits[1, 700] = logits[1, 20] = 9.0   # a tie: the first maximum wins
+    logits[2] = -1e30
+    logits[2, 999] = 0.0
+    out = torch.empty(4, dtype=torch.int32, device="cuda")
+    lp = torch.empty(4, dtype=torch.float32, device="cuda")
+    ops.sample(logits.cuda(), out, logprob_out=lp)
+    want = logits.argmax(-1)
+    want[1] = 20
+    assert out.cpu().tolist() == want.tolist()
+    torch.testing.assert_close(lp.cpu(), torch.log_softmax(logits, -1)[torch.arange(4), want],
+                               rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("V", [331, 50000])
+def test_sampling_distribution_and_draws(ops, V):
+    logits = rand(3, V, seed=6, scale=2.0)
+    temps = torch.tensor([0.7, 1.0, 1.3])
+    tops = torch.tensor([0.9, 1.0, 0.5])
+    probs = torch.empty(3, V, dtype=torch.float32, device="cuda")
+    out = torch.empty(3, dtype=torch.int32, device="cuda")
+    seed = torch.tensor([1, 2, 3], dtype=torch.int64).cuda()
+    ctr = torch.zeros(3, dtype=torch.int64).cuda()
+    ops.sample(logits.cuda(), out, temps.cuda(), tops.cuda(), seed, ctr, probs_out=probs)
+    for r in range(3):
+        want = P.sampling_distribution(logits[r], float(temps[r]), float(tops[r]))
+        got = probs[r].cpu()
+        # the kept sets agree except possibly for tokens whose mass sits on the top-p edge
+        differ = (got > 0) != (want > 0)
+        assert differ.sum() <= 1
+        if not differ.any():
+            torch.testing.assert_close(got, want, rtol=1e-4, atol=1e-7)
+        assert got[out[r].item()] > 0
+    # the same (seed, counter) draws the same token; counters walk through the distribution
+    again = torch.empty(3, dtype=torch.int32, device="cuda")
+    ops.sample(logits.cuda(), again, temps.cuda(), tops.cuda(), seed, ctr)
+    assert torch.equal(out, again)
+    n_draws = 4000
+    big = logits[2:3].expand(n_draws, V).contiguous().cuda()
+    draws = torch.empty(n_draws, dtype=torch.int32, device="cuda")
+    ops.sample(big, draws, torch.full((n_draws,), 1.3).cuda(), torch.full((n_draws,), 0.5).cuda(),
+               torch.full((n_draws,), 77, dtype=torch.int64).cuda(),
+               torch.arange(n_draws, dtype=torch.int64).cuda())
+    freq = torch.bincount(draws.cpu().long(), minlength=V).float() / n_draws
+    want = P.sampling_distribution(logits[2], 1.3, 0.5)
+    assert freq[want == 0].sum() <= 1.0 / n_draws * 2
+    top = want.argsort(descending=True)[:5]
+    torch.testing.assert_close(freq[top], want[top], rtol=0.3, atol=0.01)

@@ -1,0 +1,100 @@
+"""Replay on the GPU: every way of cutting the same requests into steps gives the logits of
+the plain implementation, in 32-bit and in bfloat16."""
+
+import pytest
+import torch
+
+import trace_util as T
+from configs import CONFIGS, PAGE_SIZE
+from plain import llama_plain as P
+
+pytestmark = pytest.mark.gpu
+
+LENGTHS = {"A": [5, 17, 33, 70, 128, 64, 15, 16, 90, 31, 120],
+           "B": [2, 9, 40, 64, 100, 130, 47, 17, 80, 33, 200, 8, 150],
+           "C": [34, 95, 200, 61, 150, 333, 16, 640, 48, 100]}
+# 32-bit: a few ulp of the largest logit per reduction; bfloat16: operands rounded to 8 bits
+TOL = {"float32": dict(rtol=2e-5, atol=5e-6), "bfloat16": dict(rtol=3e-2, atol=3e-2)}
+
+
+@pytest.fixture(scope="module")
+def expected(model_dirs):
+    """Plain logits [S, V] per configuration, dtype and request.  For bfloat16 the plain model
+    runs in 32-bit on the weights rounded to bfloat16, which is what the engine holds."""
+    cache = {}
+
+    def get(name, dtype):
+        if (name, dtype) not in cache:
+            cfg, w = P.read_model_dir(model_dirs[name])
+            if dtype == "bfloat16":
+                w = {k: v.to(torch.bfloat16).float() for k, v in w.items()}
+            reqs = T.make_requests(cfg["vocab_size"], LENGTHS[name], seed=11)
+            cache[(name, dtype)] = (reqs, {rid: P.forward(cfg, w, toks) for rid, toks in reqs.items()})
+        return cache[(name, dtype)]
+    return get
+
+
+def make_runner(model_dir, dtype, page_size, max_tokens, max_requests=4):
+    from scratch_llm_b200.engine import ModelRunner, load_model
+    model = load_model(model_dir, dtype, verbose=False)
+    return ModelRunner(model, page_size, -(-max_tokens // page_size), max_requests)
+
+
+def compare(got, want_logits, dtype):
+    assert got, "the trace produced no logits"
+    worst = 0.0
+    for (rid, pos), row in sorted(got.items()):
+        ref = want_logits[rid][pos]
+        worst = max(worst, float((row - ref).abs().max()))
+        torch.testing.assert_close(row, ref, **TOL[dtype],
+                                   msg=lambda m: f"request {rid} position {pos}: {m}")
+    return worst
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("way", ["whole", "tail", "portions", "mixed"])
+def test_replay_matches_plain(way, name, dtype, model_dirs, expected):
+    reqs, want = expected(name, dtype)
+    steps = {"whole": T.whole, "tail": T.tail_one_by_one, "portions": T.changing_portions,
+             "mixed": T.mixed}[way](reqs)
+    peak = T.peak_tokens(steps)
+    runner = make_runner(model_dirs[name], dtype, PAGE_SIZE[name], peak)
+    with torch.no_grad():
+        got = T.run_in_process(runner, steps)
+    assert len(got) == sum(len(t) for t in reqs.values())
+    compare(got, want, dtype)
+    assert not runner.cache.requests and all(
+        g.pool.n_free == g.pool.n_pages for g in runner.cache.groups)
+    if way == "mixed":
+        # the pool is smaller than what all requests need together: pages were used again
+        total_pages = sum(-(-len(t) // PAGE_SIZE[name]) for t in reqs.values())
+        assert runner.cache.groups[0].pool.n_pages < total_pages
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(dtype, model_dirs, expected, tmp_path):
+    reqs, want = expected("B", dtype)
+    steps = T.mixed(reqs, seed=3)
+    # some steps want nothing, some only a few places
+    for s in steps[::3]:
+        for e in s["entries"]:
+            e["want"] = []
+    for s in steps[1::3]:
+        for e in s["entries"]:
+            e["want"] = e["want"][-1:]
+    got = T.run_program(model_dirs["B"], dtype, steps, tmp_path / "out", T.peak_tokens(steps),
+                        CONFIGS["B"]["vocab_size"], extra=["--page-size", "8"])
+    compare(got, want, dtype)
+
+
+def test_cutting_does_not_change_logits_beyond_rounding(model_dirs, expected):
+    reqs, _ = expected("C", "float32")
+    runner = make_runner(model_dirs["C"], "float32", 16, T.peak_tokens(T.whole(reqs)))
+    with torch.no_grad():
+        a = T.run_in_process(runner, T.whole(reqs))
+        b = T.run_in_process(runner, T.changing_portions(reqs))
+        c = T.run_in_process(runner, T.tail_one_by_one(reqs))
+    for key in a:
+        torch.testing.assert_close(a[key], b[key], rtol=1e-5, atol=2e-6)
+        torch.testing.assert_close(a[key], c[key], rtol=1e-5, atol=2e-6)
