@@ -105,3 +105,66 @@ class BatchStager:
         ev.record()
         self._events[turn] = ev
         return [self._dev[o:o + a.size].view(a.shape) for a, o in zip(parts, offsets)]
+
+
+def build_batch(cache, stager: BatchStager, rows: Sequence[RowInput], vocab_size: int,
+                max_position: int) -> StepBatch:
+    """Check the rows against the cache manager's view of their requests, pack the descriptor
+    and copy it to the device."""
+    n_rows = len(rows)
+    lens = [len(r.tokens) for r in rows]
+    n_tokens = sum(lens)
+    token_ids = np.empty(n_tokens, dtype=np.int32)
+    positions = np.empty(n_tokens, dtype=np.int32)
+    token_row = np.empty(n_tokens, dtype=np.int32)
+    row_start = np.zeros(n_rows + 1, dtype=np.int32)
+    row_pos0 = np.empty(n_rows, dtype=np.int32)
+    row_slot = np.empty(n_rows, dtype=np.int32)
+    logit_index: list[int] = []
+    seen: set[Hashable] = set()
+    t = 0
+    for i, row in enumerate(rows):
+        n = lens[i]
+        if n < 1:
+            raise ValueError(f"request {row.request_id!r}: a row needs at least one token")
+        if row.request_id in seen:
+            raise ValueError(f"request {row.request_id!r} appears twice in one step")
+        seen.add(row.request_id)
+        rc = cache.requests.get(row.request_id)
+        if rc is None:
+            raise KeyError(f"request {row.request_id!r} is not live: admit it first")
+        if rc.n_tokens + n > max_position:
+            raise ValueError(f"request {row.request_id!r}: position {rc.n_tokens + n - 1} "
+                             f"is beyond max_position {max_position}")
+        ids = np.asarray(row.tokens, dtype=np.int64)
+        if ids.min() < 0 or ids.max() >= vocab_size:
+            raise ValueError(f"request {row.request_id!r}: token id out of range "
+                             f"[0, {vocab_size})")
+        token_ids[t:t + n] = ids
+        positions[t:t + n] = np.arange(rc.n_tokens, rc.n_tokens + n)
+        token_row[t:t + n] = i
+        row_pos0[i], row_slot[i] = rc.n_tokens, rc.slot
+        for w in row.want:
+            if not 0 <= w < n:
+                raise ValueError(f"request {row.request_id!r}: wanted place {w} is not "
+                                 f"among its {n} tokens")
+            logit_index.append(t + w)
+        t += n
+        row_start[i + 1] = t
+    tables = []
+    for g in range(len(cache.groups)):
+        width = max(len(cache.table_of(r.request_id, g)) for r in rows)
+        tab = np.full((n_rows, max(width, 1)), -1, dtype=np.int32)
+        for i, r in enumerate(rows):
+            pages = cache.table_of(r.request_id, g)
+            tab[i, :len(pages)] = pages
+        tables.append(tab)
+    li = np.asarray(logit_index, dtype=np.int32)
+    dev = stager.upload([token_ids, positions, token_row, row_start, row_pos0,
+                               row_slot, li, *tables])
+    return StepBatch(
+        n_tokens=n_tokens, n_rows=n_rows, n_out=len(logit_index), max_new=max(lens),
+        max_context=int(max(p + n for p, n in zip(row_pos0.tolist(), lens))),
+        token_ids=dev[0], positions=dev[1], token_row=dev[2], row_start=dev[3],
+        row_pos0=dev[4], row_slot=dev[5], logit_index=dev[6], block_tables=dev[7:],
+        host_row_new=lens, host_row_pos0=row_pos0.tolist())

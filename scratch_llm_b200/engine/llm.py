@@ -1,0 +1,149 @@
+"""The Python entry point: a model folder in, generated token ids out.
+
+The reference's entry points are ``generate(model, prompt_ids, params, device, use_cache)``
+returning the generated ids only (src/scratch_llm/sampling.py:185-204),
+``generate_with_logprobs`` (:207-217) and ``serve_continuous(model, requests, n_slots, ...)``
+returning completed requests with their tokens (src/scratch_llm/serving/continuous.py:412-446).
+:class:`LLM` offers the same three on top of the scheduler and the step function; host token
+ids go in, host token ids come out.
+"""
+
+from __future__ import annotations
+
+import time
+import zlib
+from dataclasses import dataclass
+from pathlib import Path
+from typing import Hashable, Sequence
+
+import torch
+
+from ..sampling import Sampler, SamplingParams
+from .batch import RowInput
+from .runner import ModelRunner, load_model
+from .scheduler import Request, Scheduler, SchedulerStats, Sequence_
+
+
+@dataclass(frozen=True)
+class Completed:
+    """A finished request (src/scratch_llm/serving/continuous.py:53-66 of the reference)."""
+
+    request: Request
+    token_ids: tuple[int, ...]
+    logprobs: tuple[float, ...] | None
+    finish_reason: str
+    admitted_at_step: int
+    n_preempted: int
+
+
+@dataclass(frozen=True)
+class ServeResult:
+    completed: tuple[Completed, ...]   # in the order the requests were given
+    stats: SchedulerStats
+    wall_s: float
+
+
+def _seed_of(request: Request) -> int:
+    if request.params.seed is not None:
+        return int(request.params.seed)
+    return zlib.crc32(repr(request.request_id).encode("utf-8"))
+
+
+class LLM:
+    """``max_tokens`` is the cache capacity in tokens (the page pool holds that many);
+    ``max_requests`` the number of requests that can be live at once; ``max_batch_tokens`` the
+    token budget of one step; ``chunk_size`` the largest prompt portion per request and step
+    (None: the budget alone cuts prompts)."""
+
+    def __init__(self, model: str | Path, dtype: str = "bfloat16", max_tokens: int = 65536,
+                 page_size: int = 16, max_requests: int = 64, max_batch_tokens: int = 2048,
+                 chunk_size: int | None = None, admission: str = "optimistic",
+                 verbose: bool = False) -> None:
+        self.model = load_model(model, dtype, verbose=verbose) if isinstance(model, (str, Path)) \
+            else model
+        self.runner = ModelRunner(self.model, page_size, max(1, -(-max_tokens // page_size)),
+                                  max_requests)
+        self.sampler = Sampler(self.runner.device)
+        self.max_batch_tokens, self.chunk_size, self.admission = (max_batch_tokens, chunk_size,
+                                                                  admission)
+
+    def _scheduler(self) -> Scheduler:
+        return Scheduler(self.runner.cache, self.runner.max_position, self.max_batch_tokens,
+                         self.chunk_size, self.admission, self.runner.vocab_size)
+
+    # ------------------------------------------------------------------------------ serve
+
+    @torch.no_grad()
+    def serve(self, requests: Sequence[Request], want_logprobs: bool = False) -> ServeResult:
+        """Run ``requests`` to completion under continuous batching."""
+        sched = self._scheduler()
+        for r in requests:
+            sched.submit(r)
+        start = time.perf_counter()
+        try:
+            while sched.has_work:
+                rows = sched.plan()
+                inputs = [RowInput(r.seq.request.request_id, r.seq.tokens[r.start:r.start + r.n],
+                                   [r.n - 1] if r.samples else []) for r in rows]
+                logits = self.runner.step(inputs)
+                sampling = [r.seq for r in rows if r.samples]
+                tokens, lps = [], None
+                if sampling:
+                    tokens, lps = self.sampler.sample(
+                        logits, [s.request.params for s in sampling],
+                        [_seed_of(s.request) for s in sampling],
+                        [len(s.generated) for s in sampling], want_logprobs)
+                sched.complete(rows, tokens, lps)
+        finally:
+            for seq in list(sched.running):   # an error leaves nothing held
+                self.runner.cache.release(seq.request.request_id)
+        wall = time.perf_counter() - start
+        done = []
+        for r in requests:
+            seq: Sequence_ = sched.finished[r.request_id]
+            done.append(Completed(r, tuple(seq.generated),
+                                  tuple(seq.logprobs) if want_logprobs else None,
+                                  seq.finish_reason or "", seq.admitted_at_step, seq.n_preempted))
+        return ServeResult(tuple(done), sched.stats, wall)
+
+    # --------------------------------------------------------------------------- generate
+
+    def generate(self, prompts, params: SamplingParams | Sequence[SamplingParams] | None = None):
+        """Generated token ids (without the prompt; a stop token is included) for one prompt
+        (a list of ints -> a list of ints) or several (a list of lists -> a list of lists)."""
+        return self._generate(prompts, params, False)[0]
+
+    def generate_with_logprobs(self, prompts, params=None):
+        """Like :meth:`generate`, and each token's log-probability under the raw model
+        distribution at temperature 1."""
+        return self._generate(prompts, params, True)
+
+    def _generate(self, prompts, params, want_logprobs):
+        single = len(prompts) > 0 and isinstance(prompts[0], int)
+        plist = [list(prompts)] if single else [list(p) for p in prompts]
+        if params is None:
+            params = SamplingParams()
+        pl = [params] * len(plist) if isinstance(params, SamplingParams) else list(params)
+        if len(pl) != len(plist):
+            raise ValueError("one SamplingParams per prompt, or one for all")
+        result = self.serve([Request(i, p, sp) for i, (p, sp) in enumerate(zip(plist, pl))],
+                            want_logprobs)
+        toks = [list(c.token_ids) for c in result.completed]
+        lps = [list(c.logprobs) for c in result.completed] if want_logprobs else None
+        if single:
+            return toks[0], (lps[0] if lps else None)
+        return toks, lps
+
+
+def generate(llm: LLM, prompt_ids: Sequence[int], params: SamplingParams) -> list[int]:
+    """The reference's ``generate`` with the engine in the model's place."""
+    return llm.generate(list(prompt_ids), params)
+
+
+def generate_with_logprobs(llm: LLM, prompt_ids: Sequence[int], params: SamplingParams
+                           ) -> tuple[list[int], list[float]]:
+    return llm.generate_with_logprobs(list(prompt_ids), params)
+
+
+def serve_continuous(llm: LLM, requests: Sequence[Request]) -> ServeResult:
+    return llm.serve(requests)

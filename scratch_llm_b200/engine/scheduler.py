@@ -231,10 +231,16 @@ class Scheduler:
 
     # -------------------------------------------------------------------------- complete
 
+    def commit_rows(self, rows: Sequence[PlannedRow]) -> None:
+        """What the step function does after it stored the rows' keys and values; for callers
+        that stand in for the step function."""
+        for r in rows:
+            self.cache.commit(r.seq.request.request_id, r.n)
+
     def complete(self, rows: Sequence[PlannedRow], sampled: Sequence[int],
                  logprobs: Sequence[float] | None = None) -> list[Sequence_]:
-        """The step ran: ``sampled`` holds one token for every row with ``samples`` set, in
-        order.  Returns the sequences that finished."""
+        """The step ran (and committed its tokens to the cache): ``sampled`` holds one token
+        for every row with ``samples`` set, in order.  Returns the sequences that finished."""
         done: list[Sequence_] = []
         k = 0
         st = self.stats
@@ -244,7 +250,6 @@ class Scheduler:
         st.peak_live = max(st.peak_live, len(self.running))
         for r in rows:
             rid = r.seq.request.request_id
-            self.cache.commit(rid, r.n)
             if r.n == 1 and r.start >= r.seq.n_prompt:
                 st.decode_tokens += 1
             else:

@@ -1,0 +1,130 @@
+"""Generation through the Python entry point on the GPU: greedy against the plain
+implementation, long decoding, the first tokens of a sequence, sampling, a pool so small that
+requests are set back."""
+
+import pytest
+import torch
+
+from configs import CONFIGS, PAGE_SIZE
+from plain import llama_plain as P
+
+pytestmark = pytest.mark.gpu
+
+
+def prompts_for(vocab, lengths, seed=5):
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randint(0, vocab, (n,), generator=g).tolist() for n in lengths]
+
+
+def plain_weights(model_dir, dtype):
+    cfg, w = P.read_model_dir(model_dir)
+    if dtype == "bfloat16":
+        w = {k: v.to(torch.bfloat16).float() for k, v in w.items()}
+    return cfg, w
+
+
+def assert_greedy_consistent(cfg, w, prompt, generated, slack):
+    """Every generated token is the plain model's argmax given the tokens before it, up to
+    ``slack`` in the logit (0 would demand the exact argmax; rounding may swap near-ties)."""
+    logits = P.forward(cfg, w, prompt + generated)
+    for i, tok in enumerate(generated):
+        row = logits[len(prompt) + i - 1]
+        assert row[tok] >= row.max() - slack, (i, tok, int(row.argmax()), float(row.max() - row[tok]))
+
+
+@pytest.mark.parametrize("dtype, slack", [("float32", 2e-5), ("bfloat16", 6e-2)])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_greedy_generation_matches_plain(name, dtype, slack, model_dirs):
+    from scratch_llm_b200 import LLM, SamplingParams
+    cfg, w = plain_weights(model_dirs[name], dtype)
+    lengths = {"A": [5, 17, 33], "B": [1, 9, 40, 64, 100], "C": [15, 16, 17, 70]}[name]
+    n_new = {"A": 16, "B": 24, "C": 20}[name]
+    prompts = prompts_for(cfg["vocab_size"], lengths)
+    llm = LLM(model_dirs[name], dtype=dtype, max_tokens=1024, page_size=PAGE_SIZE[name],
+              max_batch_tokens=48, chunk_size=32)
+    got = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=n_new))
+    assert [len(g) for g in got] == [n_new] * len(prompts)
+    for p, g in zip(prompts, got):
+        assert_greedy_consistent(cfg, w, p, g, slack)
+    if dtype == "float32":
+        assert got[0] == P.greedy(cfg, w, prompts[0], n_new)
+    # one prompt alone gives what it gave in the batch
+    alone = llm.generate(prompts[1], SamplingParams(temperature=0.0, max_tokens=n_new))
+    if dtype == "float32":
+        assert alone == got[1]
+    else:
+        assert_greedy_consistent(cfg, w, prompts[1], alone, slack)
+
+
+def test_long_decoding(model_dirs):
+    from scratch_llm_b200 import LLM, SamplingParams
+    cfg, w = plain_weights(model_dirs["C"], "float32")
+    prompt = prompts_for(331, [21])[0]
+    llm = LLM(model_dirs["C"], dtype="float32", max_tokens=640, page_size=16)
+    got = llm.generate(prompt, SamplingParams(temperature=0.0, max_tokens=600))
+    assert len(got) == 600
+    assert_greedy_consistent(cfg, w, prompt, got, 2e-5)
+
+
+@pytest.mark.parametrize("dtype, tol", [("float32", dict(rtol=2e-5, atol=5e-6)),
+                                        ("bfloat16", dict(rtol=3e-2, atol=3e-2))])
+def test_first_tokens_of_a_sequence(dtype, tol, model_dirs):
+    from scratch_llm_b200.engine import ModelRunner, RowInput, load_model
+    cfg, w = plain_weights(model_dirs["B"], dtype)
+    runner = ModelRunner(load_model(model_dirs["B"], dtype, verbose=False), 8, 16, 4)
+    toks = [7, 300, 12]
+    want = P.forward(cfg, w, toks)
+    with torch.no_grad():
+        runner.admit("x")
+        first = runner.step([RowInput("x", toks[:1], [0])])
+        second = runner.step([RowInput("x", toks[1:2], [0])])
+        third = runner.step([RowInput("x", toks[2:], [0])])
+    for got, pos in ((first, 0), (second, 1), (third, 2)):
+        torch.testing.assert_close(got[0].cpu(), want[pos], **tol)
+
+
+def test_small_pool_sets_requests_back_and_results_do_not_change(model_dirs):
+    from scratch_llm_b200 import LLM, SamplingParams
+    prompts = prompts_for(256, [30, 25, 28, 9, 33, 20])
+    params = SamplingParams(temperature=0.0, max_tokens=40)
+    big = LLM(model_dirs["A"], dtype="float32", max_tokens=2048, page_size=16)
+    want = big.generate(prompts, params)
+    small = LLM(model_dirs["A"], dtype="float32", max_tokens=160, page_size=16, max_requests=4)
+    res = small.serve([__import__("scratch_llm_b200").Request(i, p, params)
+                       for i, p in enumerate(prompts)])
+    assert res.stats.preemptions > 0
+    assert [list(c.token_ids) for c in res.completed] == want
+    small.runner.cache.check()
+    assert not small.runner.cache.requests
+
+
+def test_sampling_through_the_entry_point(model_dirs):
+    from scratch_llm_b200 import LLM, SamplingParams
+    llm = LLM(model_dirs["A"], dtype="float32", max_tokens=1024, page_size=16)
+    prompts = prompts_for(256, [12, 7, 19])
+    sp = [SamplingParams(temperature=0.9, top_p=0.95, max_tokens=12, seed=s) for s in (1, 2, 3)]
+    batch = llm.generate(prompts, sp)
+    # a request's draws depend on its own seed and count, not on the batch
+    assert llm.generate(prompts[1], sp[1]) == batch[1]
+    assert llm.generate(prompts[1], SamplingParams(temperature=0.9, top_p=0.95, max_tokens=12,
+                                                   seed=99)) != batch[1]
+    # stop ids end the generation and are kept
+    greedy = llm.generate(prompts[0], SamplingParams(temperature=0.0, max_tokens=12))
+    cut = llm.generate(prompts[0], SamplingParams(temperature=0.0, max_tokens=12,
+                                                  stop_ids=(greedy[4],)))
+    assert cut == greedy[:greedy.index(greedy[4]) + 1]
+    # log-probabilities are those of the plain model
+    cfg, w = plain_weights(model_dirs["A"], "float32")
+    toks, lps = llm.generate_with_logprobs(prompts[2], SamplingParams(temperature=0.0, max_tokens=5))
+    logits = P.forward(cfg, w, prompts[2] + toks)
+    want = [float(torch.log_softmax(logits[len(prompts[2]) + i - 1], -1)[t])
+            for i, t in enumerate(toks)]
+    torch.testing.assert_close(torch.tensor(lps), torch.tensor(want), rtol=1e-4, atol=1e-5)
+    with pytest.raises(ValueError, match="non-empty"):
+        llm.generate([[]], SamplingParams(max_tokens=2))
+
+
+def test_no_cpu_path():
+    from scratch_llm_b200.kernels import ops
+    with pytest.raises(ops.KernelError, match="no CPU path"):
+        ops.embed(torch.zeros(2, dtype=torch.int32), torch.zeros(4, 8), torch.zeros(2, 8))

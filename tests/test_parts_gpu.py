@@ -1,0 +1,235 @@
+"""Each part alone against its plain formula, and a model put together in the test from a toy
+mixer with state of its own, without a change to the framework's files."""
+
+import math
+from dataclasses import dataclass
+
+import pytest
+import torch
+
+from plain import llama_plain as P
+
+pytestmark = pytest.mark.gpu
+TOL = {torch.float32: dict(rtol=2e-5, atol=2e-6), torch.bfloat16: dict(rtol=3e-2, atol=2e-2)}
+
+
+def rand(*shape, seed=0, scale=1.0):
+    return torch.randn(*shape, generator=torch.Generator().manual_seed(seed)) * scale
+
+
+def ctx(dtype):
+    from scratch_llm_b200.parts import BuildContext
+    return BuildContext(dtype=dtype, device=torch.device("cuda"))
+
+
+@pytest.fixture(scope="module", autouse=True)
+def compiled():
+    from scratch_llm_b200.kernels import ops
+    ops.prepare([16, 48], verbose=False)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_norm_part(dtype):
+    from scratch_llm_b200.parts import NORMS, make
+    from scratch_llm_b200.config.spec import PartSpec
+    norm = make(NORMS, "norm", PartSpec("rmsnorm", {"size": 100, "eps": 1e-3}))
+    assert set(norm.param_specs()) == {"weight"}
+    w = rand(100, seed=1) + 1
+    norm.load({"weight": w}, ctx(dtype))
+    resid, delta = rand(6, 100, seed=2), rand(6, 100, seed=3).to(dtype)
+    r = resid.cuda()
+    out = norm.forward(r, delta.cuda())
+    assert out.dtype == dtype
+    torch.testing.assert_close(out.cpu().float(), P.rmsnorm(resid + delta.float(), w, 1e-3), **TOL[dtype])
+    torch.testing.assert_close(r.cpu(), resid + delta.float(), rtol=0, atol=0)
+
+
+def test_rotary_part_tables():
+    from scratch_llm_b200.parts.position import Rotary
+    rot = Rotary(head_dim=48, theta=50000.0, max_position=500, interleaved=True)
+    rot.load({}, ctx(torch.float32))
+    cos, sin = P.rope_tables(48, 500, 50000.0)
+    assert torch.equal(rot.cos.cpu(), cos) and torch.equal(rot.sin.cpu(), sin)
+    assert rot.cos.dtype == torch.float32
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_feed_forward_part(dtype):
+    from scratch_llm_b200.parts.feed_forward import SwiGLU
+    ff = SwiGLU(hidden_size=72, intermediate_size=200)
+    t = {"gate_proj.weight": rand(200, 72, seed=1, scale=0.1), "up_proj.weight": rand(200, 72, seed=2, scale=0.1),
+         "down_proj.weight": rand(72, 200, seed=3, scale=0.1)}
+    assert {k: v.shape for k, v in ff.param_specs().items()} == {k: tuple(v.shape) for k, v in t.items()}
+    ff.load(t, ctx(dtype))
+    x = rand(11, 72, seed=4).to(dtype)
+    tw = {k: v.to(dtype).float() for k, v in t.items()}
+    want = P.swiglu(x.float(), tw["gate_proj.weight"], tw["up_proj.weight"], tw["down_proj.weight"])
+    torch.testing.assert_close(ff.forward(x.cuda()).cpu().float(), want, **TOL[dtype])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window", [None, 9])
+def test_attention_part_in_portions(dtype, window):
+    """The attention mixer alone, fed a sequence in three steps through a cache of its own."""
+    from scratch_llm_b200.cache import CacheManager
+    from scratch_llm_b200.engine.batch import BatchStager, RowInput, build_batch
+    from scratch_llm_b200.parts import CacheView
+    from scratch_llm_b200.parts.attention import GQAttention
+    from scratch_llm_b200.parts.position import Rotary
+    d, H, G, hd, S = 80, 6, 2, 16, 45
+    att = GQAttention(d, H, G, hd, scale=0.2, window=window)
+    t = {"q_proj.weight": rand(H * hd, d, seed=1, scale=0.2), "k_proj.weight": rand(G * hd, d, seed=2, scale=0.2),
+         "v_proj.weight": rand(G * hd, d, seed=3, scale=0.2), "o_proj.weight": rand(d, H * hd, seed=4, scale=0.2)}
+    att.load(t, ctx(dtype))
+    rot = Rotary(hd, 1000.0, 64)
+    rot.load({}, ctx(dtype))
+    cache = CacheManager([att.kv_spec()], [None], page_size=4, n_pages=16, max_requests=2,
+                         dtype=dtype, device="cuda")
+    stager = BatchStager(torch.device("cuda"))
+    x = rand(S, d, seed=5).to(dtype)
+    cache.admit("r")
+    outs = []
+    for a, b in ((0, 20), (20, 22), (22, 45)):
+        assert cache.reserve("r", b - a)
+        batch = build_batch(cache, stager, [RowInput("r", [0] * (b - a))], 10, 64)
+        pages, g = cache.entry_pages(0)
+        view = CacheView(pages=pages, block_table=batch.block_tables[g], page_size=4)
+        outs.append(att.forward(x[a:b].cuda(), batch, view, True, rot).cpu().float())
+        cache.commit("r", b - a)
+    got = torch.cat(outs)
+    tw = {f"p.{k}": v.to(dtype).float() for k, v in t.items()}
+    cfgd = dict(num_attention_heads=H, num_key_value_heads=G, head_dim=hd, hidden_size=d,
+                sliding_window=window)
+    cos, sin = P.rope_tables(hd, 64, 1000.0)
+    # the plain layer divides by sqrt(hd); this part was given scale 0.2 = 0.8 / sqrt(16)
+    want, _ = P.attention_layer(x.float(), torch.arange(S), {**tw, "p.q_proj.weight": tw["p.q_proj.weight"] * 0.8},
+                                "p", cfgd, cos, sin)
+    torch.testing.assert_close(got, want, **TOL[dtype])
+    if window is not None:
+        assert any(p < 0 for p in cache.table_of("r", 0))  # pages behind the window went back
+
+
+# ----------------------------------------------------------------- a toy mixer with state
+
+def make_toy():
+    """A mixer whose output at token t is W applied to the running mean of the inputs up to t.
+    Its state per request is (sum of inputs, count): fixed size, carried from step to step in
+    the cache manager's state slots."""
+    from scratch_llm_b200.config import LlamaConfig, register_architecture, ARCHITECTURES
+    from scratch_llm_b200.config.spec import LayerSpec, ModelSpec, PartSpec, Run
+    from scratch_llm_b200.parts import MIXERS, Mixer, StateSpec, register_mixer
+    from scratch_llm_b200.weights import ParamSpec
+
+    if "running_mean" not in MIXERS:
+        @register_mixer("running_mean")
+        class RunningMean(Mixer):
+            def __init__(self, hidden_size):
+                self.d = hidden_size
+
+            def state_spec(self):
+                return StateSpec((self.d + 1,), torch.float32)
+
+            def param_specs(self):
+                return {"mix.weight": ParamSpec((self.d, self.d))}
+
+            def load(self, tensors, ctx):
+                self.w = tensors["mix.weight"].to(ctx.device, torch.float32)
+                self.dtype = ctx.dtype
+
+            def forward(self, x, batch, cache, write, position):
+                out = torch.empty_like(x)
+                t = 0
+                for n, slot in zip(batch.host_row_new, batch.row_slot.tolist()):
+                    st = cache.state[slot]
+                    sums = st[:self.d] + torch.cumsum(x[t:t + n].float(), 0)
+                    counts = st[self.d] + torch.arange(1, n + 1, device=x.device)
+                    out[t:t + n] = ((sums / counts[:, None]) @ self.w.T).to(x.dtype)
+                    st[:self.d] = sums[-1]
+                    st[self.d] = counts[-1]
+                    t += n
+                return out
+
+    if "ToyStateForCausalLM" not in ARCHITECTURES:
+        @dataclass(frozen=True)
+        class ToyConfig:
+            width: int
+            n_vocab: int
+            inner: int
+            architecture = "ToyStateForCausalLM"
+
+            @classmethod
+            def from_dict(cls, raw):
+                return cls(raw["width"], raw["n_vocab"], raw["inner"])
+
+            def to_dict(self):
+                return {"architectures": [self.architecture], "width": self.width,
+                        "n_vocab": self.n_vocab, "inner": self.inner}
+
+            def model_spec(self):
+                d = self.width
+                norm = PartSpec("rmsnorm", {"size": d, "eps": 1e-5})
+                ff = PartSpec("swiglu", {"hidden_size": d, "intermediate_size": self.inner})
+                att = PartSpec("gqa_attention", {"hidden_size": d, "n_heads": 2, "n_kv_heads": 1,
+                                                 "head_dim": 16, "scale": 0.25, "window": None})
+                rot = PartSpec("rotary", {"head_dim": 16, "theta": 100.0, "max_position": 128})
+                names = {"mixer": "mixer", "feed_forward": "ff", "mixer_norm": "n1",
+                         "feed_forward_norm": "n2"}
+                layers = (
+                    LayerSpec("l0", "pre_norm", att, ff, norm, norm, rot, names),
+                    LayerSpec("l1", "pre_norm", PartSpec("running_mean", {"hidden_size": d}), ff,
+                              norm, norm, PartSpec("none"), names))
+                # layer 0 runs twice: once with a cache of its own, once more reading it
+                order = (Run(0, 0), Run(1, 1), Run(0, 0, write=False))
+                return ModelSpec(d, self.n_vocab, 128, layers, order, norm, "emb.weight", "out_norm",
+                                 "head.weight", tie_embeddings=True)
+
+        register_architecture("ToyStateForCausalLM", ToyConfig)
+    return ARCHITECTURES["ToyStateForCausalLM"].config_cls
+
+
+def toy_plain(cfg, w, ids):
+    d = cfg.width
+    x = w["emb.weight"][torch.tensor(ids)]
+    pos = torch.arange(len(ids))
+    cos, sin = P.rope_tables(16, 128, 100.0)
+    acfg = dict(num_attention_heads=2, num_key_value_heads=1, head_dim=16, hidden_size=d)
+
+    def ffn(x, p):
+        h = P.rmsnorm(x, w[f"{p}.n2.weight"], 1e-5)
+        return x + P.swiglu(h, w[f"{p}.ff.gate_proj.weight"], w[f"{p}.ff.up_proj.weight"],
+                            w[f"{p}.ff.down_proj.weight"])
+
+    def attn(x, kv):
+        a, kv = P.attention_layer(P.rmsnorm(x, w["l0.n1.weight"], 1e-5), pos, w, "l0.mixer", acfg,
+                                  cos, sin, kv)
+        return ffn(x + a, "l0"), kv
+    x, kv = attn(x, None)
+    h = P.rmsnorm(x, w["l1.n1.weight"], 1e-5)
+    mean = torch.cumsum(h, 0) / torch.arange(1, len(ids) + 1)[:, None]
+    x = ffn(x + mean @ w["l1.mixer.mix.weight"].T, "l1")
+    x, _ = attn(x, kv)
+    return P.rmsnorm(x, w["out_norm.weight"], 1e-5) @ w["emb.weight"].T
+
+
+def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
+    import trace_util as T
+    from scratch_llm_b200.engine import ModelRunner, load_model
+    from scratch_llm_b200.weights import write_random_model
+    Toy = make_toy()
+    cfg = Toy(width=48, n_vocab=90, inner=100)
+    d = write_random_model(cfg, tmp_path / "toy", seed=4, std=0.1, dtype="float32")
+    _, w = P.read_model_dir(d)
+    # the attention scale of the toy is 0.25 = 1/sqrt(16), the plain layer's own
+    model = load_model(d, "float32", verbose=False)
+    kv, st = model.cache_specs()
+    assert kv[0] is not None and kv[1] is None and st[1] is not None and st[0] is None
+    reqs = T.make_requests(90, [37, 5, 64, 20, 9], seed=2)
+    want = {rid: toy_plain(cfg, w, toks) for rid, toks in reqs.items()}
+    for way in (T.whole, T.changing_portions, T.mixed):
+        steps = way(reqs)
+        runner = ModelRunner(model, 8, -(-T.peak_tokens(steps) // 8), 4)
+        with torch.no_grad():
+            got = T.run_in_process(runner, steps)
+        for (rid, pos), row in got.items():
+            torch.testing.assert_close(row, want[rid][pos], rtol=1e-4, atol=1e-5,
+                                       msg=lambda m: f"{way.__name__} {rid} {pos}: {m}")

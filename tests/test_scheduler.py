@@ -1,0 +1,197 @@
+"""The scheduler's decisions, without a GPU: a stand-in step function whose next token is a
+function of the sequence so far."""
+
+import random
+import zlib
+
+import pytest
+
+from scratch_llm_b200.cache import CacheManager
+from scratch_llm_b200.engine.scheduler import Request, Scheduler
+from scratch_llm_b200.parts import KVSpec
+from scratch_llm_b200.sampling import SamplingParams
+
+VOCAB = 97
+
+
+def next_token(tokens):
+    return zlib.crc32(repr(list(tokens)).encode()) % VOCAB
+
+
+def oracle(prompt, params, max_position=10_000):
+    toks, out = list(prompt), []
+    while True:
+        t = next_token(toks)
+        toks.append(t)
+        out.append(t)
+        if t in params.stop_ids or len(out) >= params.max_tokens or len(toks) >= max_position:
+            return out
+
+
+def make(n_pages, page_size=4, max_requests=4, max_position=256, **kw):
+    cache = CacheManager([KVSpec(1, 16, None)], [None], page_size, n_pages, max_requests)
+    return Scheduler(cache, max_position, vocab_size=VOCAB, **kw), cache
+
+
+def run(sched, cache, log=None, limit=10_000):
+    for _ in range(limit):
+        if not sched.has_work:
+            break
+        rows = sched.plan()
+        assert rows, "a step with nothing in it"
+        assert sum(r.n for r in rows) <= sched.max_batch_tokens
+        assert len({id(r.seq) for r in rows}) == len(rows)
+        for r in rows:
+            assert r.start == cache.requests[r.seq.request.request_id].n_tokens
+            assert 1 <= r.n <= len(r.seq.tokens) - r.start
+            assert r.samples == (r.start + r.n == len(r.seq.tokens))
+        sched.commit_rows(rows)
+        sampled = [next_token(r.seq.tokens) for r in rows if r.samples]
+        if log is not None:
+            log.append([(r.seq.request.request_id, r.start, r.n, r.samples) for r in rows])
+        sched.complete(rows, sampled)
+        cache.check()
+    else:
+        raise AssertionError("the scheduler did not finish")
+    assert not cache.requests
+    assert cache.free_pages() == [g.pool.n_pages for g in cache.groups]
+
+
+def greedy(n):
+    return SamplingParams(temperature=0.0, max_tokens=n)
+
+
+def test_mixed_steps_budget_and_portions():
+    sched, cache = make(n_pages=200, max_batch_tokens=16, chunk_size=10)
+    reqs = [Request("a", list(range(5)), greedy(6)), Request("b", list(range(23)), greedy(3)),
+            Request("c", list(range(40, 52)), greedy(2))]
+    for r in reqs:
+        sched.submit(r)
+    log = []
+    run(sched, cache, log)
+    # step 0: a whole (5), b's first portion (10, the chunk cap), c gets the last 1 of the budget
+    assert log[0] == [("a", 0, 5, True), ("b", 0, 10, False), ("c", 0, 1, False)]
+    # step 1: a decodes beside portions of b and c: one batch
+    assert log[1][0] == ("a", 5, 1, True)
+    assert ("b", 10, 10, False) in log[1] and ("c", 1, 5, False) in log[1]
+    for r in reqs:
+        assert sched.finished[r.request_id].generated == oracle(r.prompt_ids, r.params)
+    assert sched.stats.preemptions == 0
+    assert sched.stats.prefill_tokens == 5 + 23 + 12
+    assert sched.stats.decode_tokens == (6 - 1) + (3 - 1) + (2 - 1)
+
+
+def test_first_come_first_served_and_slots():
+    sched, cache = make(n_pages=200, max_requests=2, max_batch_tokens=64)
+    for i in range(5):
+        sched.submit(Request(i, [i + 1] * 3, greedy(2 + i)))
+    log = []
+    run(sched, cache, log)
+    first_seen = {}
+    for s, rows in enumerate(log):
+        assert len(rows) <= 2
+        for rid, *_ in rows:
+            first_seen.setdefault(rid, s)
+    assert [first_seen[i] for i in range(5)] == sorted(first_seen[i] for i in range(5))
+    assert all(sched.finished[i].generated == oracle([i + 1] * 3, greedy(2 + i)) for i in range(5))
+
+
+def test_finish_reasons():
+    sched, cache = make(n_pages=200, max_position=12)
+    p_stop = SamplingParams(temperature=0.0, max_tokens=50, stop_ids=())
+    first = oracle([1, 2, 3], SamplingParams(temperature=0.0, max_tokens=4))
+    with_stop = SamplingParams(temperature=0.0, max_tokens=9, stop_ids=(first[2],))
+    sched.submit(Request("one", [1, 2, 3], greedy(1)))       # finishes with its first token
+    sched.submit(Request("stop", [1, 2, 3], with_stop))
+    sched.submit(Request("edge", [7] * 6, SamplingParams(temperature=0.0, max_tokens=6)))
+    run(sched, cache)
+    assert sched.finished["one"].generated == first[:1]
+    assert sched.finished["one"].finish_reason == "length"
+    stop_at = first.index(first[2])
+    assert sched.finished["stop"].generated == first[:stop_at + 1]  # the stop token is kept
+    assert sched.finished["stop"].finish_reason == "stop"
+    assert len(sched.finished["edge"].tokens) == 12
+    assert sched.finished["edge"].finish_reason in ("length", "max_position")
+    with pytest.raises(ValueError, match="exceeds max_position"):
+        sched.submit(Request("long", [1] * 6, p_stop))
+
+
+def test_submit_errors():
+    sched, _ = make(n_pages=4, page_size=4)
+    with pytest.raises(ValueError, match="non-empty"):
+        sched.submit(Request("e", [], greedy(1)))
+    with pytest.raises(ValueError, match="out of range"):
+        sched.submit(Request("v", [VOCAB], greedy(1)))
+    with pytest.raises(ValueError, match="could never finish"):
+        sched.submit(Request("big", [1] * 10, greedy(8)))   # 17 places > 16
+    sched.submit(Request("ok", [1] * 10, greedy(7)))
+    with pytest.raises(ValueError, match="already submitted"):
+        sched.submit(Request("ok", [1], greedy(1)))
+
+
+def test_pages_run_out_the_newest_request_is_set_back():
+    # 8 pages of 4: two requests of 8 + 9 tokens fit at first, not to their ends
+    sched, cache = make(n_pages=8, page_size=4, max_batch_tokens=64)
+    reqs = [Request("old", [3] * 8, greedy(12)), Request("new", [5] * 9, greedy(12))]
+    for r in reqs:
+        sched.submit(r)
+    log = []
+    run(sched, cache, log)
+    assert sched.stats.preemptions >= 1
+    assert sched.finished["old"].n_preempted == 0     # the older request is never the victim
+    assert sched.finished["new"].n_preempted >= 1
+    for r in reqs:
+        assert sched.finished[r.request_id].generated == oracle(r.prompt_ids, r.params)
+    # after it was set back, "new" came in again with its prompt and its generated tokens
+    again = [row for rows in log for row in rows if row[0] == "new" and row[1] == 0]
+    assert len(again) >= 2 and again[-1][2] > 9
+
+
+def test_reserve_full_never_sets_back_and_serialises():
+    sched, cache = make(n_pages=8, page_size=4, max_batch_tokens=64, admission="reserve_full")
+    reqs = [Request("a", [3] * 8, greedy(12)), Request("b", [5] * 9, greedy(12)),
+            Request("c", [6] * 2, greedy(3))]
+    for r in reqs:
+        sched.submit(r)
+    log = []
+    run(sched, cache, log)
+    assert sched.stats.preemptions == 0
+    live = [{rid for rid, *_ in rows} for rows in log]
+    assert not any({"a", "b"} <= s for s in live)       # 5 + 5 pages do not fit 8 together
+    assert not any("c" in s and "b" not in s for s in live[:-4])  # no skipping ahead of b
+    for r in reqs:
+        assert sched.finished[r.request_id].generated == oracle(r.prompt_ids, r.params)
+
+
+def test_prompt_portion_is_cut_to_the_pages_that_are_free():
+    sched, cache = make(n_pages=6, page_size=4, max_batch_tokens=64)
+    sched.submit(Request("a", [1] * 13, greedy(2)))   # 4 pages
+    sched.submit(Request("b", [2] * 15, greedy(2)))   # wants 4, 2 are free
+    log = []
+    run(sched, cache, log)
+    assert log[0] == [("a", 0, 13, True), ("b", 0, 8, False)]
+    for rid, p in (("a", [1] * 13), ("b", [2] * 15)):
+        assert sched.finished[rid].generated == oracle(p, greedy(2))
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_traffic_small_pool(seed):
+    rng = random.Random(seed)
+    sched, cache = make(n_pages=rng.choice([12, 20, 40]), page_size=rng.choice([2, 4, 8]),
+                        max_requests=rng.choice([2, 3, 5]),
+                        max_batch_tokens=rng.choice([8, 24, 100]),
+                        chunk_size=rng.choice([None, 3, 16]), max_position=80)
+    reqs = []
+    pool_tokens = cache.groups[0].pool.n_pages * cache.page_size
+    for i in range(14):
+        n_p, n_g = rng.randint(1, 30), rng.randint(1, 20)
+        if n_p + n_g - 1 > pool_tokens or n_p + n_g > 80:
+            continue
+        stop = (rng.randrange(VOCAB),) if rng.random() < 0.3 else ()
+        reqs.append(Request(i, [rng.randrange(VOCAB) for _ in range(n_p)],
+                            SamplingParams(temperature=0.0, max_tokens=n_g, stop_ids=stop)))
+        sched.submit(reqs[-1])
+    run(sched, cache)
+    for r in reqs:
+        assert sched.finished[r.request_id].generated == oracle(r.prompt_ids, r.params, 80)
+    assert sched.stats.steps == len(sched.stats.tokens_per_step)
