@@ -68,6 +68,7 @@ class BatchStager:
         self._events: list[torch.cuda.Event | None] = [None, None]
         self._dev = torch.empty(capacity_ints, dtype=torch.int32, device=device)
         self._turn = 0
+        self.bytes_uploaded = 0   # host-to-device bytes so far
 
     @staticmethod
     def _pinned(n: int) -> torch.Tensor:
@@ -101,6 +102,7 @@ class BatchStager:
             hnp[o:o + a.size] = a.reshape(-1)
         if total:
             self._dev[:total].copy_(host[:total], non_blocking=True)
+            self.bytes_uploaded += 4 * total
         ev = torch.cuda.Event()
         ev.record()
         self._events[turn] = ev

@@ -66,6 +66,7 @@ class LLM:
         self.sampler = Sampler(self.runner.device)
         self.max_batch_tokens, self.chunk_size, self.admission = (max_batch_tokens, chunk_size,
                                                                   admission)
+        self._sched: Scheduler | None = None
 
     def _scheduler(self) -> Scheduler:
         return Scheduler(self.runner.cache, self.runner.max_position, self.max_batch_tokens,
@@ -73,30 +74,62 @@ class LLM:
 
     # ------------------------------------------------------------------------------ serve
 
+    # ------------------------------------------------------------------- submit and step
+
+    def submit(self, request: Request) -> None:
+        """Queue a request; :meth:`step` runs it."""
+        if self._sched is None:
+            self._sched = self._scheduler()
+        self._sched.submit(request)
+
+    @property
+    def has_work(self) -> bool:
+        return self._sched is not None and self._sched.has_work
+
     @torch.no_grad()
+    def step(self, want_logprobs: bool = False) -> dict[Hashable, int]:
+        """One scheduler step: plan a batch, run it, choose the next tokens.  Returns the token
+        each request produced in this step ({request id: token}, on the host)."""
+        sched = self._sched
+        rows = sched.plan()
+        inputs = [RowInput(r.seq.request.request_id, r.seq.tokens[r.start:r.start + r.n],
+                           [r.n - 1] if r.samples else []) for r in rows]
+        logits = self.runner.step(inputs)
+        sampling = [r.seq for r in rows if r.samples]
+        tokens, lps = [], None
+        if sampling:
+            tokens, lps = self.sampler.sample(
+                logits, [s.request.params for s in sampling],
+                [_seed_of(s.request) for s in sampling],
+                [len(s.generated) for s in sampling], want_logprobs)
+        sched.complete(rows, tokens, lps)
+        return {s.request.request_id: t for s, t in zip(sampling, tokens)}
+
+    def abort_all(self) -> None:
+        """Drop every queued and live request and give back what they hold."""
+        if self._sched is not None:
+            for seq in list(self._sched.running):
+                self.runner.cache.release(seq.request.request_id)
+        self._sched = None
+
+    # ------------------------------------------------------------------------------ serve
+
     def serve(self, requests: Sequence[Request], want_logprobs: bool = False) -> ServeResult:
         """Run ``requests`` to completion under continuous batching."""
-        sched = self._scheduler()
-        for r in requests:
-            sched.submit(r)
+        if self.has_work:
+            raise RuntimeError("serve() needs an idle engine: requests from submit() are live")
+        self._sched = None
         start = time.perf_counter()
         try:
-            while sched.has_work:
-                rows = sched.plan()
-                inputs = [RowInput(r.seq.request.request_id, r.seq.tokens[r.start:r.start + r.n],
-                                   [r.n - 1] if r.samples else []) for r in rows]
-                logits = self.runner.step(inputs)
-                sampling = [r.seq for r in rows if r.samples]
-                tokens, lps = [], None
-                if sampling:
-                    tokens, lps = self.sampler.sample(
-                        logits, [s.request.params for s in sampling],
-                        [_seed_of(s.request) for s in sampling],
-                        [len(s.generated) for s in sampling], want_logprobs)
-                sched.complete(rows, tokens, lps)
-        finally:
-            for seq in list(sched.running):   # an error leaves nothing held
-                self.runner.cache.release(seq.request.request_id)
+            for r in requests:
+                self.submit(r)
+            while self.has_work:
+                self.step(want_logprobs)
+            sched = self._sched
+        except BaseException:
+            self.abort_all()   # an error leaves nothing held
+            raise
+        self._sched = None
         wall = time.perf_counter() - start
         done = []
         for r in requests:

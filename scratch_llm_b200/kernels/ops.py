@@ -68,7 +68,13 @@ def prepare(head_dims: Sequence[int] = (), verbose: bool = True) -> None:
         _load(n, s, d)
 
 
+#: kernels of this package launched so far in this process (one per successful op call)
+launch_count = 0
+
+
 def _check(code: int, what: str) -> None:
+    global launch_count
+    launch_count += 1
     if code != 0:
         raise KernelError(f"{what} failed with CUDA error {code} "
                           f"({'invalid value: a size this kernel does not take' if code == 1 else 'see cudaError_t'})")

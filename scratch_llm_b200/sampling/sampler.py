@@ -21,6 +21,7 @@ from .params import SamplingParams
 class Sampler:
     def __init__(self, device: torch.device) -> None:
         self.device = device
+        self.bytes_read = 0   # device-to-host bytes so far
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams],
                seeds: Sequence[int], counters: Sequence[int], want_logprobs: bool = False
@@ -40,4 +41,5 @@ class Sampler:
             idv = torch.from_numpy(i).to(self.device, non_blocking=True)
             ops.sample(logits, out, fd[0], fd[1], idv[0], idv[1], logprob_out=lp)
         tokens = out.tolist()  # the one device-to-host read of a step
+        self.bytes_read += 4 * n * (2 if lp is not None else 1)
         return tokens, (lp.tolist() if lp is not None else None)
