@@ -1,0 +1,446 @@
+// Causal attention of a packed batch over the paged cache on the tensor cores (bfloat16
+// operands, 32-bit accumulation and softmax): the serving path's attention for prefill
+// portions and for decode.
+//
+// Restates src/scratch_llm/model.py:172-182 and :330-345 of the reference (scores scaled,
+// disallowed keys -inf, softmax in 32-bit, probabilities rounded to the model dtype before
+// they multiply v; query head h reads kv head h / (H/G)) as a tiled online-softmax kernel in
+// the manner of its flash-attention oracle (src/scratch_llm/kernels/attention/reference.py:26-85).
+// Like the reference's CUDA decode kernel (csrc/attention/a_r3_paged_decode_sm90.cu:32-39) a
+// CTA serves one kv head and ALL query heads of its group, so keys and values are read once
+// per group; unlike it, the products run on mma.sync tensor-core instructions, the head size
+// and group size are free, and long rows are split over CTAs and merged by log-sum-exp
+// (its merge: a_r3_paged_decode_sm90.cu:350-398).
+//
+// Work decomposition.  The queries of a row r and kv head g are "packed": packed index
+// p = token * GS + j stands for the row's token `token` and query head g*GS + j (GS = H/G).
+// A CTA takes BQ consecutive packed queries and walks the keys in tiles of 64 that are
+// aligned to absolute positions.
+//   wide  (SPLIT = false): BQ = 64; each of 4 warps owns 16 packed queries and all 64 keys
+//                          of a tile.  For rows with many new tokens.
+//   split (SPLIT = true):  BQ = 16; the 4 warps share the 16 packed queries and each takes
+//                          16 keys of a tile; the key range is also split over `n_splits`
+//                          CTAs whose partial results a merge kernel combines.  For decode.
+// Compiled once per head size: -DSLLM_HEAD_DIM=<multiple of 16, at most 256>.
+#include "common.cuh"
+
+#ifndef SLLM_HEAD_DIM
+#error "compile with -DSLLM_HEAD_DIM=<head size>"
+#endif
+
+namespace sllm {
+
+constexpr int HD = SLLM_HEAD_DIM;
+static_assert(HD % 16 == 0 && HD >= 16 && HD <= 256, "head size: a multiple of 16 up to 256");
+constexpr int LDS = HD + 8;  // shared-memory row stride in elements: rows 16 bytes apart in banks
+constexpr int BKV = 64, NWARP = 4, THREADS = 128;
+constexpr int KSTEPS = HD / 16;  // k-steps of q k^T
+constexpr int DTILES = HD / 8;   // 8-wide column tiles of the output
+constexpr int CHUNKS = HD / 8;   // 16-byte chunks per row
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    const int bytes = valid ? 16 : 0;  // 0: the 16 bytes are filled with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* smem) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], const void* smem) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+// d (16x8, f32) += a (16x16, bf16, row) * b (16x8, bf16, col)
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0,
+                                         uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+        "{%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ float quad_max(float v) {
+    v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
+    return fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 2));
+}
+__device__ __forceinline__ float quad_sum(float v) {
+    v += __shfl_xor_sync(0xffffffffu, v, 1);
+    return v + __shfl_xor_sync(0xffffffffu, v, 2);
+}
+
+template <bool SPLIT> struct Mode {
+    static constexpr int BQ = SPLIT ? 16 : 64;
+    static constexpr int WKEYS = SPLIT ? BKV / NWARP : BKV;  // keys of a tile one warp takes
+    static constexpr int NT = WKEYS / 8;                     // 8-wide score tiles per warp
+    static constexpr int PK = WKEYS / 16;                    // k-steps of p v per warp
+};
+
+template <bool SPLIT> constexpr size_t smem_bytes() {
+    return ((size_t)Mode<SPLIT>::BQ + 4 * BKV) * LDS * sizeof(bf16);
+}
+
+struct AttnArgs {
+    const bf16* q; int64_t q_stride;
+    const bf16* pages; const int* block_table; int table_stride; int page_size;
+    const int* row_start; const int* row_pos0; const int* row_list;
+    bf16* out; int64_t out_stride;
+    float* part_o; float* part_lse; int n_splits;
+    int H; int G; float scale_log2; int window;
+};
+
+template <bool SPLIT>
+__global__ void __launch_bounds__(THREADS) attn_mma_kernel(const AttnArgs a) {
+    using M = Mode<SPLIT>;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* Qs = reinterpret_cast<bf16*>(smem_raw);
+    bf16* Ks = Qs + M::BQ * LDS;       // 2 stages of [BKV][LDS]
+    bf16* Vs = Ks + 2 * BKV * LDS;     // 2 stages of [BKV][LDS]
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n_splits = SPLIT ? a.n_splits : 1;
+    const int q_tile = blockIdx.x / n_splits, split = blockIdx.x % n_splits;
+    const int r = a.row_list ? a.row_list[blockIdx.y] : blockIdx.y;
+    const int g = blockIdx.z;
+    const int GS = a.H / a.G;
+    const int t0 = a.row_start[r];
+    const int n_new = a.row_start[r + 1] - t0;
+    const int pos0 = a.row_pos0[r];
+    const int n_packed = n_new * GS;
+    const int q0 = q_tile * M::BQ;
+    if (q0 >= n_packed) return;
+    const int first_pos = pos0 + q0 / GS;
+    const int last_pos = pos0 + min(n_packed - 1, q0 + M::BQ - 1) / GS;
+    int k_lo = 0;
+    if (a.window > 0) k_lo = max(0, first_pos - a.window + 1) / BKV * BKV;
+    const int n_tiles = (last_pos - k_lo) / BKV + 1;
+    const int per_split = (n_tiles + n_splits - 1) / n_splits;
+    const int tile_begin = split * per_split;
+    const int tile_end = min(n_tiles, tile_begin + per_split);
+
+    // ---- queries into shared memory
+    for (int idx = tid; idx < M::BQ * CHUNKS; idx += THREADS) {
+        const int i = idx / CHUNKS, c = idx - i * CHUNKS;
+        const int p = q0 + i;
+        const bool valid = p < n_packed;
+        const int tok = valid ? p / GS : 0, j = valid ? p - tok * GS : 0;
+        const bf16* src = a.q + (int64_t)(t0 + tok) * a.q_stride + (int64_t)(g * GS + j) * HD + c * 8;
+        cp_async16(Qs + i * LDS + c * 8, src, valid);
+    }
+    cp_async_commit();
+
+    const int64_t v_off = (int64_t)a.G * a.page_size * HD;
+    auto load_tile = [&](int tile, int stage) {
+        const int kt = k_lo + tile * BKV;
+        bf16* ks = Ks + stage * BKV * LDS;
+        bf16* vs = Vs + stage * BKV * LDS;
+        for (int idx = tid; idx < BKV * CHUNKS; idx += THREADS) {
+            const int j = idx / CHUNKS, c = idx - j * CHUNKS;
+            const int kpos = kt + j;
+            bool valid = kpos <= last_pos;
+            const bf16* src = a.pages;
+            if (valid) {
+                const int page = a.block_table[(int64_t)r * a.table_stride + kpos / a.page_size];
+                valid = page >= 0;
+                if (valid)
+                    src = a.pages + (((int64_t)page * 2 * a.G + g) * a.page_size +
+                                     kpos % a.page_size) * HD + c * 8;
+            }
+            cp_async16(ks + j * LDS + c * 8, src, valid);
+            cp_async16(vs + j * LDS + c * 8, valid ? src + v_off : src, valid);
+        }
+    };
+
+    if (tile_begin < tile_end) load_tile(tile_begin, 0);
+    cp_async_commit();
+    cp_async_wait<1>();  // the queries have landed (the first key tile may still be in flight)
+    __syncthreads();
+
+    // ---- this warp's query fragments
+    const int wq = SPLIT ? 0 : warp * 16;  // first packed query of the warp within the CTA
+    uint32_t qf[KSTEPS][4];
+#pragma unroll
+    for (int ks = 0; ks < KSTEPS; ++ks)
+        ldsm_x4(qf[ks], Qs + (wq + (lane & 15)) * LDS + ks * 16 + (lane >> 4) * 8);
+
+    const int key_lo_w = SPLIT ? warp * M::WKEYS : 0;  // first key of a tile this warp takes
+    // the two query rows of this thread: wq + lane/4 and wq + lane/4 + 8
+    int qpos[2];
+    bool qvalid[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int p = q0 + wq + (lane >> 2) + 8 * h;
+        qvalid[h] = p < n_packed;
+        qpos[h] = pos0 + (qvalid[h] ? p / GS : 0);
+    }
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    float o[DTILES][4];
+#pragma unroll
+    for (int dn = 0; dn < DTILES; ++dn)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[dn][e] = 0.f;
+
+    for (int tile = tile_begin; tile < tile_end; ++tile) {
+        const int stage = (tile - tile_begin) & 1;
+        if (tile + 1 < tile_end) load_tile(tile + 1, stage ^ 1);
+        cp_async_commit();
+        cp_async_wait<1>();  // everything but the group just committed has landed
+        __syncthreads();
+        const bf16* ks_s = Ks + stage * BKV * LDS + key_lo_w * LDS;
+        const bf16* vs_s = Vs + stage * BKV * LDS + key_lo_w * LDS;
+        const int kt = k_lo + tile * BKV + key_lo_w;  // absolute position of the warp's key 0
+
+        // ---- scores s = q k^T
+        float s[M::NT][4];
+#pragma unroll
+        for (int nt = 0; nt < M::NT; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) s[nt][e] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks) {
+#pragma unroll
+            for (int nt = 0; nt < M::NT; nt += 2) {
+                uint32_t b[4];
+                ldsm_x4(b, ks_s + (nt * 8 + (lane & 7) + (lane >> 4) * 8) * LDS + ks * 16 +
+                               ((lane >> 3) & 1) * 8);
+                mma_bf16(s[nt], qf[ks], b[0], b[1]);
+                mma_bf16(s[nt + 1], qf[ks], b[2], b[3]);
+            }
+        }
+        // ---- mask, online softmax (base 2, in 32-bit)
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int nt = 0; nt < M::NT; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int h = e >> 1;
+                const int kpos = kt + nt * 8 + (lane & 3) * 2 + (e & 1);
+                const bool ok = qvalid[h] && kpos <= qpos[h] &&
+                                (a.window <= 0 || kpos > qpos[h] - a.window);
+                s[nt][e] = ok ? s[nt][e] * a.scale_log2 : -INFINITY;
+                mx[h] = fmaxf(mx[h], s[nt][e]);
+            }
+        float corr[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const float m_new = fmaxf(m_run[h], quad_max(mx[h]));
+            corr[h] = m_new == -INFINITY ? 1.f : exp2f(m_run[h] - m_new);
+            m_run[h] = m_new;
+            l_run[h] *= corr[h];
+        }
+        uint32_t pa[M::PK][4];
+#pragma unroll
+        for (int nt = 0; nt < M::NT; ++nt) {
+            float p[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int h = e >> 1;
+                p[e] = m_run[h] == -INFINITY ? 0.f : exp2f(s[nt][e] - m_run[h]);
+                l_run[h] += p[e];
+            }
+            pa[nt >> 1][(nt & 1) * 2 + 0] = pack_bf16(p[0], p[1]);
+            pa[nt >> 1][(nt & 1) * 2 + 1] = pack_bf16(p[2], p[3]);
+        }
+#pragma unroll
+        for (int dn = 0; dn < DTILES; ++dn) {
+            o[dn][0] *= corr[0]; o[dn][1] *= corr[0];
+            o[dn][2] *= corr[1]; o[dn][3] *= corr[1];
+        }
+        // ---- o += p v
+#pragma unroll
+        for (int kk = 0; kk < M::PK; ++kk) {
+#pragma unroll
+            for (int dn = 0; dn < DTILES; dn += 2) {
+                uint32_t b[4];
+                ldsm_x4_trans(b, vs_s + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDS +
+                                     dn * 8 + (lane >> 4) * 8);
+                mma_bf16(o[dn], pa[kk], b[0], b[1]);
+                mma_bf16(o[dn + 1], pa[kk], b[2], b[3]);
+            }
+        }
+        __syncthreads();  // this stage is overwritten by the load issued two iterations on
+    }
+    cp_async_wait<0>();
+
+    l_run[0] = quad_sum(l_run[0]);
+    l_run[1] = quad_sum(l_run[1]);
+
+    if (!SPLIT) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int p = q0 + wq + (lane >> 2) + 8 * h;
+            if (p >= n_packed) continue;
+            const int tok = p / GS, j = p - tok * GS;
+            const float inv = l_run[h] > 0.f ? 1.0f / l_run[h] : 0.f;
+            bf16* dst = a.out + (int64_t)(t0 + tok) * a.out_stride + (int64_t)(g * GS + j) * HD +
+                        (lane & 3) * 2;
+#pragma unroll
+            for (int dn = 0; dn < DTILES; ++dn)
+                *reinterpret_cast<__nv_bfloat162*>(dst + dn * 8) =
+                    __floats2bfloat162_rn(o[dn][2 * h] * inv, o[dn][2 * h + 1] * inv);
+        }
+        return;
+    }
+
+    // ---- split mode: combine the four warps' partial results for the same 16 queries
+    __syncthreads();  // all warps are done with the key and value stages
+    float* sm_o = reinterpret_cast<float*>(Ks);           // [NWARP][16][HD]
+    float* sm_m = sm_o + NWARP * 16 * HD;                  // [NWARP][16]
+    float* sm_l = sm_m + NWARP * 16;                       // [NWARP][16]
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int i = (lane >> 2) + 8 * h;
+        if ((lane & 3) == 0) {
+            sm_m[warp * 16 + i] = m_run[h];
+            sm_l[warp * 16 + i] = l_run[h];
+        }
+#pragma unroll
+        for (int dn = 0; dn < DTILES; ++dn) {
+            float* dst = sm_o + ((warp * 16 + i) * HD) + dn * 8 + (lane & 3) * 2;
+            dst[0] = o[dn][2 * h];
+            dst[1] = o[dn][2 * h + 1];
+        }
+    }
+    __syncthreads();
+    for (int idx = tid; idx < 16 * HD; idx += THREADS) {
+        const int i = idx / HD, d = idx - i * HD;
+        const int p = q0 + i;
+        if (p >= n_packed) continue;
+        float mm = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < NWARP; ++w) mm = fmaxf(mm, sm_m[w * 16 + i]);
+        float num = 0.f, den = 0.f;
+        if (mm != -INFINITY) {
+#pragma unroll
+            for (int w = 0; w < NWARP; ++w) {
+                const float f = exp2f(sm_m[w * 16 + i] - mm);
+                num += f * sm_o[(w * 16 + i) * HD + d];
+                den += f * sm_l[w * 16 + i];
+            }
+        }
+        const float val = den > 0.f ? num / den : 0.f;
+        const int tok = p / GS, j = p - tok * GS;
+        const int64_t qh = (int64_t)(t0 + tok) * a.H + g * GS + j;  // (token, head) index
+        if (n_splits == 1) {
+            a.out[(int64_t)(t0 + tok) * a.out_stride + (int64_t)(g * GS + j) * HD + d] =
+                __float2bfloat16_rn(val);
+        } else {
+            a.part_o[(qh * n_splits + split) * HD + d] = val;
+            if (d == 0)
+                a.part_lse[qh * n_splits + split] = den > 0.f ? mm + log2f(den) : -INFINITY;
+        }
+    }
+}
+
+// Combines the partial results of the splits: o = sum_s 2^(lse_s - m) o_s / sum_s 2^(lse_s - m).
+// grid (listed rows, H); a block walks the row's tokens.
+__global__ void attn_merge_kernel(const float* __restrict__ part_o,
+                                  const float* __restrict__ part_lse, int n_splits,
+                                  const int* __restrict__ row_start,
+                                  const int* __restrict__ row_list, bf16* __restrict__ out,
+                                  int64_t out_stride, int H) {
+    const int r = row_list ? row_list[blockIdx.x] : blockIdx.x;
+    const int head = blockIdx.y;
+    for (int t = row_start[r]; t < row_start[r + 1]; ++t) {
+        const int64_t qh = (int64_t)t * H + head;
+        float mm = -INFINITY;
+        for (int s = 0; s < n_splits; ++s) mm = fmaxf(mm, part_lse[qh * n_splits + s]);
+        for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+            float num = 0.f, den = 0.f;
+            if (mm != -INFINITY) {
+                for (int s = 0; s < n_splits; ++s) {
+                    const float f = exp2f(part_lse[qh * n_splits + s] - mm);
+                    num += f * part_o[(qh * n_splits + s) * HD + d];
+                    den += f;
+                }
+            }
+            out[(int64_t)t * out_stride + (int64_t)head * HD + d] =
+                __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+        }
+    }
+}
+
+}  // namespace sllm
+
+using namespace sllm;
+
+SLLM_EXPORT int sllm_attn_mma_head_dim() { return HD; }
+
+// Scratch floats the split kernel needs for `n_tokens` tokens in its listed rows.
+SLLM_EXPORT int64_t sllm_attn_mma_scratch_floats(int64_t n_tokens, int H, int n_splits) {
+    return n_splits > 1 ? n_tokens * H * n_splits * (HD + 1) : 0;
+}
+
+// q / out: [n_tokens, stride] bfloat16 with head h at columns [h*HD, (h+1)*HD).
+// pages: [n_pages, 2, G, page_size, HD] bfloat16.  block_table: [rows, table_stride], -1 = none.
+// row_list: the n_list rows this launch serves (nullptr: rows 0..n_list-1).
+// split = 0: the wide kernel; max_new = the largest number of new tokens of a listed row.
+// split = 1: the split kernel with n_splits CTAs along the keys; for n_splits > 1,
+//            `scratch` holds sllm_attn_mma_scratch_floats(total tokens of the batch, H, n_splits)
+//            floats and a merge kernel writes the result.
+SLLM_EXPORT int sllm_attn_mma(const void* q, int64_t q_stride, const void* pages,
+                              const int* block_table, int table_stride, int page_size,
+                              const int* row_start, const int* row_pos0, const int* row_list,
+                              int n_list, int max_new, void* out, int64_t out_stride, int H, int G,
+                              float scale, int window, int split, int n_splits, float* scratch,
+                              int64_t n_tokens_total, cudaStream_t stream) {
+    if (n_list <= 0 || max_new <= 0) return 0;
+    if (H <= 0 || G <= 0 || H % G != 0 || page_size <= 0 || window < 0 || n_list > 65535 ||
+        G > 65535 || (q_stride % 8) != 0 || (out_stride % 2) != 0)
+        return (int)cudaErrorInvalidValue;
+    if (((uintptr_t)q & 15) || ((uintptr_t)pages & 15) || ((uintptr_t)out & 3))
+        return (int)cudaErrorInvalidValue;
+    AttnArgs a;
+    a.q = (const bf16*)q; a.q_stride = q_stride;
+    a.pages = (const bf16*)pages; a.block_table = block_table; a.table_stride = table_stride;
+    a.page_size = page_size; a.row_start = row_start; a.row_pos0 = row_pos0; a.row_list = row_list;
+    a.out = (bf16*)out; a.out_stride = out_stride;
+    a.part_o = nullptr; a.part_lse = nullptr; a.n_splits = 1;
+    a.H = H; a.G = G; a.scale_log2 = scale * 1.4426950408889634f; a.window = window;
+    const int GS = H / G;
+    cudaError_t e;
+    if (!split) {
+        const size_t smem = smem_bytes<false>();
+        e = cudaFuncSetAttribute(attn_mma_kernel<false>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        dim3 grid(((int64_t)max_new * GS + 63) / 64, n_list, G);
+        attn_mma_kernel<false><<<grid, THREADS, smem, stream>>>(a);
+        SLLM_LAUNCH_CHECK();
+        return 0;
+    }
+    if (n_splits < 1) return (int)cudaErrorInvalidValue;
+    if (n_splits > 1) {
+        if (!scratch) return (int)cudaErrorInvalidValue;
+        a.part_o = scratch;
+        a.part_lse = scratch + n_tokens_total * H * n_splits * HD;
+    }
+    a.n_splits = n_splits;
+    const size_t smem = smem_bytes<true>();
+    e = cudaFuncSetAttribute(attn_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    dim3 grid((((int64_t)max_new * GS + 15) / 16) * n_splits, n_list, G);
+    attn_mma_kernel<true><<<grid, THREADS, smem, stream>>>(a);
+    SLLM_LAUNCH_CHECK();
+    if (n_splits > 1) {
+        dim3 mgrid(n_list, H);
+        attn_merge_kernel<<<mgrid, HD >= 128 ? 128 : 32, 0, stream>>>(
+            a.part_o, a.part_lse, n_splits, row_start, row_list, (bf16*)out, out_stride, H);
+        SLLM_LAUNCH_CHECK();
+    }
+    return 0;
+}

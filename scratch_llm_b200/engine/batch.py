@@ -52,6 +52,14 @@ class StepBatch:
     row_slot: torch.Tensor
     logit_index: torch.Tensor
     block_tables: list[torch.Tensor] = field(default_factory=list)
+    # rows with exactly one new token (decode) and rows with several (prompt portions), as
+    # device lists, with what a part needs to plan its launches for them
+    single_rows: torch.Tensor | None = None
+    multi_rows: torch.Tensor | None = None
+    n_single: int = 0
+    n_multi: int = 0
+    max_new_multi: int = 0
+    max_context_single: int = 0
     # host copies, for parts that plan their launches from them
     host_row_new: list[int] = field(default_factory=list)
     host_row_pos0: list[int] = field(default_factory=list)
@@ -162,11 +170,17 @@ def build_batch(cache, stager: BatchStager, rows: Sequence[RowInput], vocab_size
             tab[i, :len(pages)] = pages
         tables.append(tab)
     li = np.asarray(logit_index, dtype=np.int32)
-    dev = stager.upload([token_ids, positions, token_row, row_start, row_pos0,
-                               row_slot, li, *tables])
+    single = [i for i, n in enumerate(lens) if n == 1]
+    multi = [i for i, n in enumerate(lens) if n > 1]
+    dev = stager.upload([token_ids, positions, token_row, row_start, row_pos0, row_slot, li,
+                         np.asarray(single, dtype=np.int32), np.asarray(multi, dtype=np.int32),
+                         *tables])
     return StepBatch(
         n_tokens=n_tokens, n_rows=n_rows, n_out=len(logit_index), max_new=max(lens),
         max_context=int(max(p + n for p, n in zip(row_pos0.tolist(), lens))),
         token_ids=dev[0], positions=dev[1], token_row=dev[2], row_start=dev[3],
-        row_pos0=dev[4], row_slot=dev[5], logit_index=dev[6], block_tables=dev[7:],
+        row_pos0=dev[4], row_slot=dev[5], logit_index=dev[6], single_rows=dev[7],
+        multi_rows=dev[8], block_tables=dev[9:], n_single=len(single), n_multi=len(multi),
+        max_new_multi=max((lens[i] for i in multi), default=0),
+        max_context_single=max((int(row_pos0[i]) + 1 for i in single), default=0),
         host_row_new=lens, host_row_pos0=row_pos0.tolist())

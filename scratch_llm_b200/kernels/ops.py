@@ -40,6 +40,14 @@ def attention_library(head_dim: int) -> tuple[str, tuple[str, ...], tuple[str, .
             (f"SLLM_HEAD_DIM={head_dim}",))
 
 
+def attention_mma_library(head_dim: int) -> tuple[str, tuple[str, ...], tuple[str, ...]]:
+    return (f"sllm_attention_mma_hd{head_dim}", ("attention_mma.cu",),
+            (f"SLLM_HEAD_DIM={head_dim}",))
+
+
+#: the tensor-core attention kernels take head sizes up to this; larger ones use the CUDA cores
+MMA_MAX_HEAD_DIM = 256
+
 _loaded: dict[str, ctypes.CDLL] = {}
 
 
@@ -63,6 +71,7 @@ def prepare(head_dims: Sequence[int] = (), verbose: bool = True) -> None:
     """Compile (in parallel) and load everything a model with these head sizes needs."""
     jobs = [(n, s, d) for n, (s, d) in CORE_LIBRARIES.items()]
     jobs += [attention_library(hd) for hd in sorted(set(head_dims))]
+    jobs += [attention_mma_library(hd) for hd in sorted(set(head_dims)) if hd <= MMA_MAX_HEAD_DIM]
     build.compile_many(jobs, verbose=verbose)
     for n, s, d in jobs:
         _load(n, s, d)
@@ -245,6 +254,56 @@ def attention_simt(q: torch.Tensor, pages: torch.Tensor, block_table: torch.Tens
         c_int(n_kv_heads), c_float(scale), c_int(window or 0), c_int(_code(q.dtype)),
         _stream()), "attention_simt")
     return out
+
+
+def attention_mma(q: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor,
+                  page_size: int, row_start: torch.Tensor, row_pos0: torch.Tensor,
+                  out: torch.Tensor, row_list: torch.Tensor | None, n_list: int, max_new: int,
+                  n_heads: int, n_kv_heads: int, head_dim: int, scale: float,
+                  window: int | None, split: bool, n_splits: int = 1,
+                  scratch: torch.Tensor | None = None) -> torch.Tensor:
+    """Causal attention of the listed rows over the paged cache on the tensor cores
+    (bfloat16).  ``split`` False: the wide kernel for rows with many new tokens; True: the
+    split kernel for decode rows, ``n_splits`` CTAs along the keys, partial results in
+    ``scratch`` (32-bit, :func:`attention_mma_scratch_floats` entries) when ``n_splits`` > 1."""
+    _need(q, torch.bfloat16, "q", contiguous=False)
+    _need(pages, torch.bfloat16, "pages")
+    _need(out, torch.bfloat16, "out", contiguous=False)
+    _need(block_table, torch.int32, "block_table", contiguous=False)
+    _need(row_start, torch.int32, "row_start")
+    _need(row_pos0, torch.int32, "row_pos0")
+    if row_list is not None:
+        _need(row_list, torch.int32, "row_list")
+    if q.stride(1) != 1 or out.stride(1) != 1 or q.shape[1] != n_heads * head_dim \
+            or out.shape != q.shape:
+        raise KernelError("attention q/out layout")
+    if pages.shape[1:] != (2, n_kv_heads, page_size, head_dim):
+        raise KernelError(f"pages must be [n_pages, 2, {n_kv_heads}, {page_size}, {head_dim}], "
+                          f"got {list(pages.shape)}")
+    if head_dim % 16 or not 16 <= head_dim <= MMA_MAX_HEAD_DIM:
+        raise KernelError(f"head size {head_dim}: the tensor-core attention kernels take "
+                          f"multiples of 16 up to {MMA_MAX_HEAD_DIM}")
+    n_tokens = q.shape[0]
+    if split and n_splits > 1:
+        need = attention_mma_scratch_floats(n_tokens, n_heads, head_dim, n_splits)
+        if scratch is None:
+            raise KernelError("the split kernel needs scratch memory for its partial results")
+        _need(scratch, torch.float32, "scratch")
+        if scratch.numel() < need:
+            raise KernelError(f"scratch holds {scratch.numel()} floats, {need} are needed")
+    lib = _load(*attention_mma_library(head_dim))
+    _check(lib.sllm_attn_mma(
+        _ptr(q), c_int64(q.stride(0)), _ptr(pages), _ptr(block_table),
+        c_int(block_table.stride(0)), c_int(page_size), _ptr(row_start), _ptr(row_pos0),
+        _ptr(row_list), c_int(n_list), c_int(max_new), _ptr(out), c_int64(out.stride(0)),
+        c_int(n_heads), c_int(n_kv_heads), c_float(scale), c_int(window or 0),
+        c_int(int(split)), c_int(n_splits), _ptr(scratch), c_int64(n_tokens), _stream()),
+        "attention_mma")
+    return out
+
+
+def attention_mma_scratch_floats(n_tokens: int, n_heads: int, head_dim: int, n_splits: int) -> int:
+    return n_tokens * n_heads * n_splits * (head_dim + 1) if n_splits > 1 else 0
 
 
 # --------------------------------------------------------------------------------- sampling

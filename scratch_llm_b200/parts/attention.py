@@ -70,7 +70,34 @@ class GQAttention(Mixer):
                           cache.block_table, cache.page_size, H, G, hd, interleaved, write)
         q = qkv[:, :H * hd]
         out = torch.empty((qkv.shape[0], H * hd), dtype=qkv.dtype, device=qkv.device)
-        ops.attention_simt(q, cache.pages, cache.block_table, cache.page_size, batch.row_start,
-                           batch.row_pos0, out, batch.n_rows, batch.max_new, H, G, hd,
-                           self.scale, self.window)
+        if qkv.dtype == torch.bfloat16 and hd <= ops.MMA_MAX_HEAD_DIM:
+            self._attend_tensor_cores(q, out, batch, cache)
+        else:
+            ops.attention_simt(q, cache.pages, cache.block_table, cache.page_size,
+                               batch.row_start, batch.row_pos0, out, batch.n_rows,
+                               batch.max_new, H, G, hd, self.scale, self.window)
         return self.o(out)
+
+    def _attend_tensor_cores(self, q, out, batch, cache: CacheView) -> None:
+        """Rows with several new tokens go to the wide kernel, rows with one to the split
+        kernel.  The number of splits along the keys is a fixed function of the batch's shape
+        (rows, groups, longest context): enough CTAs to fill the GPU's 148 SMs twice."""
+        H, G, hd = self.n_heads, self.n_kv_heads, self.head_dim
+        common = (q, cache.pages, cache.block_table, cache.page_size, batch.row_start,
+                  batch.row_pos0, out)
+        if batch.n_multi:
+            ops.attention_mma(*common, batch.multi_rows, batch.n_multi, batch.max_new_multi,
+                              H, G, hd, self.scale, self.window, split=False)
+        if batch.n_single:
+            ctas = batch.n_single * G * (-(-(H // G) // 16))
+            context = batch.max_context_single
+            if self.window is not None:
+                context = min(context, self.window + 63)
+            n_splits = max(1, min(-(-context // 64), 296 // ctas, 32))
+            scratch = None
+            if n_splits > 1:
+                scratch = torch.empty(ops.attention_mma_scratch_floats(q.shape[0], H, hd, n_splits),
+                                      dtype=torch.float32, device=q.device)
+            ops.attention_mma(*common, batch.single_rows, batch.n_single, 1, H, G, hd,
+                              self.scale, self.window, split=True, n_splits=n_splits,
+                              scratch=scratch)

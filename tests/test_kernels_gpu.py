@@ -110,49 +110,89 @@ def paged_cache(k, v, page_size, n_pages, seed, dtype):
     return pages, table
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("H, G, hd, page, window", [(4, 2, 16, 16, None), (6, 3, 48, 8, None),
-                                                    (8, 1, 128, 32, None), (5, 5, 80, 4, None),
-                                                    (4, 2, 16, 16, 37), (6, 2, 48, 8, 5)])
-def test_attention_over_pages(ops, dtype, H, G, hd, page, window):
-    # rows: (cached before this step, new tokens): a whole prompt, portions, single tokens
-    rows = [(0, 70), (33, 1), (64, 18), (100, 2), (0, 1), (255, 1), (17, 47)]
+ATTN_SHAPES = [(4, 2, 16, 16, None), (6, 3, 48, 8, None), (8, 1, 128, 32, None),
+               (5, 5, 80, 4, None), (4, 2, 16, 16, 37), (6, 2, 48, 8, 5), (40, 2, 16, 16, None)]
+# rows: (cached before this step, new tokens): a whole prompt, portions, single tokens
+ATTN_ROWS = [(0, 70), (33, 1), (64, 18), (100, 2), (0, 1), (255, 1), (17, 47), (63, 1), (64, 1)]
+FAR = 5  # the row with 255 cached keys
+
+
+def attention_case(dtype, H, G, hd, page):
     dt = DT[dtype]
+    rows = ATTN_ROWS
     ks = [rand(G, a + n, hd, seed=10 + i).to(dt).float() for i, (a, n) in enumerate(rows)]
     vs = [rand(G, a + n, hd, seed=50 + i).to(dt).float() for i, (a, n) in enumerate(rows)]
     qs = [rand(H, n, hd, seed=90 + i).to(dt).float() for i, (a, n) in enumerate(rows)]
-    # a far key among hundreds: in the row with 255 cached keys, key 3 of kv head 0 points
-    # along the query and is scaled so that its score stands out
-    far = 5
-    ks[far][0, 3] = qs[far][0, 0] / qs[far][0, 0].norm() * 12.0
-    ks[far] = ks[far].to(dt).float()
+    # a far key among hundreds: key 3 of kv head 0 points along the query of head 0 and is
+    # scaled so that its score stands out
+    ks[FAR][0, 3] = qs[FAR][0, 0] / qs[FAR][0, 0].norm() * 12.0
+    ks[FAR] = ks[FAR].to(dt).float()
     n_pages = sum(-(-(a + n) // page) for a, n in rows) + 3
     pages, table = paged_cache(ks, vs, page, n_pages, seed=7, dtype=dt)
-    scale = 1.0 / math.sqrt(hd)
+    # unused places of the pages hold NaN: nothing may read them into a result
     q_flat = torch.cat([q.transpose(0, 1).reshape(q.shape[1], H * hd) for q in qs]).to(dt)
-    # q lives inside a wider buffer, as in the fused qkv
-    wide = torch.zeros(q_flat.shape[0], H * hd + 64, dtype=dt)
+    wide = torch.zeros(q_flat.shape[0], H * hd + 64, dtype=dt)  # q inside a wider buffer
     wide[:, :H * hd] = q_flat
-    wide = wide.cuda()
-    row_start = torch.tensor([0] + list(torch.tensor([n for _, n in rows]).cumsum(0)), dtype=torch.int32)
+    row_start = torch.tensor([0] + list(torch.tensor([n for _, n in rows]).cumsum(0)),
+                             dtype=torch.int32)
     row_pos0 = torch.tensor([a for a, _ in rows], dtype=torch.int32)
-    out = torch.empty(q_flat.shape[0], H * hd, dtype=dt, device="cuda")
-    ops.attention_simt(wide[:, :H * hd], pages.cuda(), table.cuda(), page, row_start.cuda(),
-                       row_pos0.cuda(), out, len(rows), max(n for _, n in rows), H, G, hd, scale,
-                       window)
-    got = out.cpu().float()
-    t = 0
-    for i, (a, n) in enumerate(rows):
-        want = P.attention(qs[i], ks[i], vs[i], torch.arange(a, a + n), torch.arange(a + n),
-                           scale, window)
+    return dict(qs=qs, ks=ks, vs=vs, pages=pages.cuda(), table=table.cuda(), wide=wide.cuda(),
+                row_start=row_start.cuda(), row_pos0=row_pos0.cuda(), starts=row_start.tolist())
+
+
+def check_attention(case, got, rows_checked, dtype, H, hd, window):
+    scale = 1.0 / math.sqrt(hd)
+    for i in rows_checked:
+        a, n = ATTN_ROWS[i]
+        t = case["starts"][i]
+        want = P.attention(case["qs"][i], case["ks"][i], case["vs"][i], torch.arange(a, a + n),
+                           torch.arange(a + n), scale, window)
         want = want.transpose(0, 1).reshape(n, H * hd)
         torch.testing.assert_close(got[t:t + n], want, **TOL[dtype],
-                                   msg=lambda m: f"row {i} {rows[i]}: {m}")
-        t += n
-    if window is None:
+                                   msg=lambda m: f"row {i} {ATTN_ROWS[i]}: {m}")
+    if window is None and FAR in rows_checked:
         # the far key took nearly all the weight of head 0 in its row
-        t_far = int(row_start[far])
-        torch.testing.assert_close(got[t_far, :hd], vs[far][0, 3], rtol=0.05, atol=0.05)
+        torch.testing.assert_close(got[case["starts"][FAR], :hd], case["vs"][FAR][0, 3],
+                                   rtol=0.05, atol=0.05)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H, G, hd, page, window", ATTN_SHAPES)
+def test_attention_over_pages(ops, dtype, H, G, hd, page, window):
+    case = attention_case(dtype, H, G, hd, page)
+    out = torch.full((case["wide"].shape[0], H * hd), float("nan"), dtype=DT[dtype], device="cuda")
+    ops.attention_simt(case["wide"][:, :H * hd], case["pages"], case["table"], page,
+                       case["row_start"], case["row_pos0"], out, len(ATTN_ROWS),
+                       max(n for _, n in ATTN_ROWS), H, G, hd, 1.0 / math.sqrt(hd), window)
+    check_attention(case, out.cpu().float(), range(len(ATTN_ROWS)), dtype, H, hd, window)
+
+
+@pytest.mark.parametrize("n_splits", [1, 3, 8])
+@pytest.mark.parametrize("H, G, hd, page, window", ATTN_SHAPES)
+def test_attention_on_tensor_cores(ops, H, G, hd, page, window, n_splits):
+    """The wide kernel on the rows with several new tokens, the split kernel on the rows with
+    one; then each kernel on all rows (either takes any row)."""
+    case = attention_case("bfloat16", H, G, hd, page)
+    q = case["wide"][:, :H * hd]
+    n_tok = q.shape[0]
+    single = [i for i, (_, n) in enumerate(ATTN_ROWS) if n == 1]
+    multi = [i for i, (_, n) in enumerate(ATTN_ROWS) if n > 1]
+    every = list(range(len(ATTN_ROWS)))
+    scale = 1.0 / math.sqrt(hd)
+    scratch = torch.full((ops.attention_mma_scratch_floats(n_tok, H, hd, n_splits) + 1,),
+                         float("nan"), dtype=torch.float32, device="cuda")
+    base = (q, case["pages"], case["table"], page, case["row_start"], case["row_pos0"])
+    for wide_rows, split_rows in ((multi, single), (every, []), ([], every)):
+        out = torch.full((n_tok, H * hd), float("nan"), dtype=torch.bfloat16, device="cuda")
+        if wide_rows:
+            ops.attention_mma(*base, out, torch.tensor(wide_rows, dtype=torch.int32).cuda(),
+                              len(wide_rows), max(ATTN_ROWS[i][1] for i in wide_rows), H, G, hd,
+                              scale, window, split=False)
+        if split_rows:
+            ops.attention_mma(*base, out, torch.tensor(split_rows, dtype=torch.int32).cuda(),
+                              len(split_rows), max(ATTN_ROWS[i][1] for i in split_rows), H, G, hd,
+                              scale, window, split=True, n_splits=n_splits, scratch=scratch)
+        check_attention(case, out.cpu().float(), every, "bfloat16", H, hd, window)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
