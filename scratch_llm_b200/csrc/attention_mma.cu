@@ -444,3 +444,85 @@ SLLM_EXPORT int sllm_attn_mma(const void* q, int64_t q_stride, const void* pages
     }
     return 0;
 }
+
+// ------------------------------------------------------------------------------------------
+// The split kernel for callers that must not allocate: see attention_mma_noalloc.h.
+#include <stdio.h>
+
+#include "attention_mma_noalloc.h"
+
+// Scratch for the partial results.  In host code this name is only a handle for
+// cudaGetSymbolAddress: it is not a device address and must never be passed to a kernel.
+static __device__ __align__(256) float g_noalloc_scratch[SLLM_NOALLOC_SCRATCH_FLOATS];
+
+static float* g_noalloc_ptr[64];  // device address of the array, per device ordinal
+static char g_noalloc_error[256] = "";
+
+SLLM_EXPORT int64_t sllm_attn_mma_noalloc_capacity_floats(void) {
+    return SLLM_NOALLOC_SCRATCH_FLOATS;
+}
+
+SLLM_EXPORT const char* sllm_attn_mma_noalloc_error(void) { return g_noalloc_error; }
+
+SLLM_EXPORT int sllm_attn_mma_split_noalloc(const void* q, int64_t q_stride, const void* pages,
+                                            const int* block_table, int table_stride,
+                                            int page_size, const int* row_start,
+                                            const int* row_pos0, const int* row_list, int n_list,
+                                            int max_new, void* out, int64_t out_stride, int H,
+                                            int G, float scale, int window, int n_splits,
+                                            int64_t n_tokens_total, cudaStream_t stream) {
+    if (n_list <= 0 || max_new <= 0) return 0;
+    if (H <= 0 || G <= 0 || H % G != 0 || page_size <= 0 || window < 0 || n_list > 65535 ||
+        G > 65535 || (q_stride % 8) != 0 || (out_stride % 2) != 0 || n_splits < 1 ||
+        n_tokens_total < 0)
+        return (int)cudaErrorInvalidValue;
+    if (((uintptr_t)q & 15) || ((uintptr_t)pages & 15) || ((uintptr_t)out & 3))
+        return (int)cudaErrorInvalidValue;
+    const int64_t need = sllm_attn_mma_scratch_floats(n_tokens_total, H, n_splits);
+    if (need > (int64_t)SLLM_NOALLOC_SCRATCH_FLOATS) {
+        snprintf(g_noalloc_error, sizeof(g_noalloc_error),
+                 "sllm_attn_mma_split_noalloc: %lld tokens x %d heads x %d splits need %lld "
+                 "scratch floats, the built-in array holds %lld: use fewer splits or tokens, or "
+                 "sllm_attn_mma with scratch of your own",
+                 (long long)n_tokens_total, H, n_splits, (long long)need,
+                 (long long)SLLM_NOALLOC_SCRATCH_FLOATS);
+        return (int)cudaErrorInvalidValue;
+    }
+    // set-up, once per device, with that device current
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= 64) return (int)cudaErrorInvalidDevice;
+    if (g_noalloc_ptr[dev] == nullptr) {
+        float* ptr = nullptr;
+        e = cudaGetSymbolAddress((void**)&ptr, g_noalloc_scratch);
+        if (e != cudaSuccess) return (int)e;
+        g_noalloc_ptr[dev] = ptr;
+    }
+    float* scratch = g_noalloc_ptr[dev];
+
+    AttnArgs a;
+    a.q = (const bf16*)q; a.q_stride = q_stride;
+    a.pages = (const bf16*)pages; a.block_table = block_table; a.table_stride = table_stride;
+    a.page_size = page_size; a.row_start = row_start; a.row_pos0 = row_pos0; a.row_list = row_list;
+    a.out = (bf16*)out; a.out_stride = out_stride;
+    a.part_o = n_splits > 1 ? scratch : nullptr;
+    a.part_lse = n_splits > 1 ? scratch + n_tokens_total * H * n_splits * HD : nullptr;
+    a.n_splits = n_splits;
+    a.H = H; a.G = G; a.scale_log2 = scale * 1.4426950408889634f; a.window = window;
+    const int GS = H / G;
+    const size_t smem = smem_bytes<true>();
+    e = cudaFuncSetAttribute(attn_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    dim3 grid((((int64_t)max_new * GS + 15) / 16) * n_splits, n_list, G);
+    attn_mma_kernel<true><<<grid, THREADS, smem, stream>>>(a);
+    SLLM_LAUNCH_CHECK();
+    if (n_splits > 1) {
+        dim3 mgrid(n_list, H);
+        attn_merge_kernel<<<mgrid, HD >= 128 ? 128 : 32, 0, stream>>>(
+            a.part_o, a.part_lse, n_splits, row_start, row_list, (bf16*)out, out_stride, H);
+        SLLM_LAUNCH_CHECK();
+    }
+    return 0;
+}
