@@ -187,14 +187,14 @@ def time_decode_device(llm, cfg, batch: int, context: int, steps: int, warmup: i
     for k in range(warmup):
         one(k)
     torch.cuda.synchronize()
-    before = ops.launch_count
+    before = ops.launch_count + runner.replayed_kernels
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for k in range(warmup, warmup + steps):
         one(k)
     e1.record()
     torch.cuda.synchronize()
-    launches = ops.launch_count - before
+    launches = ops.launch_count + runner.replayed_kernels - before
     for rid in ids:
         runner.release(rid)
     return e0.elapsed_time(e1) / steps, launches

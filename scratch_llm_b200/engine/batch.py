@@ -82,6 +82,11 @@ class BatchStager:
     def _pinned(n: int) -> torch.Tensor:
         return torch.empty(n, dtype=torch.int32, pin_memory=True)
 
+    def reserve(self, n: int) -> None:
+        """Make room for ``n`` ints now, so that later uploads keep their device addresses."""
+        if n > self._dev.numel():
+            self._grow(n)
+
     def _grow(self, n: int) -> None:
         cap = self._dev.numel()
         while cap < n:
@@ -118,9 +123,10 @@ class BatchStager:
 
 
 def build_batch(cache, stager: BatchStager, rows: Sequence[RowInput], vocab_size: int,
-                max_position: int) -> StepBatch:
+                max_position: int, table_width: int | None = None) -> StepBatch:
     """Check the rows against the cache manager's view of their requests, pack the descriptor
-    and copy it to the device."""
+    and copy it to the device.  ``table_width`` fixes the width of the block tables (for a
+    step that replays a captured CUDA graph, every array must keep its size and address)."""
     n_rows = len(rows)
     lens = [len(r.tokens) for r in rows]
     n_tokens = sum(lens)
@@ -164,6 +170,11 @@ def build_batch(cache, stager: BatchStager, rows: Sequence[RowInput], vocab_size
     tables = []
     for g in range(len(cache.groups)):
         width = max(len(cache.table_of(r.request_id, g)) for r in rows)
+        if table_width is not None:
+            if width > table_width:
+                raise ValueError(f"a block table of {width} pages exceeds the fixed width "
+                                 f"{table_width}")
+            width = table_width
         tab = np.full((n_rows, max(width, 1)), -1, dtype=np.int32)
         for i, r in enumerate(rows):
             pages = cache.table_of(r.request_id, g)

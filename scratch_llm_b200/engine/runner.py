@@ -37,9 +37,24 @@ def require_cuda() -> torch.device:
     return torch.device("cuda", torch.cuda.current_device())
 
 
+class _CapturedStep:
+    """A decode step of a fixed number of rows, captured as a CUDA graph."""
+
+    def __init__(self, graph: torch.cuda.CUDAGraph, logits: torch.Tensor, pointers: tuple) -> None:
+        self.graph, self.logits, self.pointers = graph, logits, pointers
+        self.n_kernels = 0
+
+
 class ModelRunner:
-    def __init__(self, model: DecoderModel, page_size: int, n_pages: int, max_requests: int
-                 ) -> None:
+    """``cuda_graphs``: steps in which every row brings one token and wants its logits (decode)
+    are captured once per number of rows and replayed afterwards, in the manner of the
+    reference's CudaGraphDecoder (src/scratch_llm/serving/cudagraph.py:31-96) and its
+    per-batch-size buckets (src/scratch_llm/serving/graph_buckets.py:94-200): the descriptor
+    arrays, the block tables (at their full width) and the pools keep their addresses, the
+    kernels read contexts and pages on the device."""
+
+    def __init__(self, model: DecoderModel, page_size: int, n_pages: int, max_requests: int,
+                 cuda_graphs: bool = True) -> None:
         if model.ctx is None:
             raise ValueError("load the model's weights before building a runner")
         self.model = model
@@ -50,6 +65,16 @@ class ModelRunner:
         self._stager = BatchStager(self.device)
         self.vocab_size = model.spec.vocab_size
         self.max_position = model.spec.max_position
+        self.cuda_graphs = cuda_graphs and all(
+            getattr(part, "capturable", True) for block in model.blocks
+            for part in (block.mixer, block.feed_forward))
+        self._table_width = self.cache.max_pages_per_request(self.max_position)
+        self._captured: dict[int, _CapturedStep] = {}
+        self.replayed_kernels = 0   # kernels of this package launched through graph replays
+        self._seen_sizes: set[int] = set()
+        # room for the widest decode step, so that captured addresses stay valid
+        self._stager.reserve(8 * (max_requests + 4) + 4 * max(1, len(self.cache.groups)) +
+                             max_requests * (self._table_width + 4) * max(1, len(self.cache.groups)))
 
     # ----------------------------------------------------------------------- requests
 
@@ -79,11 +104,47 @@ class ModelRunner:
             if not self.cache.reserve(row.request_id, len(row.tokens)):
                 raise OutOfPages(f"no free pages for {len(row.tokens)} more tokens of request "
                                  f"{row.request_id!r} (free per group: {self.cache.free_pages()})")
-        batch = self.build_batch(rows)
-        logits = self.model.forward(batch, self.cache)
+        if self.cuda_graphs and all(len(r.tokens) == 1 and len(r.want) == 1 for r in rows):
+            logits = self._decode_step(rows)
+        else:
+            logits = self.model.forward(self.build_batch(rows), self.cache)
         for row in rows:
             self.cache.commit(row.request_id, len(row.tokens))
         return logits
+
+    def _decode_step(self, rows: Sequence[RowInput]) -> torch.Tensor:
+        """Replay (or, at a size's second use, capture) the decode step for len(rows) rows."""
+        n = len(rows)
+        batch = build_batch(self.cache, self._stager, rows, self.vocab_size, self.max_position,
+                            table_width=self._table_width)
+        pointers = (batch.token_ids.data_ptr(), batch.logit_index.data_ptr(),
+                    tuple(t.data_ptr() for t in batch.block_tables))
+        cap = self._captured.get(n)
+        if cap is not None and cap.pointers == pointers:
+            cap.graph.replay()
+            self.replayed_kernels += cap.n_kernels
+            return cap.logits.clone()   # the graph's own output is overwritten by the next replay
+        if n not in self._seen_sizes:   # first use of this size: run it plainly (warms up)
+            self._seen_sizes.add(n)
+            return self.model.forward(batch, self.cache)
+        graph = torch.cuda.CUDAGraph()
+        before = ops.launch_count
+        try:
+            with torch.cuda.graph(graph):
+                logits = self.model.forward(batch, self.cache)
+        except RuntimeError:
+            # a part that reads device values on the host while it runs cannot be captured:
+            # from here on this runner launches every step plainly
+            self.cuda_graphs = False
+            self._captured.clear()
+            torch.cuda.synchronize()
+            return self.model.forward(batch, self.cache)
+        cap = _CapturedStep(graph, logits, pointers)
+        cap.n_kernels = ops.launch_count - before
+        self._captured[n] = cap
+        graph.replay()
+        self.replayed_kernels += cap.n_kernels
+        return logits.clone()
 
 
 def load_model(model_dir: str | Path, dtype: str | torch.dtype = "bfloat16",

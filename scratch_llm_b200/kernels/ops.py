@@ -32,6 +32,7 @@ CORE_LIBRARIES: dict[str, tuple[tuple[str, ...], tuple[str, ...]]] = {
     "sllm_rope_cache": (("rope_cache.cu",), ()),
     "sllm_gemm_simt": (("gemm_simt.cu",), ()),
     "sllm_sampling": (("sampling.cu",), ()),
+    "sllm_gemv_mma": (("gemv_mma.cu",), ()),
 }
 
 
@@ -185,6 +186,34 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tens
         _ptr(x), _ptr(w), _ptr(out), c_int(m), c_int(n), c_int(k), c_int64(x.stride(0)),
         c_int64(w.stride(0)), c_int64(out.stride(0)), c_int(_code(x.dtype)),
         c_int(_code(out.dtype)), _stream()), "gemm_simt")
+    return out
+
+
+#: the streaming small-batch product takes up to this many tokens
+GEMV_MAX_TOKENS = 64
+
+
+def gemv_mma(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool = False
+             ) -> torch.Tensor:
+    """out[M, N] = x[M, K] @ w[N, K]^T for M <= 64 tokens (bfloat16 operands, tensor cores,
+    32-bit accumulation), streaming w once.  ``swiglu``: w = [gate rows; up rows] and
+    out[M, N/2] = silu(x gate^T) * (x up^T).  ``out`` is bfloat16 or float32."""
+    _need(x, torch.bfloat16, "x", contiguous=False)
+    _need(w, torch.bfloat16, "w", contiguous=False)
+    _need(out, None, "out", contiguous=False)
+    (m, k), (n, k2) = x.shape, w.shape
+    n_out = n // 2 if swiglu else n
+    if k != k2 or out.shape != (m, n_out) or x.stride(1) != 1 or w.stride(1) != 1 \
+            or out.stride(1) != 1:
+        raise KernelError(f"gemv shapes/strides: x {list(x.shape)}, w {list(w.shape)}, "
+                          f"out {list(out.shape)}")
+    if m > GEMV_MAX_TOKENS or k % 8 or x.stride(0) % 8 or w.stride(0) % 8:
+        raise KernelError(f"gemv_mma takes up to {GEMV_MAX_TOKENS} tokens and rows that are "
+                          f"multiples of 8 elements; got M={m}, K={k}")
+    _check(_core("sllm_gemv_mma").sllm_gemv_mma(
+        _ptr(x), _ptr(w), _ptr(out), c_int(m), c_int(n), c_int(k), c_int64(x.stride(0)),
+        c_int64(w.stride(0)), c_int64(out.stride(0)), c_int(int(swiglu)),
+        c_int(_code(out.dtype)), _stream()), "gemv_mma")
     return out
 
 

@@ -81,7 +81,7 @@ class GQAttention(Mixer):
     def _attend_tensor_cores(self, q, out, batch, cache: CacheView) -> None:
         """Rows with several new tokens go to the wide kernel, rows with one to the split
         kernel.  The number of splits along the keys is a fixed function of the batch's shape
-        (rows, groups, longest context): enough CTAs to fill the GPU's 148 SMs twice."""
+        (rows and groups): enough CTAs to fill the GPU's 148 SMs twice."""
         H, G, hd = self.n_heads, self.n_kv_heads, self.head_dim
         common = (q, cache.pages, cache.block_table, cache.page_size, batch.row_start,
                   batch.row_pos0, out)
@@ -89,11 +89,11 @@ class GQAttention(Mixer):
             ops.attention_mma(*common, batch.multi_rows, batch.n_multi, batch.max_new_multi,
                               H, G, hd, self.scale, self.window, split=False)
         if batch.n_single:
+            # a function of the batch's shape alone (not of the contexts, which the kernel
+            # reads on the device and divides evenly over the splits), so that a captured
+            # decode step can be replayed as the contexts grow
             ctas = batch.n_single * G * (-(-(H // G) // 16))
-            context = batch.max_context_single
-            if self.window is not None:
-                context = min(context, self.window + 63)
-            n_splits = max(1, min(-(-context // 64), 296 // ctas, 32))
+            n_splits = max(1, min(296 // ctas, 32))
             scratch = None
             if n_splits > 1:
                 scratch = torch.empty(ops.attention_mma_scratch_floats(q.shape[0], H, hd, n_splits),

@@ -74,6 +74,10 @@ class CacheView:
 
 
 class Part:
+    #: False if ``forward`` reads device values on the host (``.item()``, ``.tolist()``) or
+    #: otherwise cannot be recorded into a CUDA graph; decode steps are then launched plainly
+    capturable = True
+
     def param_specs(self) -> dict[str, ParamSpec]:
         return {}
 

@@ -9,7 +9,6 @@ from typing import Mapping
 
 import torch
 
-from ..kernels import ops
 from ..weights.loader import ParamSpec
 from .base import BuildContext, FeedForward
 from .linear import Linear
@@ -38,6 +37,4 @@ class SwiGLU(FeedForward):
         self.down = Linear(put(tensors[self.names["down"]]).contiguous())
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        gu = self.gate_up(x)
-        act = torch.empty((x.shape[0], self.intermediate_size), dtype=x.dtype, device=x.device)
-        return self.down(ops.swiglu(gu, act))
+        return self.down(self.gate_up.swiglu(x))

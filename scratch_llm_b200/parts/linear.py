@@ -14,6 +14,10 @@ import torch
 from ..kernels import ops
 
 
+#: up to this many tokens the streaming small-batch kernel runs instead of the library product
+SMALL_BATCH = 8
+
+
 class Linear:
     def __init__(self, weight: torch.Tensor) -> None:
         if weight.dim() != 2 or not weight.is_contiguous():
@@ -30,6 +34,20 @@ class Linear:
             out = torch.empty((x.shape[0], self.out_features), dtype=torch.float32,
                               device=x.device)
             return ops.gemm_simt(x, w, out)
+        if x.shape[0] <= SMALL_BATCH and self.in_features % 8 == 0 and x.stride(0) % 8 == 0:
+            out = torch.empty((x.shape[0], self.out_features), dtype=out_dtype, device=x.device)
+            return ops.gemv_mma(x, w, out)
         if out_dtype == torch.float32:
             return torch.mm(x, w.t(), out_dtype=torch.float32)
         return torch.mm(x, w.t())
+
+    def swiglu(self, x: torch.Tensor) -> torch.Tensor:
+        """For a weight [gate rows; up rows]: silu(x gate^T) * (x up^T), fused where a kernel
+        takes the shape."""
+        w = self.weight
+        half = self.out_features // 2
+        out = torch.empty((x.shape[0], half), dtype=x.dtype, device=x.device)
+        if (w.dtype == torch.bfloat16 and x.shape[0] <= SMALL_BATCH and self.in_features % 8 == 0
+                and x.stride(0) % 8 == 0):
+            return ops.gemv_mma(x, w, out, swiglu=True)
+        return ops.swiglu(self(x), out)

@@ -92,6 +92,33 @@ def test_gemm_simt_bfloat16_inputs(ops):
     torch.testing.assert_close(out.cpu(), x.float() @ w.float().T, rtol=1e-5, atol=1e-5)
 
 
+@pytest.mark.parametrize("m, n, k", [(1, 16, 64), (3, 100, 200), (8, 4096 + 8, 4096), (9, 130, 264),
+                                     (16, 512, 14336), (17, 96, 1000), (33, 260, 520),
+                                     (64, 1024, 4096), (5, 7, 8)])
+def test_gemv_streams_weights_once(ops, m, n, k):
+    x = rand(m, k, dtype=torch.bfloat16, seed=1)
+    w = rand(n, k, dtype=torch.bfloat16, seed=2, scale=0.05)
+    want = x.float() @ w.float().T
+    for dt in (torch.float32, torch.bfloat16):
+        out = torch.full((m, n), float("nan"), dtype=dt, device="cuda")
+        ops.gemv_mma(x.cuda(), w.cuda(), out)
+        tol = dict(rtol=2e-3, atol=2e-3) if dt == torch.float32 else TOL["bfloat16"]
+        torch.testing.assert_close(out.cpu().float(), want, **tol)
+    # a token's result does not depend on its neighbours, nor on how many there are: bitwise
+    full = torch.empty(m, n, dtype=torch.float32, device="cuda")
+    ops.gemv_mma(x.cuda(), w.cuda(), full)
+    one = torch.empty(1, n, dtype=torch.float32, device="cuda")
+    ops.gemv_mma(x[m - 1:].cuda(), w.cuda(), one)
+    assert torch.equal(one.cpu()[0], full.cpu()[m - 1])
+    if n % 2 == 0:
+        half = n // 2
+        out = torch.full((m, half), float("nan"), dtype=torch.bfloat16, device="cuda")
+        ops.gemv_mma(x.cuda(), w.cuda(), out, swiglu=True)
+        gate, up = want[:, :half].to(torch.bfloat16).float(), want[:, half:].to(torch.bfloat16).float()
+        torch.testing.assert_close(out.cpu().float(), gate * torch.sigmoid(gate) * up,
+                                   **TOL["bfloat16"])
+
+
 def paged_cache(k, v, page_size, n_pages, seed, dtype):
     """Scatter k, v [G, T, hd] of several rows into shuffled pages.  Returns pages, tables."""
     g = torch.Generator().manual_seed(seed)
