@@ -1,0 +1,348 @@
+// Y[M, N] = X[M, K] * W[N, K]^T in bfloat16 on the 5th-generation tensor cores of sm_100a:
+// TMA (cp.async.bulk.tensor) stages 128-byte-swizzled tiles in shared memory, one thread
+// issues tcgen05.mma (cta_group::1, kind::f16, M = 128, N = 256, K = 16) with the accumulator
+// in tensor memory, and four warps drain it with tcgen05.ld.  With SWIGLU the 256 accumulator
+// columns are 128 gate and the matching 128 up features, and the epilogue writes
+// silu(gate) * up (src/scratch_llm/model.py:236-237 of the reference): the activation costs no
+// pass over memory.
+//
+// The reference's own tcgen05 kernel (csrc/gemm/tcgen05_sm100.cu:222-291) is a single-stage
+// skeleton whose instruction descriptor is a placeholder (:123-127) and whose tiles ignore the
+// block index (:264-265); this kernel is written from the PTX ISA's descriptor formats instead:
+//   instruction descriptor: D = f32 (bits 4-5 = 1), A = B = bf16 (bits 7-9 = 10-12 = 1), both
+//     K-major (bits 15, 16 = 0), N >> 3 in bits 17-22, M >> 4 in bits 24-28;
+//   shared-memory descriptor: start >> 4 (bits 0-13), leading byte offset 1 (16-29, unused by
+//     swizzled K-major layouts), stride byte offset 1024 >> 4 between 8-row groups (32-45),
+//     version 1 (46-47), layout SWIZZLE_128B = 2 (61-63); a K step of 16 elements advances
+//     the start address by 32 bytes inside the 128-byte swizzle atom.
+//
+// Roles in a CTA of 192 threads: warp 0 = TMA producer, warp 1 = MMA issuer and owner of the
+// tensor-memory allocation, warps 2-5 = epilogue (warp w reads the lanes 32*(w%4)..+31 it may
+// access).  One output tile of 128 x 256 per CTA, 4 pipeline stages of 48 KB.
+//
+// Every mbarrier wait is bounded: after WAIT_LIMIT polls a thread records an error code in
+// `g_gemm_error`, stops waiting, and the CTA still reaches its end, where the tensor memory is
+// freed.  No cluster launch, no multicast, no peer memory.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace sllm {
+
+typedef __nv_bfloat16 bf16;
+constexpr int TM = 128, TN = 256, TK = 64, STAGES = 4;
+constexpr int A_BYTES = TM * TK * 2, B_BYTES = TN * TK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int TC_THREADS = 192;
+constexpr uint32_t WAIT_LIMIT = 1u << 24;
+constexpr size_t TC_SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+
+__device__ int g_gemm_error = 0;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)),
+                 "r"(bytes) : "memory");
+}
+// Bounded wait for the phase with the given parity.  false = gave up (error recorded).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int code) {
+    const uint32_t addr = smem_u32(bar);
+    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n.reg .pred p;\n"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+            "selp.u32 %0, 1, 0, p;\n}\n"
+            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+        if (i > 1024) __nanosleep(64);
+    }
+    atomicCAS(&g_gemm_error, 0, code);
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar,
+                                            int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4}], [%2];\n"
+        ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
+    return (uint64_t)((smem_addr >> 4) & 0x3FFF) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           (1ull << 46) | (2ull << 61);
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+                                          uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n}\n"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u),
+          "r"(0u), "r"(0u) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n"
+                 ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
+          "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
+          "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() {
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+}
+
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Grid (tiles along N, tiles along M).  SWIGLU: W = [gate rows; up rows] (n_half each); tile
+// column block j covers features j*128..+127 and Y has n_half columns.
+template <bool SWIGLU>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+               bf16* __restrict__ Y, int M, int N, int K, int64_t ldy, int n_half) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>(
+        ((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    unsigned char* a_stage = smem;                          // STAGES x 16 KB
+    unsigned char* b_stage = smem + STAGES * A_BYTES;       // STAGES x 32 KB
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+    uint64_t* empty = full + STAGES;
+    uint64_t* acc_ready = empty + STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_ready + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.y * TM;
+    const int n_blk = blockIdx.x;
+    // rows of W this tile multiplies: two boxes of 128 rows
+    const int w_row0 = SWIGLU ? n_blk * 128 : n_blk * TN;
+    const int w_row1 = SWIGLU ? n_half + n_blk * 128 : n_blk * TN + 128;
+    const int k_blocks = (K + TK - 1) / TK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        mbar_init(acc_ready, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
+                     ::"r"(smem_u32(tmem_slot)), "r"(256u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int kb = 0; kb < k_blocks; ++kb) {
+                const int s = kb % STAGES;
+                if (!mbar_wait(&empty[s], ((kb / STAGES) & 1) ^ 1, 1)) break;
+                mbar_expect_tx(&full[s], STAGE_BYTES);
+                tma_load_2d(a_stage + s * A_BYTES, &map_x, &full[s], kb * TK, m0);
+                tma_load_2d(b_stage + s * B_BYTES, &map_w, &full[s], kb * TK, w_row0);
+                tma_load_2d(b_stage + s * B_BYTES + B_BYTES / 2, &map_w, &full[s], kb * TK, w_row1);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TN >> 3) << 17) |
+                                   ((uint32_t)(TM >> 4) << 24);
+            bool ok = true;
+            for (int kb = 0; kb < k_blocks && ok; ++kb) {
+                const int s = kb % STAGES;
+                ok = mbar_wait(&full[s], (kb / STAGES) & 1, 2);
+                if (!ok) break;
+                tc_fence_after();
+                const uint64_t da = make_smem_desc(smem_u32(a_stage + s * A_BYTES));
+                const uint64_t db = make_smem_desc(smem_u32(b_stage + s * B_BYTES));
+#pragma unroll
+                for (int k = 0; k < TK / 16; ++k)   // 32 bytes = 2 units of 16 bytes per K step
+                    umma_bf16(tmem_base, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+                umma_commit(&empty[s]);   // the stage is free once these products have read it
+            }
+            umma_commit(acc_ready);       // arrives when every product above has finished
+        }
+    } else {
+        const int quad = warp & 3;        // the 32 tensor-memory lanes this warp may read
+        const int row = m0 + quad * 32 + lane;
+        const bool got = mbar_wait(acc_ready, 0, 3);
+        tc_fence_after();
+        if (got) {
+            const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+            if (!SWIGLU) {
+                const int n0 = n_blk * TN;
+#pragma unroll 1
+                for (int c = 0; c < TN / 32; ++c) {
+                    uint32_t v[32];
+                    tmem_ld32(lane_addr + c * 32, v);
+                    tmem_ld_wait();
+                    const int col = n0 + c * 32;
+                    if (row < M && col < N) {
+                        bf16* dst = Y + (int64_t)row * ldy + col;
+                        if (col + 32 <= N && ((ldy & 7) == 0)) {
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                uint4 o;
+                                o.x = pack2(__uint_as_float(v[8 * i + 0]), __uint_as_float(v[8 * i + 1]));
+                                o.y = pack2(__uint_as_float(v[8 * i + 2]), __uint_as_float(v[8 * i + 3]));
+                                o.z = pack2(__uint_as_float(v[8 * i + 4]), __uint_as_float(v[8 * i + 5]));
+                                o.w = pack2(__uint_as_float(v[8 * i + 6]), __uint_as_float(v[8 * i + 7]));
+                                reinterpret_cast<uint4*>(dst)[i] = o;
+                            }
+                        } else {
+                            for (int i = 0; i < 32 && col + i < N; ++i)
+                                dst[i] = __float2bfloat16_rn(__uint_as_float(v[i]));
+                        }
+                    }
+                }
+            } else {
+                const int f0 = n_blk * 128;
+#pragma unroll 1
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t gv[32], uv[32];
+                    tmem_ld32(lane_addr + c * 32, gv);
+                    tmem_ld32(lane_addr + 128 + c * 32, uv);
+                    tmem_ld_wait();
+                    const int col = f0 + c * 32;
+                    if (row < M && col < n_half) {
+                        bf16* dst = Y + (int64_t)row * ldy + col;
+                        float o[32];
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            // gate and up are rounded to bfloat16 first, as the unfused path does
+                            const float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(gv[i])));
+                            const float u = __bfloat162float(__float2bfloat16_rn(__uint_as_float(uv[i])));
+                            o[i] = g / (1.0f + expf(-g)) * u;
+                        }
+                        if (col + 32 <= n_half && ((ldy & 7) == 0)) {
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                uint4 q;
+                                q.x = pack2(o[8 * i + 0], o[8 * i + 1]);
+                                q.y = pack2(o[8 * i + 2], o[8 * i + 3]);
+                                q.z = pack2(o[8 * i + 4], o[8 * i + 5]);
+                                q.w = pack2(o[8 * i + 6], o[8 * i + 7]);
+                                reinterpret_cast<uint4*>(dst)[i] = q;
+                            }
+                        } else {
+                            for (int i = 0; i < 32 && col + i < n_half; ++i)
+                                dst[i] = __float2bfloat16_rn(o[i]);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n"
+                     ::"r"(tmem_base), "r"(256u) : "memory");
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) ==
+                cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// A [rows, K] bfloat16 matrix with row stride ld, boxes of 128 rows x 64 columns, 128-byte swizzle.
+static bool make_map(CUtensorMap* map, const void* base, int rows, int K, int64_t ld) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)TK, 128u};
+    cuuint32_t elem[2] = {1u, 1u};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
+              elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace sllm
+
+using namespace sllm;
+
+// The first error a bounded wait recorded since the last call (0 = none): 1 = producer waiting
+// for a free stage, 2 = MMA issuer waiting for data, 3 = epilogue waiting for the accumulator.
+// Synchronises the device.
+SLLM_EXPORT int sllm_gemm_tc_error() {
+    int code = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&code, g_gemm_error, sizeof(int)) != cudaSuccess) return -1;
+    if (code) cudaMemcpyToSymbol(g_gemm_error, &zero, sizeof(int));
+    return code;
+}
+
+// X [M, K], W [N, K] bfloat16, 16-byte aligned with row strides that are multiples of 8;
+// Y bfloat16 [M, N] (swiglu = 0) or [M, N / 2] (swiglu = 1, W = [gate rows; up rows]).
+SLLM_EXPORT int sllm_gemm_tc(const void* X, const void* W, void* Y, int M, int N, int K,
+                             int64_t ldx, int64_t ldw, int64_t ldy, int swiglu,
+                             cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || (K % 8) || (ldx % 8) || (ldw % 8) || (swiglu && (N % 2)))
+        return (int)cudaErrorInvalidValue;
+    if (((uintptr_t)X & 15) || ((uintptr_t)W & 15) || ((uintptr_t)Y & 1))
+        return (int)cudaErrorInvalidValue;
+    CUtensorMap map_x, map_w;
+    if (!make_map(&map_x, X, M, K, ldx) || !make_map(&map_w, W, N, K, ldw))
+        return (int)cudaErrorNotSupported;
+    const int n_half = N / 2;
+    const int tiles_n = swiglu ? (n_half + 127) / 128 : (N + TN - 1) / TN;
+    dim3 grid(tiles_n, (M + TM - 1) / TM);
+    if (grid.y > 65535) return (int)cudaErrorInvalidValue;
+    cudaError_t e;
+    if (swiglu) {
+        e = cudaFuncSetAttribute(gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)TC_SMEM);
+        if (e != cudaSuccess) return (int)e;
+        gemm_tc_kernel<true><<<grid, TC_THREADS, TC_SMEM, stream>>>(map_x, map_w, (bf16*)Y, M, N, K,
+                                                                  ldy, n_half);
+    } else {
+        e = cudaFuncSetAttribute(gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)TC_SMEM);
+        if (e != cudaSuccess) return (int)e;
+        gemm_tc_kernel<false><<<grid, TC_THREADS, TC_SMEM, stream>>>(map_x, map_w, (bf16*)Y, M, N, K,
+                                                                   ldy, n_half);
+    }
+    SLLM_LAUNCH_CHECK();
+    return 0;
+}

@@ -33,6 +33,7 @@ CORE_LIBRARIES: dict[str, tuple[tuple[str, ...], tuple[str, ...]]] = {
     "sllm_gemm_simt": (("gemm_simt.cu",), ()),
     "sllm_sampling": (("sampling.cu",), ()),
     "sllm_gemv_mma": (("gemv_mma.cu",), ()),
+    "sllm_gemm_tcgen05": (("gemm_tcgen05.cu",), ()),
 }
 
 
@@ -215,6 +216,33 @@ def gemv_mma(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool =
         c_int64(w.stride(0)), c_int64(out.stride(0)), c_int(int(swiglu)),
         c_int(_code(out.dtype)), _stream()), "gemv_mma")
     return out
+
+
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool = False
+            ) -> torch.Tensor:
+    """out[M, N] = x[M, K] @ w[N, K]^T in bfloat16 on tcgen05 tensor cores (TMA-fed, accumulator
+    in tensor memory).  ``swiglu``: w = [gate rows; up rows], out[M, N/2] = silu(gate) * up."""
+    _need(x, torch.bfloat16, "x", contiguous=False)
+    _need(w, torch.bfloat16, "w", contiguous=False)
+    _need(out, torch.bfloat16, "out", contiguous=False)
+    (m, k), (n, k2) = x.shape, w.shape
+    n_out = n // 2 if swiglu else n
+    if k != k2 or out.shape != (m, n_out) or x.stride(1) != 1 or w.stride(1) != 1 \
+            or out.stride(1) != 1:
+        raise KernelError(f"gemm shapes/strides: x {list(x.shape)}, w {list(w.shape)}, "
+                          f"out {list(out.shape)}")
+    if k % 8 or x.stride(0) % 8 or w.stride(0) % 8:
+        raise KernelError("gemm_tc needs rows that are multiples of 8 elements (16 bytes)")
+    _check(_core("sllm_gemm_tcgen05").sllm_gemm_tc(
+        _ptr(x), _ptr(w), _ptr(out), c_int(m), c_int(n), c_int(k), c_int64(x.stride(0)),
+        c_int64(w.stride(0)), c_int64(out.stride(0)), c_int(int(swiglu)), _stream()), "gemm_tc")
+    return out
+
+
+def gemm_tc_error() -> int:
+    """The first error a bounded wait inside gemm_tc recorded since the last call (0 = none).
+    Synchronises the device."""
+    return int(_core("sllm_gemm_tcgen05").sllm_gemm_tc_error())
 
 
 # --------------------------------------------------------------------------- rope and cache

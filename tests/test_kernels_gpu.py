@@ -119,6 +119,33 @@ def test_gemv_streams_weights_once(ops, m, n, k):
                                    **TOL["bfloat16"])
 
 
+@pytest.mark.parametrize("m, n, k", [(128, 256, 64), (128, 256, 256), (256, 512, 192), (300, 600, 200),
+                                     (5, 40, 72), (2048, 1024, 512), (130, 6144, 4096)])
+def test_gemm_tcgen05(ops, m, n, k):
+    g = torch.Generator().manual_seed(m + n + k)
+    if k <= 256:   # small integers: every product and sum is exact, also in bfloat16
+        x = torch.randint(-1, 2, (m, k), generator=g).to(torch.bfloat16)
+        w = torch.randint(-1, 2, (n, k), generator=g).to(torch.bfloat16)
+        tol = dict(rtol=0, atol=0)
+    else:
+        x = rand(m, k, dtype=torch.bfloat16, seed=1)
+        w = rand(n, k, dtype=torch.bfloat16, seed=2, scale=0.05)
+        tol = TOL["bfloat16"]
+    want = x.float() @ w.float().T
+    out = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.gemm_tc(x.cuda(), w.cuda(), out)
+    assert ops.gemm_tc_error() == 0
+    torch.testing.assert_close(out.cpu().float(), want.to(torch.bfloat16).float(), **tol)
+    if n % 2 == 0:
+        half = n // 2
+        out = torch.full((m, half), float("nan"), dtype=torch.bfloat16, device="cuda")
+        ops.gemm_tc(x.cuda(), w.cuda(), out, swiglu=True)
+        assert ops.gemm_tc_error() == 0
+        gate, up = want[:, :half].to(torch.bfloat16).float(), want[:, half:].to(torch.bfloat16).float()
+        torch.testing.assert_close(out.cpu().float(), gate * torch.sigmoid(gate) * up,
+                                   **TOL["bfloat16"])
+
+
 def paged_cache(k, v, page_size, n_pages, seed, dtype):
     """Scatter k, v [G, T, hd] of several rows into shuffled pages.  Returns pages, tables."""
     g = torch.Generator().manual_seed(seed)
