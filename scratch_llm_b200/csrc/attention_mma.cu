@@ -87,10 +87,13 @@ template <bool SPLIT> struct Mode {
     static constexpr int WKEYS = SPLIT ? BKV / NWARP : BKV;  // keys of a tile one warp takes
     static constexpr int NT = WKEYS / 8;                     // 8-wide score tiles per warp
     static constexpr int PK = WKEYS / 16;                    // k-steps of p v per warp
+    // Pipeline depth.  Two stages leave room for three CTAs of the split kernel per SM; the
+    // kernel is bound by instruction issue, so more resident warps pay more than deeper queues.
+    static constexpr int NSTAGE = 2;
 };
 
 template <bool SPLIT> constexpr size_t smem_bytes() {
-    return ((size_t)Mode<SPLIT>::BQ + 4 * BKV) * LDS * sizeof(bf16);
+    return ((size_t)Mode<SPLIT>::BQ + 2 * Mode<SPLIT>::NSTAGE * BKV) * LDS * sizeof(bf16);
 }
 
 struct AttnArgs {
@@ -103,16 +106,20 @@ struct AttnArgs {
 };
 
 template <bool SPLIT>
-__global__ void __launch_bounds__(THREADS) attn_mma_kernel(const AttnArgs a) {
+__global__ void __launch_bounds__(THREADS, SPLIT ? 3 : 2) attn_mma_kernel(const AttnArgs a) {
     using M = Mode<SPLIT>;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);
-    bf16* Ks = Qs + M::BQ * LDS;       // 2 stages of [BKV][LDS]
-    bf16* Vs = Ks + 2 * BKV * LDS;     // 2 stages of [BKV][LDS]
+    bf16* Ks = Qs + M::BQ * LDS;               // NSTAGE stages of [BKV][LDS]
+    bf16* Vs = Ks + M::NSTAGE * BKV * LDS;     // NSTAGE stages of [BKV][LDS]
 
+    pdl_trigger();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n_splits = SPLIT ? a.n_splits : 1;
-    const int q_tile = blockIdx.x / n_splits, split = blockIdx.x % n_splits;
+    // query tiles in descending order: under the causal mask the last tile of a row has the
+    // most keys to walk, and the longest jobs should start first
+    const int q_tile = (int)(gridDim.x / n_splits) - 1 - (int)(blockIdx.x / n_splits);
+    const int split = blockIdx.x % n_splits;
     const int r = a.row_list ? a.row_list[blockIdx.y] : blockIdx.y;
     const int g = blockIdx.z;
     const int GS = a.H / a.G;
@@ -143,30 +150,47 @@ __global__ void __launch_bounds__(THREADS) attn_mma_kernel(const AttnArgs a) {
     cp_async_commit();
 
     const int64_t v_off = (int64_t)a.G * a.page_size * HD;
-    auto load_tile = [&](int tile, int stage) {
-        const int kt = k_lo + tile * BKV;
+    // Where a tile's keys live: thread j < 64 looks up key j's page once and leaves the element
+    // offset of its K row in shared memory (-1: no such key); all threads then copy 16-byte
+    // pieces from those offsets.  The lookup for a tile happens one step before its copy.
+    __shared__ long long key_off[2][BKV];
+    auto locate_tile = [&](int tile, int slot) {
+        if (tid < BKV) {
+            const int kpos = k_lo + tile * BKV + tid;
+            long long off = -1;
+            if (tile < tile_end && kpos <= last_pos) {
+                const int page = a.block_table[(int64_t)r * a.table_stride + kpos / a.page_size];
+                if (page >= 0)
+                    off = (((long long)page * 2 * a.G + g) * a.page_size + kpos % a.page_size) * HD;
+            }
+            key_off[slot][tid] = off;
+        }
+    };
+    constexpr int PIECES = BKV * CHUNKS / THREADS;
+    static_assert(BKV * CHUNKS % THREADS == 0, "pieces per thread");
+    auto load_tile = [&](int tile, int stage, int slot) {
         bf16* ks = Ks + stage * BKV * LDS;
         bf16* vs = Vs + stage * BKV * LDS;
-        for (int idx = tid; idx < BKV * CHUNKS; idx += THREADS) {
+#pragma unroll
+        for (int i = 0; i < PIECES; ++i) {
+            const int idx = tid + i * THREADS;
             const int j = idx / CHUNKS, c = idx - j * CHUNKS;
-            const int kpos = kt + j;
-            bool valid = kpos <= last_pos;
-            const bf16* src = a.pages;
-            if (valid) {
-                const int page = a.block_table[(int64_t)r * a.table_stride + kpos / a.page_size];
-                valid = page >= 0;
-                if (valid)
-                    src = a.pages + (((int64_t)page * 2 * a.G + g) * a.page_size +
-                                     kpos % a.page_size) * HD + c * 8;
-            }
-            cp_async16(ks + j * LDS + c * 8, src, valid);
-            cp_async16(vs + j * LDS + c * 8, valid ? src + v_off : src, valid);
+            const long long off = key_off[slot][j];
+            const bool ok = off >= 0;
+            const bf16* src = ok ? a.pages + off + c * 8 : a.pages;
+            cp_async16(ks + j * LDS + c * 8, src, ok);
+            cp_async16(vs + j * LDS + c * 8, ok ? src + v_off : src, ok);
         }
     };
 
-    if (tile_begin < tile_end) load_tile(tile_begin, 0);
+    // prologue: the first NSTAGE - 1 tiles (one commit group each, empty past the end)
+    static_assert(M::NSTAGE == 2, "the key-offset slots below assume two stages");
+    locate_tile(tile_begin, 0);
+    __syncthreads();
+    if (tile_begin < tile_end) load_tile(tile_begin, 0, 0);
     cp_async_commit();
-    cp_async_wait<1>();  // the queries have landed (the first key tile may still be in flight)
+    locate_tile(tile_begin + 1, 1);
+    cp_async_wait<1>();  // the queries have landed (the first key tile may be in flight)
     __syncthreads();
 
     // ---- this warp's query fragments
@@ -186,6 +210,9 @@ __global__ void __launch_bounds__(THREADS) attn_mma_kernel(const AttnArgs a) {
         qvalid[h] = p < n_packed;
         qpos[h] = pos0 + (qvalid[h] ? p / GS : 0);
     }
+    // tiles that lie wholly before the warp's first query need no mask
+    const bool warp_full = q0 + wq + 15 < n_packed && a.window <= 0;
+    const int warp_first_pos = pos0 + (q0 + wq) / GS;
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
     float o[DTILES][4];
 #pragma unroll
@@ -195,10 +222,14 @@ __global__ void __launch_bounds__(THREADS) attn_mma_kernel(const AttnArgs a) {
 
     for (int tile = tile_begin; tile < tile_end; ++tile) {
         const int stage = (tile - tile_begin) & 1;
-        if (tile + 1 < tile_end) load_tile(tile + 1, stage ^ 1);
+        // offsets of tile + 1 were located one step ago (slot stage ^ 1) and are visible since
+        // the barrier that ended that step
+        if (tile + 1 < tile_end) load_tile(tile + 1, stage ^ 1, stage ^ 1);
         cp_async_commit();
         cp_async_wait<1>();  // everything but the group just committed has landed
         __syncthreads();
+        // slot `stage` was read by the copy issued one step ago; it is free for tile + 2
+        locate_tile(tile + 2, stage);
         const bf16* ks_s = Ks + stage * BKV * LDS + key_lo_w * LDS;
         const bf16* vs_s = Vs + stage * BKV * LDS + key_lo_w * LDS;
         const int kt = k_lo + tile * BKV + key_lo_w;  // absolute position of the warp's key 0
@@ -222,17 +253,27 @@ __global__ void __launch_bounds__(THREADS) attn_mma_kernel(const AttnArgs a) {
         }
         // ---- mask, online softmax (base 2, in 32-bit)
         float mx[2] = {-INFINITY, -INFINITY};
+        if (warp_full && kt + M::WKEYS - 1 <= warp_first_pos) {
 #pragma unroll
-        for (int nt = 0; nt < M::NT; ++nt)
+            for (int nt = 0; nt < M::NT; ++nt)
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int h = e >> 1;
-                const int kpos = kt + nt * 8 + (lane & 3) * 2 + (e & 1);
-                const bool ok = qvalid[h] && kpos <= qpos[h] &&
-                                (a.window <= 0 || kpos > qpos[h] - a.window);
-                s[nt][e] = ok ? s[nt][e] * a.scale_log2 : -INFINITY;
-                mx[h] = fmaxf(mx[h], s[nt][e]);
-            }
+                for (int e = 0; e < 4; ++e) {
+                    s[nt][e] *= a.scale_log2;
+                    mx[e >> 1] = fmaxf(mx[e >> 1], s[nt][e]);
+                }
+        } else {
+#pragma unroll
+            for (int nt = 0; nt < M::NT; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int h = e >> 1;
+                    const int kpos = kt + nt * 8 + (lane & 3) * 2 + (e & 1);
+                    const bool ok = qvalid[h] && kpos <= qpos[h] &&
+                                    (a.window <= 0 || kpos > qpos[h] - a.window);
+                    s[nt][e] = ok ? s[nt][e] * a.scale_log2 : -INFINITY;
+                    mx[h] = fmaxf(mx[h], s[nt][e]);
+                }
+        }
         float corr[2];
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
@@ -271,7 +312,7 @@ __global__ void __launch_bounds__(THREADS) attn_mma_kernel(const AttnArgs a) {
                 mma_bf16(o[dn + 1], pa[kk], b[2], b[3]);
             }
         }
-        __syncthreads();  // this stage is overwritten by the load issued two iterations on
+        __syncthreads();  // this stage is overwritten by the load issued in the next iteration
     }
     cp_async_wait<0>();
 
@@ -352,6 +393,7 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o,
                                   const int* __restrict__ row_start,
                                   const int* __restrict__ row_list, bf16* __restrict__ out,
                                   int64_t out_stride, int H) {
+    pdl_trigger();
     const int r = row_list ? row_list[blockIdx.x] : blockIdx.x;
     const int head = blockIdx.y;
     for (int t = row_start[r]; t < row_start[r + 1]; ++t) {

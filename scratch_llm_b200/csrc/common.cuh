@@ -20,6 +20,19 @@
 
 namespace sllm {
 
+// Programmatic dependent launch.  pdl_trigger() lets the next kernel in the stream start to be
+// scheduled while this one still runs; it only takes effect if that kernel was launched with
+// the programmatic-stream-serialization attribute, and such a kernel must call pdl_wait()
+// before it reads or writes anything an earlier kernel may touch (weights, which nothing
+// writes, may be read before).  pdl_wait() returns once all earlier kernels have completed
+// and their writes are visible; without the launch attribute it returns at once.
+__device__ __forceinline__ void pdl_trigger() {
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait() {
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
+}
+
 __device__ __forceinline__ float to_float(float v) { return v; }
 __device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
 

@@ -12,6 +12,7 @@ namespace sllm {
 template <typename T>
 __global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ table,
                              float* __restrict__ out, int d) {
+    pdl_trigger();
     const int64_t n = blockIdx.x;
     const T* src = table + (int64_t)ids[n] * d;
     float* dst = out + n * d;
@@ -26,6 +27,7 @@ template <typename T>
 __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const T* __restrict__ delta,
                                    const int* __restrict__ index, const float* __restrict__ w,
                                    float eps, T* __restrict__ out, int d) {
+    pdl_trigger();
     __shared__ float scratch[33];
     const int64_t o = blockIdx.x;
     const int64_t row = index ? (int64_t)index[o] : o;
@@ -58,6 +60,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const T* __restric
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int64_t n_rows,
                               int F) {
+    pdl_trigger();
     const int64_t total = n_rows * F;
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
          i += (int64_t)gridDim.x * blockDim.x) {
@@ -67,6 +70,91 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
         const float u = to_float(gu[n * 2 * F + F + f]);
         const float s = g / (1.0f + expf(-g));
         out[i] = from_float<T>(s * u);
+    }
+}
+
+// The same as add_rmsnorm_kernel for d % 4 == 0 and d <= 4 * VEC_CHUNKS * blockDim.x: 16-byte
+// accesses, the row stays in registers between the two passes.  The sum of squares is taken
+// in the same thread-strided order as in the scalar kernel's formula, in 32-bit.
+constexpr int VEC_CHUNKS = 4;
+
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+    const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+    return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 raw;
+    raw.x = *reinterpret_cast<uint32_t*>(&a);
+    raw.y = *reinterpret_cast<uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(p) = raw;
+}
+
+template <typename T>
+__global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const T* __restrict__ delta,
+                                       const int* __restrict__ index, const float* __restrict__ w,
+                                       float eps, T* __restrict__ out, int d) {
+    pdl_trigger();
+    __shared__ float scratch[33];
+    const int64_t o = blockIdx.x;
+    const int64_t row = index ? (int64_t)index[o] : o;
+    float* x = resid + row * d;
+    const T* dl = delta ? delta + row * d : nullptr;
+    T* y = out + o * d;
+    float4 v[VEC_CHUNKS];
+    float ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < VEC_CHUNKS; ++c) {
+        const int i = (threadIdx.x + c * blockDim.x) * 4;
+        if (i < d) {
+            v[c] = load4(x + i);
+            if (dl) {
+                const float4 a = load4(dl + i);
+                v[c].x += a.x; v[c].y += a.y; v[c].z += a.z; v[c].w += a.w;
+                if (!index) store4(x + i, v[c]);
+            }
+            ss += v[c].x * v[c].x + v[c].y * v[c].y + v[c].z * v[c].z + v[c].w * v[c].w;
+        }
+    }
+    const float total = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(total / (float)d + eps);
+#pragma unroll
+    for (int c = 0; c < VEC_CHUNKS; ++c) {
+        const int i = (threadIdx.x + c * blockDim.x) * 4;
+        if (i < d) {
+            const float4 g = load4(w + i);
+            store4(y + i, make_float4(v[c].x * inv * g.x, v[c].y * inv * g.y, v[c].z * inv * g.z,
+                                      v[c].w * inv * g.w));
+        }
+    }
+}
+
+// swiglu for F % 8 == 0: 16-byte accesses (bfloat16) / 32-byte (float).
+template <typename T>
+__global__ void swiglu_vec_kernel(const T* __restrict__ gu, T* __restrict__ out, int64_t n_rows,
+                                  int F) {
+    pdl_trigger();
+    const int per_row = F / 8;
+    const int64_t total = n_rows * per_row;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t n = i / per_row;
+        const int f = (int)(i - n * per_row) * 8;
+        const T* g = gu + n * 2 * F + f;
+        const T* u = g + F;
+        T* o = out + n * F + f;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const float4 a = load4(g + 4 * h), b = load4(u + 4 * h);
+            store4(o + 4 * h, make_float4(a.x / (1.0f + expf(-a.x)) * b.x,
+                                          a.y / (1.0f + expf(-a.y)) * b.y,
+                                          a.z / (1.0f + expf(-a.z)) * b.z,
+                                          a.w / (1.0f + expf(-a.w)) * b.w));
+        }
     }
 }
 
@@ -102,6 +190,18 @@ SLLM_EXPORT int sllm_add_rmsnorm(float* resid, const void* delta, const int* ind
                                  int dtype, cudaStream_t stream) {
     if (n_out <= 0) return 0;
     if (d <= 0) return (int)cudaErrorInvalidValue;
+    if (d % 4 == 0 && d <= 4 * VEC_CHUNKS * 1024 && dtype >= 0 && dtype <= 1) {
+        int vt = 32;
+        while (vt < 1024 && vt * 4 * (d > 4096 ? VEC_CHUNKS : 1) < d) vt <<= 1;
+        if (dtype == 0)
+            add_rmsnorm_vec_kernel<float><<<n_out, vt, 0, stream>>>(
+                resid, (const float*)delta, index, w, eps, (float*)out, d);
+        else
+            add_rmsnorm_vec_kernel<__nv_bfloat16><<<n_out, vt, 0, stream>>>(
+                resid, (const __nv_bfloat16*)delta, index, w, eps, (__nv_bfloat16*)out, d);
+        SLLM_LAUNCH_CHECK();
+        return 0;
+    }
     const int threads = norm_threads(d);
     if (dtype == 0)
         add_rmsnorm_kernel<float><<<n_out, threads, 0, stream>>>(
@@ -119,8 +219,20 @@ SLLM_EXPORT int sllm_swiglu(const void* gu, void* out, int n_rows, int F, int dt
                             cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (F <= 0) return (int)cudaErrorInvalidValue;
-    const int64_t total = (int64_t)n_rows * F;
     const int threads = 256;
+    if (F % 8 == 0 && dtype >= 0 && dtype <= 1) {
+        int64_t vblocks = ((int64_t)n_rows * (F / 8) + threads - 1) / threads;
+        if (vblocks > 148 * 16) vblocks = 148 * 16;
+        if (dtype == 0)
+            swiglu_vec_kernel<float><<<(int)vblocks, threads, 0, stream>>>(
+                (const float*)gu, (float*)out, n_rows, F);
+        else
+            swiglu_vec_kernel<__nv_bfloat16><<<(int)vblocks, threads, 0, stream>>>(
+                (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, n_rows, F);
+        SLLM_LAUNCH_CHECK();
+        return 0;
+    }
+    const int64_t total = (int64_t)n_rows * F;
     int64_t blocks = (total + threads - 1) / threads;
     if (blocks > 148 * 32) blocks = 148 * 32;
     if (dtype == 0)

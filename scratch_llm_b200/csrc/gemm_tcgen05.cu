@@ -115,7 +115,7 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// Grid (tiles along N, tiles along M).  SWIGLU: W = [gate rows; up rows] (n_half each); tile
+// Grid (tiles along M, tiles along N).  SWIGLU: W = [gate rows; up rows] (n_half each); tile
 // column block j covers features j*128..+127 and Y has n_half columns.
 template <bool SWIGLU>
 __global__ void __launch_bounds__(TC_THREADS, 1)
@@ -132,8 +132,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_ready + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.y * TM;
-    const int n_blk = blockIdx.x;
+    // consecutive CTAs share a tile of W and walk the token blocks, so W streams from HBM once
+    // while the (smaller) activations are re-read from L2
+    const int m0 = blockIdx.x * TM;
+    const int n_blk = blockIdx.y;
     // rows of W this tile multiplies: two boxes of 128 rows
     const int w_row0 = SWIGLU ? n_blk * 128 : n_blk * TN;
     const int w_row1 = SWIGLU ? n_half + n_blk * 128 : n_blk * TN + 128;
@@ -327,7 +329,7 @@ SLLM_EXPORT int sllm_gemm_tc(const void* X, const void* W, void* Y, int M, int N
         return (int)cudaErrorNotSupported;
     const int n_half = N / 2;
     const int tiles_n = swiglu ? (n_half + 127) / 128 : (N + TN - 1) / TN;
-    dim3 grid(tiles_n, (M + TM - 1) / TM);
+    dim3 grid((M + TM - 1) / TM, tiles_n);
     if (grid.y > 65535) return (int)cudaErrorInvalidValue;
     cudaError_t e;
     if (swiglu) {

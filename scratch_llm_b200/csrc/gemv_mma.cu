@@ -85,9 +85,9 @@ gemv_mma_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, TOut* __
     }
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
 
-    for (int s0 = step_begin; s0 < step_end; s0 += GV_UNROLL) {
-        uint4 wv[GV_UNROLL][NW][2];
-        uint4 xv[GV_UNROLL][MT];
+    uint4 wv[GV_UNROLL][NW][2];
+    uint4 xv[GV_UNROLL][MT];
+    auto load_w = [&](int s0) {
 #pragma unroll
         for (int u = 0; u < GV_UNROLL; ++u) {
             const int k = (s0 + u) * 32 + 8 * t;
@@ -97,10 +97,19 @@ gemv_mma_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, TOut* __
 #pragma unroll
                 for (int h = 0; h < 2; ++h)
                     wv[u][b][h] = (kin && wok[b][h]) ? ld_stream16(wrow[b][h] + k) : zero;
+        }
+    };
+    auto load_x = [&](int s0) {
+#pragma unroll
+        for (int u = 0; u < GV_UNROLL; ++u) {
+            const int k = (s0 + u) * 32 + 8 * t;
+            const bool kin = (s0 + u) < step_end && k < K;
 #pragma unroll
             for (int j = 0; j < MT; ++j)
                 xv[u][j] = (kin && xok[j]) ? *reinterpret_cast<const uint4*>(xrow[j] + k) : zero;
         }
+    };
+    auto multiply = [&]() {
 #pragma unroll
         for (int u = 0; u < GV_UNROLL; ++u)
 #pragma unroll
@@ -112,6 +121,20 @@ gemv_mma_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, TOut* __
                     mma16816(acc[b][j], wv[u][b][0].z, wv[u][b][1].z, wv[u][b][0].w,
                              wv[u][b][1].w, xv[u][j].z, xv[u][j].w);
                 }
+    };
+    // The weights of the first steps are requested before the wait for earlier kernels: nothing
+    // writes weights, so this part of the stream overlaps the previous kernel's tail.
+    pdl_trigger();
+    if (step_begin < step_end) load_w(step_begin);
+    pdl_wait();
+    if (step_begin < step_end) {
+        load_x(step_begin);
+        multiply();
+    }
+    for (int s0 = step_begin + GV_UNROLL; s0 < step_end; s0 += GV_UNROLL) {
+        load_w(s0);
+        load_x(s0);
+        multiply();
     }
     // acc[b][j]: e0, e1 = (row g, tokens 8j + 2t, +1); e2, e3 = (row g + 8, same tokens).
     // The warps' partial sums meet in shared memory, one block kind after the other, and are
@@ -155,14 +178,28 @@ gemv_mma_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, TOut* __
     }
 }
 
+static int g_gemv_pdl = 1;
+
 template <int MT, bool SWIGLU, typename TOut>
 static int launch_gemv(const void* X, const void* W, void* Y, int M, int N, int K, int64_t ldx,
                        int64_t ldw, int64_t ldy, cudaStream_t stream) {
     const int n_out = SWIGLU ? N / 2 : N;
     const int grid = (n_out + GV_ROWS - 1) / GV_ROWS;
-    gemv_mma_kernel<MT, SWIGLU, TOut><<<grid, GV_THREADS, 0, stream>>>(
-        (const bf16*)X, (const bf16*)W, (TOut*)Y, M, N, K, ldx, ldw, ldy);
-    SLLM_LAUNCH_CHECK();
+    // launched so that it may start while the previous kernel of the stream drains: the kernel
+    // requests its first weights, then waits for that kernel (pdl_wait) before it reads X
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(GV_THREADS);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = g_gemv_pdl;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_mma_kernel<MT, SWIGLU, TOut>, (const bf16*)X,
+                                       (const bf16*)W, (TOut*)Y, M, N, K, ldx, ldw, ldy);
+    if (e != cudaSuccess) return (int)e;
     return 0;
 }
 
@@ -180,6 +217,9 @@ static int pick_mt(const void* X, const void* W, void* Y, int M, int N, int K, i
 using namespace sllm;
 
 SLLM_EXPORT int sllm_gemv_max_tokens() { return 64; }
+
+// 1 (default): launch with programmatic stream serialization; 0: plain launches.
+SLLM_EXPORT void sllm_gemv_set_pdl(int on) { g_gemv_pdl = on ? 1 : 0; }
 
 // X [M, K], W [N, K] bfloat16, rows 16-byte aligned (K, ldx, ldw multiples of 8).
 // swiglu = 0: Y [M, N].  swiglu = 1: W = [gate rows; up rows], Y [M, N / 2].

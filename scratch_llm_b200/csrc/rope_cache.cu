@@ -21,6 +21,7 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
                                      const int* __restrict__ block_table, int table_stride,
                                      int page_size, int H, int G, int hd, int rotate,
                                      int interleaved, int write) {
+    pdl_trigger();
     const int64_t n = blockIdx.x;
     const int half = hd >> 1;
     const int pos = positions[n];
