@@ -60,6 +60,7 @@ class StepBatch:
     n_multi: int = 0
     max_new_multi: int = 0
     max_context_single: int = 0
+    context_bucket: int = 0   # max_context_single rounded up to a power of two (at least 256)
     # host copies, for parts that plan their launches from them
     host_row_new: list[int] = field(default_factory=list)
     host_row_pos0: list[int] = field(default_factory=list)
@@ -120,6 +121,13 @@ class BatchStager:
         ev.record()
         self._events[turn] = ev
         return [self._dev[o:o + a.size].view(a.shape) for a, o in zip(parts, offsets)]
+
+
+def context_bucket(context: int) -> int:
+    bucket = 256
+    while bucket < context:
+        bucket *= 2
+    return bucket
 
 
 def build_batch(cache, stager: BatchStager, rows: Sequence[RowInput], vocab_size: int,
@@ -194,4 +202,5 @@ def build_batch(cache, stager: BatchStager, rows: Sequence[RowInput], vocab_size
         multi_rows=dev[8], block_tables=dev[9:], n_single=len(single), n_multi=len(multi),
         max_new_multi=max((lens[i] for i in multi), default=0),
         max_context_single=max((int(row_pos0[i]) + 1 for i in single), default=0),
+        context_bucket=context_bucket(max((int(row_pos0[i]) + 1 for i in single), default=0)),
         host_row_new=lens, host_row_pos0=row_pos0.tolist())

@@ -47,7 +47,7 @@ class _CapturedStep:
 
 class ModelRunner:
     """``cuda_graphs``: steps in which every row brings one token and wants its logits (decode)
-    are captured once per number of rows and replayed afterwards, in the manner of the
+    are captured once per (number of rows, context bucket) and replayed afterwards, in the manner of the
     reference's CudaGraphDecoder (src/scratch_llm/serving/cudagraph.py:31-96) and its
     per-batch-size buckets (src/scratch_llm/serving/graph_buckets.py:94-200): the descriptor
     arrays, the block tables (at their full width) and the pools keep their addresses, the
@@ -69,9 +69,9 @@ class ModelRunner:
             getattr(part, "capturable", True) for block in model.blocks
             for part in (block.mixer, block.feed_forward))
         self._table_width = self.cache.max_pages_per_request(self.max_position)
-        self._captured: dict[int, _CapturedStep] = {}
+        self._captured: dict[tuple[int, int], _CapturedStep] = {}
         self.replayed_kernels = 0   # kernels of this package launched through graph replays
-        self._seen_sizes: set[int] = set()
+        self._seen_sizes: set[tuple[int, int]] = set()
         # room for the widest decode step, so that captured addresses stay valid
         self._stager.reserve(8 * (max_requests + 4) + 4 * max(1, len(self.cache.groups)) +
                              max_requests * (self._table_width + 4) * max(1, len(self.cache.groups)))
@@ -119,13 +119,14 @@ class ModelRunner:
                             table_width=self._table_width)
         pointers = (batch.token_ids.data_ptr(), batch.logit_index.data_ptr(),
                     tuple(t.data_ptr() for t in batch.block_tables))
-        cap = self._captured.get(n)
+        key = (n, batch.context_bucket)   # launch shapes depend on these two alone
+        cap = self._captured.get(key)
         if cap is not None and cap.pointers == pointers:
             cap.graph.replay()
             self.replayed_kernels += cap.n_kernels
             return cap.logits.clone()   # the graph's own output is overwritten by the next replay
-        if n not in self._seen_sizes:   # first use of this size: run it plainly (warms up)
-            self._seen_sizes.add(n)
+        if key not in self._seen_sizes:   # first use of this shape: run it plainly (warms up)
+            self._seen_sizes.add(key)
             return self.model.forward(batch, self.cache)
         graph = torch.cuda.CUDAGraph()
         before = ops.launch_count
@@ -141,7 +142,7 @@ class ModelRunner:
             return self.model.forward(batch, self.cache)
         cap = _CapturedStep(graph, logits, pointers)
         cap.n_kernels = ops.launch_count - before
-        self._captured[n] = cap
+        self._captured[key] = cap
         graph.replay()
         self.replayed_kernels += cap.n_kernels
         return logits.clone()

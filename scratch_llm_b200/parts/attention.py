@@ -21,6 +21,20 @@ from .linear import Linear
 from .registry import register_mixer
 
 
+def decode_splits(base_ctas: int, context: int, slots: int = 3 * 148) -> int:
+    """How many CTAs share the keys of one (row, kv head) in the split decode kernel: the count
+    that minimises waves x (key tiles per CTA + fixed cost), a function of the batch's shape
+    and of the context bucket alone, so that it is the same for every step that replays one
+    captured graph.  ``slots``: CTAs of the split kernel resident on the GPU at once."""
+    tiles = max(1, -(-context // 64))
+    best, best_cost = 1, None
+    for n in range(1, min(32, tiles) + 1):
+        cost = -(-base_ctas * n // slots) * (-(-tiles // n) + 2) + (1 if n > 1 else 0)
+        if best_cost is None or cost < best_cost:
+            best, best_cost = n, cost
+    return best
+
+
 @register_mixer("gqa_attention")
 class GQAttention(Mixer):
     def __init__(self, hidden_size: int, n_heads: int, n_kv_heads: int, head_dim: int,
@@ -80,8 +94,7 @@ class GQAttention(Mixer):
 
     def _attend_tensor_cores(self, q, out, batch, cache: CacheView) -> None:
         """Rows with several new tokens go to the wide kernel, rows with one to the split
-        kernel.  The number of splits along the keys is a fixed function of the batch's shape
-        (rows and groups): enough CTAs to fill the GPU's 148 SMs twice."""
+        kernel, whose number of splits along the keys comes from :func:`decode_splits`."""
         H, G, hd = self.n_heads, self.n_kv_heads, self.head_dim
         common = (q, cache.pages, cache.block_table, cache.page_size, batch.row_start,
                   batch.row_pos0, out)
@@ -89,11 +102,9 @@ class GQAttention(Mixer):
             ops.attention_mma(*common, batch.multi_rows, batch.n_multi, batch.max_new_multi,
                               H, G, hd, self.scale, self.window, split=False)
         if batch.n_single:
-            # a function of the batch's shape alone (not of the contexts, which the kernel
-            # reads on the device and divides evenly over the splits), so that a captured
-            # decode step can be replayed as the contexts grow
-            ctas = batch.n_single * G * (-(-(H // G) // 16))
-            n_splits = max(1, min(296 // ctas, 32))
+            n_splits = decode_splits(batch.n_single * G * (-(-(H // G) // 16)),
+                                     batch.context_bucket if self.window is None
+                                     else min(batch.context_bucket, self.window + 64))
             scratch = None
             if n_splits > 1:
                 scratch = torch.empty(ops.attention_mma_scratch_floats(q.shape[0], H, hd, n_splits),
