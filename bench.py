@@ -179,10 +179,11 @@ def time_decode_device(llm, cfg, batch: int, context: int, steps: int, warmup: i
                                                         prompts[start:start + 2])])
     nxt = random_prompts(warmup + steps, batch, cfg.vocab_size, seed=99)
     out = torch.empty(batch, dtype=torch.int32, device=runner.device)
+    scratch = torch.zeros(ops.argmax_scratch_bytes(batch), dtype=torch.uint8, device=runner.device)
 
     def one(k):
         logits = runner.step([RowInput(rid, [nxt[k][i]], [0]) for i, rid in enumerate(ids)])
-        ops.sample(logits, out)
+        ops.argmax(logits, out, scratch, batch)   # greedy choice, as LLM.step does
 
     for k in range(warmup):
         one(k)

@@ -13,6 +13,8 @@
 
 namespace sllm {
 
+// grid (tokens, blocks of heads); a block of 256 threads takes as many heads as fit, one thread
+// per rotated pair (for v heads: per copied pair).
 template <typename T>
 __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
                                      const int* __restrict__ token_row,
@@ -20,52 +22,44 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
                                      const float* __restrict__ sin_t, T* __restrict__ pages,
                                      const int* __restrict__ block_table, int table_stride,
                                      int page_size, int H, int G, int hd, int rotate,
-                                     int interleaved, int write) {
+                                     int interleaved, int write, int heads_per_block) {
     pdl_trigger();
     const int64_t n = blockIdx.x;
     const int half = hd >> 1;
+    const int local = threadIdx.x / half, j = threadIdx.x - local * half;
+    const int head = blockIdx.y * heads_per_block + local;
+    if (local >= heads_per_block || head >= H + 2 * G) return;
+    if (head >= H && !write) return;
     const int pos = positions[n];
-    T* row = qkv + n * (int64_t)(H + 2 * G) * hd;
-    T* page_base = nullptr;
-    int off = 0;
-    if (write) {
-        const int page = block_table[(int64_t)token_row[n] * table_stride + pos / page_size];
-        off = pos % page_size;
-        page_base = pages + (int64_t)page * 2 * G * page_size * hd;
+    T* h = qkv + n * (int64_t)(H + 2 * G) * hd + (int64_t)head * hd;
+    const int i0 = interleaved ? 2 * j : j;
+    const int i1 = interleaved ? 2 * j + 1 : j + half;
+    float r0 = to_float(h[i0]), r1 = to_float(h[i1]);
+    if (rotate && head < H + G) {
+        const float cj = cos_t[(int64_t)pos * half + j], sj = sin_t[(int64_t)pos * half + j];
+        const float x0 = r0, x1 = r1;
+        r0 = x0 * cj - x1 * sj;
+        r1 = x0 * sj + x1 * cj;
     }
-    const float* c = cos_t + (int64_t)pos * half;
-    const float* s = sin_t + (int64_t)pos * half;
-    const int n_rot = (H + G) * half;
-    for (int idx = threadIdx.x; idx < n_rot; idx += blockDim.x) {
-        const int head = idx / half, j = idx - head * half;
-        const int i0 = interleaved ? 2 * j : j;
-        const int i1 = interleaved ? 2 * j + 1 : j + half;
-        T* h = row + (int64_t)head * hd;
-        const float x0 = to_float(h[i0]), x1 = to_float(h[i1]);
-        float r0 = x0, r1 = x1;
+    if (head < H) {
         if (rotate) {
-            const float cj = c[j], sj = s[j];
-            r0 = x0 * cj - x1 * sj;
-            r1 = x0 * sj + x1 * cj;
+            h[i0] = from_float<T>(r0);
+            h[i1] = from_float<T>(r1);
         }
-        if (head < H) {
-            if (rotate) {
-                h[i0] = from_float<T>(r0);
-                h[i1] = from_float<T>(r1);
-            }
-        } else if (write) {
-            T* dst = page_base + ((int64_t)(head - H) * page_size + off) * hd;
-            dst[i0] = from_float<T>(r0);
-            dst[i1] = from_float<T>(r1);
-        }
+        return;
     }
-    if (write) {
-        const T* v = row + (int64_t)(H + G) * hd;
-        T* vbase = page_base + (int64_t)G * page_size * hd;
-        for (int idx = threadIdx.x; idx < G * hd; idx += blockDim.x) {
-            const int g = idx / hd, i = idx - g * hd;
-            vbase[((int64_t)g * page_size + off) * hd + i] = v[idx];
-        }
+    const int page = block_table[(int64_t)token_row[n] * table_stride + pos / page_size];
+    const int off = pos % page_size;
+    const bool is_v = head >= H + G;
+    const int g = head - H - (is_v ? G : 0);
+    T* dst = pages + (((int64_t)page * 2 + (is_v ? 1 : 0)) * G + g) * page_size * hd +
+             (int64_t)off * hd;
+    if (is_v) {   // v is copied as it is
+        dst[i0] = h[i0];
+        dst[i1] = h[i1];
+    } else {
+        dst[i0] = from_float<T>(r0);
+        dst[i1] = from_float<T>(r1);
     }
 }
 
@@ -81,16 +75,21 @@ SLLM_EXPORT int sllm_rope_kv_write(void* qkv, const int* positions, const int* t
                                    int interleaved, int write, int dtype, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (H <= 0 || G <= 0 || hd <= 0 || (hd & 1) || page_size <= 0) return (int)cudaErrorInvalidValue;
-    int threads = 32;
-    while (threads < 256 && threads < (H + G) * (hd / 2)) threads <<= 1;
+    if (hd / 2 > 256) return (int)cudaErrorInvalidValue;
+    const int threads = 256;
+    const int heads_per_block = threads / (hd / 2);
+    const int n_heads = write ? H + 2 * G : H;
+    dim3 grid(n_tokens, (n_heads + heads_per_block - 1) / heads_per_block);
+    if (grid.y > 65535) return (int)cudaErrorInvalidValue;
     if (dtype == 0)
-        rope_kv_write_kernel<float><<<n_tokens, threads, 0, stream>>>(
+        rope_kv_write_kernel<float><<<grid, threads, 0, stream>>>(
             (float*)qkv, positions, token_row, cos_t, sin_t, (float*)pages, block_table,
-            table_stride, page_size, H, G, hd, rotate, interleaved, write);
+            table_stride, page_size, H, G, hd, rotate, interleaved, write, heads_per_block);
     else if (dtype == 1)
-        rope_kv_write_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(
+        rope_kv_write_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(
             (__nv_bfloat16*)qkv, positions, token_row, cos_t, sin_t, (__nv_bfloat16*)pages,
-            block_table, table_stride, page_size, H, G, hd, rotate, interleaved, write);
+            block_table, table_stride, page_size, H, G, hd, rotate, interleaved, write,
+            heads_per_block);
     else
         return (int)cudaErrorInvalidValue;
     SLLM_LAUNCH_CHECK();

@@ -196,9 +196,63 @@ sample_kernel(const float* __restrict__ logits, int64_t ld, int V,
     }
 }
 
+// Greedy choice for many rows at once: grid (ARGMAX_CHUNKS, rows).  Each block finds the
+// argmax of its slice of the row; the block that finishes last for a row (a ticket from an
+// atomic counter, no waiting) combines the slices.  `partial` holds ARGMAX_CHUNKS (value,
+// index) pairs per row; `tickets` holds one counter per row, zero before the first call and
+// reset to zero by the combining block.
+constexpr int ARGMAX_CHUNKS = 32, ARGMAX_THREADS = 256;
+
+__global__ void __launch_bounds__(ARGMAX_THREADS)
+argmax_kernel(const float* __restrict__ logits, int64_t ld, int V, ArgMax* __restrict__ partial,
+              unsigned* __restrict__ tickets, int* __restrict__ out) {
+    __shared__ ArgMax ascratch[33];
+    __shared__ bool last;
+    const int row = blockIdx.y, chunk = blockIdx.x, tid = threadIdx.x;
+    const float* z = logits + (int64_t)row * ld;
+    const int per = (V + ARGMAX_CHUNKS - 1) / ARGMAX_CHUNKS;
+    const int begin = min(V, chunk * per), end = min(V, begin + per);
+    ArgMax best{0.f, -1};
+    for (int i = begin + tid; i < end; i += ARGMAX_THREADS) best = better(best, ArgMax{z[i], i});
+    best = block_argmax(best, ascratch);
+    if (tid == 0) {
+        partial[row * ARGMAX_CHUNKS + chunk] = best;
+        __threadfence();
+        last = atomicAdd(&tickets[row], 1u) == ARGMAX_CHUNKS - 1;
+    }
+    __syncthreads();
+    if (!last) return;
+    __threadfence();
+    ArgMax b = tid < ARGMAX_CHUNKS ? partial[row * ARGMAX_CHUNKS + tid] : ArgMax{0.f, -1};
+    b = block_argmax(b, ascratch);
+    if (tid == 0) {
+        out[row] = b.i;
+        tickets[row] = 0u;
+    }
+}
+
 }  // namespace sllm
 
 using namespace sllm;
+
+// Bytes of scratch sllm_argmax needs for n_rows rows (partial results and tickets).  The
+// tickets (the last 4 * n_rows bytes) must be zero before the first call.
+SLLM_EXPORT int64_t sllm_argmax_scratch_bytes(int n_rows) {
+    return (int64_t)n_rows * (ARGMAX_CHUNKS * (int64_t)sizeof(ArgMax) + 4);
+}
+
+// out[r] = index of the first maximum of logits[r, 0..V).
+SLLM_EXPORT int sllm_argmax(const float* logits, int64_t ld, int n_rows, int V, void* scratch,
+                            int* out, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (V <= 0 || ld < V || n_rows > 65535 || !scratch) return (int)cudaErrorInvalidValue;
+    ArgMax* partial = (ArgMax*)scratch;
+    unsigned* tickets = (unsigned*)((char*)scratch + (int64_t)n_rows * ARGMAX_CHUNKS * sizeof(ArgMax));
+    argmax_kernel<<<dim3(ARGMAX_CHUNKS, n_rows), ARGMAX_THREADS, 0, stream>>>(logits, ld, V, partial,
+                                                                              tickets, out);
+    SLLM_LAUNCH_CHECK();
+    return 0;
+}
 
 // logits: [n_rows, ld] 32-bit, V columns used.  temperature == nullptr (or an entry 0) is
 // greedy.  top_p / seed / counter / logprob_out / probs_out may be nullptr.

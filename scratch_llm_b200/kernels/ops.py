@@ -365,6 +365,30 @@ def attention_mma_scratch_floats(n_tokens: int, n_heads: int, head_dim: int, n_s
 
 # --------------------------------------------------------------------------------- sampling
 
+def argmax_scratch_bytes(n_rows: int) -> int:
+    lib = _core("sllm_sampling")
+    lib.sllm_argmax_scratch_bytes.restype = c_int64
+    return int(lib.sllm_argmax_scratch_bytes(c_int(n_rows)))
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor, scratch: torch.Tensor, rows_capacity: int
+           ) -> torch.Tensor:
+    """out[r] = first maximum of logits[r] (32-bit, [n, V]), many blocks per row.  ``scratch``:
+    uint8 of ``argmax_scratch_bytes(rows_capacity)``, zero-filled once; its layout depends on
+    ``rows_capacity``, which must be the same on every call with this scratch."""
+    _need(logits, torch.float32, "logits", contiguous=False)
+    _need(out, torch.int32, "out")
+    _need(scratch, torch.uint8, "scratch")
+    n, v = logits.shape
+    if logits.stride(1) != 1 or out.numel() != n or n != rows_capacity \
+            or scratch.numel() < argmax_scratch_bytes(rows_capacity):
+        raise KernelError("argmax shapes")
+    _check(_core("sllm_sampling").sllm_argmax(
+        _ptr(logits), c_int64(logits.stride(0)), c_int(n), c_int(v), _ptr(scratch), _ptr(out),
+        _stream()), "argmax")
+    return out
+
+
 def sample(logits: torch.Tensor, out: torch.Tensor, temperature: torch.Tensor | None = None,
            top_p: torch.Tensor | None = None, seed: torch.Tensor | None = None,
            counter: torch.Tensor | None = None, logprob_out: torch.Tensor | None = None,

@@ -22,6 +22,7 @@ class Sampler:
     def __init__(self, device: torch.device) -> None:
         self.device = device
         self.bytes_read = 0   # device-to-host bytes so far
+        self._argmax_scratch: dict[int, torch.Tensor] = {}
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams],
                seeds: Sequence[int], counters: Sequence[int], want_logprobs: bool = False
@@ -31,7 +32,14 @@ class Sampler:
         n = logits.shape[0]
         out = torch.empty(n, dtype=torch.int32, device=self.device)
         lp = torch.empty(n, dtype=torch.float32, device=self.device) if want_logprobs else None
-        if all(p.temperature == 0.0 for p in params):
+        if all(p.temperature == 0.0 for p in params) and lp is None:
+            scratch = self._argmax_scratch.get(n)
+            if scratch is None:   # one zero-filled scratch per batch size, kept
+                scratch = torch.zeros(ops.argmax_scratch_bytes(n), dtype=torch.uint8,
+                                      device=self.device)
+                self._argmax_scratch[n] = scratch
+            ops.argmax(logits, out, scratch, n)
+        elif all(p.temperature == 0.0 for p in params):
             ops.sample(logits, out, logprob_out=lp)
         else:
             f = np.array([[p.temperature for p in params], [p.top_p for p in params]],

@@ -302,6 +302,20 @@ def test_sampling_greedy_ties_and_logprob(ops):
                                rtol=1e-5, atol=1e-5)
 
 
+@pytest.mark.parametrize("n, V", [(1, 7), (5, 331), (8, 128256), (64, 50000)])
+def test_argmax_many_blocks_per_row(ops, n, V):
+    logits = rand(n, V, seed=3)
+    logits[0, V - 1] = logits[0, V // 3] = 50.0      # a tie: the first maximum wins
+    scratch = torch.zeros(ops.argmax_scratch_bytes(n), dtype=torch.uint8, device="cuda")
+    out = torch.empty(n, dtype=torch.int32, device="cuda")
+    want = logits.argmax(-1)
+    want[0] = V // 3
+    for _ in range(3):   # the scratch resets itself
+        out.fill_(-1)
+        ops.argmax(logits.cuda(), out, scratch, n)
+        assert out.cpu().tolist() == want.tolist()
+
+
 @pytest.mark.parametrize("V", [331, 50000])
 def test_sampling_distribution_and_draws(ops, V):
     logits = rand(3, V, seed=6, scale=2.0)
