@@ -18,7 +18,9 @@
 //
 // Roles in a CTA of 192 threads: warp 0 = TMA producer, warp 1 = MMA issuer and owner of the
 // tensor-memory allocation, warps 2-5 = epilogue (warp w reads the lanes 32*(w%4)..+31 it may
-// access).  One output tile of 128 x 256 per CTA, 4 pipeline stages of 48 KB.
+// access).  Persistent CTAs (one per SM) walk output tiles of 128 x 256 through 4 pipeline
+// stages of 48 KB; the accumulator is double-buffered in tensor memory so that the epilogue of
+// one tile overlaps the products of the next.
 //
 // Every mbarrier wait is bounded: after WAIT_LIMIT polls a thread records an error code in
 // `g_gemm_error`, stops waiting, and the CTA still reaches its end, where the tensor memory is
@@ -115,12 +117,39 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// Grid (tiles along M, tiles along N).  SWIGLU: W = [gate rows; up rows] (n_half each); tile
-// column block j covers features j*128..+127 and Y has n_half columns.
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// Writes 32 consecutive outputs of one row; `n_valid` of them exist.
+__device__ __forceinline__ void store_row32(bf16* dst, const float (&o)[32], int n_valid,
+                                            bool aligned) {
+    if (n_valid >= 32 && aligned) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            uint4 q;
+            q.x = pack2(o[8 * i + 0], o[8 * i + 1]);
+            q.y = pack2(o[8 * i + 2], o[8 * i + 3]);
+            q.z = pack2(o[8 * i + 4], o[8 * i + 5]);
+            q.w = pack2(o[8 * i + 6], o[8 * i + 7]);
+            reinterpret_cast<uint4*>(dst)[i] = q;
+        }
+    } else {
+        for (int i = 0; i < 32 && i < n_valid; ++i) dst[i] = __float2bfloat16_rn(o[i]);
+    }
+}
+
+// Persistent: gridDim.x CTAs walk the output tiles (token blocks fastest, so that consecutive
+// tiles share a tile of W, which then streams from HBM once while the smaller activations are
+// re-read from L2).  The accumulator is double-buffered in tensor memory (2 x 256 columns):
+// the epilogue warps drain tile i while the MMA warp already multiplies tile i + 1.
+// SWIGLU: W = [gate rows; up rows] (n_half each); column block j covers features j*128..+127
+// and Y has n_half columns.
 template <bool SWIGLU>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-               bf16* __restrict__ Y, int M, int N, int K, int64_t ldy, int n_half) {
+               bf16* __restrict__ Y, int M, int N, int K, int64_t ldy, int n_half, int tiles_m,
+               int tiles_n) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(
         ((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -128,31 +157,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     unsigned char* b_stage = smem + STAGES * A_BYTES;       // STAGES x 32 KB
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
     uint64_t* empty = full + STAGES;
-    uint64_t* acc_ready = empty + STAGES;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_ready + 1);
+    uint64_t* acc_full = empty + STAGES;     // [2]: the MMA warp has finished a tile
+    uint64_t* acc_empty = acc_full + 2;      // [2]: the four epilogue warps have drained it
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // consecutive CTAs share a tile of W and walk the token blocks, so W streams from HBM once
-    // while the (smaller) activations are re-read from L2
-    const int m0 = blockIdx.x * TM;
-    const int n_blk = blockIdx.y;
-    // rows of W this tile multiplies: two boxes of 128 rows
-    const int w_row0 = SWIGLU ? n_blk * 128 : n_blk * TN;
-    const int w_row1 = SWIGLU ? n_half + n_blk * 128 : n_blk * TN + 128;
     const int k_blocks = (K + TK - 1) / TK;
+    const int total_tiles = tiles_m * tiles_n;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], 1);
         }
-        mbar_init(acc_ready, 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], 4);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
-                     ::"r"(smem_u32(tmem_slot)), "r"(256u) : "memory");
+                     ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
     }
     tc_fence_before();
@@ -162,41 +189,62 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 
     if (warp == 0) {
         if (lane == 0) {
-            for (int kb = 0; kb < k_blocks; ++kb) {
-                const int s = kb % STAGES;
-                if (!mbar_wait(&empty[s], ((kb / STAGES) & 1) ^ 1, 1)) break;
-                mbar_expect_tx(&full[s], STAGE_BYTES);
-                tma_load_2d(a_stage + s * A_BYTES, &map_x, &full[s], kb * TK, m0);
-                tma_load_2d(b_stage + s * B_BYTES, &map_w, &full[s], kb * TK, w_row0);
-                tma_load_2d(b_stage + s * B_BYTES + B_BYTES / 2, &map_w, &full[s], kb * TK, w_row1);
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const int m0 = (tile % tiles_m) * TM, n_blk = tile / tiles_m;
+                const int w_row0 = SWIGLU ? n_blk * 128 : n_blk * TN;
+                const int w_row1 = SWIGLU ? n_half + n_blk * 128 : n_blk * TN + 128;
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    ok = mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1, 1);
+                    if (!ok) break;
+                    mbar_expect_tx(&full[s], STAGE_BYTES);
+                    tma_load_2d(a_stage + s * A_BYTES, &map_x, &full[s], kb * TK, m0);
+                    tma_load_2d(b_stage + s * B_BYTES, &map_w, &full[s], kb * TK, w_row0);
+                    tma_load_2d(b_stage + s * B_BYTES + B_BYTES / 2, &map_w, &full[s], kb * TK,
+                                w_row1);
+                }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TN >> 3) << 17) |
                                    ((uint32_t)(TM >> 4) << 24);
+            uint32_t it = 0, local = 0;
             bool ok = true;
-            for (int kb = 0; kb < k_blocks && ok; ++kb) {
-                const int s = kb % STAGES;
-                ok = mbar_wait(&full[s], (kb / STAGES) & 1, 2);
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
+                const uint32_t buf = local & 1;
+                ok = mbar_wait(&acc_empty[buf], ((local >> 1) & 1) ^ 1, 4);
                 if (!ok) break;
                 tc_fence_after();
-                const uint64_t da = make_smem_desc(smem_u32(a_stage + s * A_BYTES));
-                const uint64_t db = make_smem_desc(smem_u32(b_stage + s * B_BYTES));
+                const uint32_t tmem_d = tmem_base + buf * TN;
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    ok = mbar_wait(&full[s], (it / STAGES) & 1, 2);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint64_t da = make_smem_desc(smem_u32(a_stage + s * A_BYTES));
+                    const uint64_t db = make_smem_desc(smem_u32(b_stage + s * B_BYTES));
 #pragma unroll
-                for (int k = 0; k < TK / 16; ++k)   // 32 bytes = 2 units of 16 bytes per K step
-                    umma_bf16(tmem_base, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
-                umma_commit(&empty[s]);   // the stage is free once these products have read it
+                    for (int k = 0; k < TK / 16; ++k)   // 32 bytes = 2 units of 16 bytes per K step
+                        umma_bf16(tmem_d, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+                    umma_commit(&empty[s]);   // the stage is free once these products have read it
+                }
+                umma_commit(&acc_full[buf]);  // arrives when every product of the tile is done
             }
-            umma_commit(acc_ready);       // arrives when every product above has finished
         }
     } else {
         const int quad = warp & 3;        // the 32 tensor-memory lanes this warp may read
-        const int row = m0 + quad * 32 + lane;
-        const bool got = mbar_wait(acc_ready, 0, 3);
-        tc_fence_after();
-        if (got) {
-            const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+        uint32_t local = 0;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
+            const uint32_t buf = local & 1;
+            const int m0 = (tile % tiles_m) * TM, n_blk = tile / tiles_m;
+            const int row = m0 + quad * 32 + lane;
+            if (!mbar_wait(&acc_full[buf], (local >> 1) & 1, 3)) break;
+            tc_fence_after();
+            const uint32_t lane_addr = tmem_base + buf * TN + ((uint32_t)(quad * 32) << 16);
+            const bool aligned = (ldy & 7) == 0;
             if (!SWIGLU) {
                 const int n0 = n_blk * TN;
 #pragma unroll 1
@@ -206,21 +254,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                     tmem_ld_wait();
                     const int col = n0 + c * 32;
                     if (row < M && col < N) {
-                        bf16* dst = Y + (int64_t)row * ldy + col;
-                        if (col + 32 <= N && ((ldy & 7) == 0)) {
+                        float o[32];
 #pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                uint4 o;
-                                o.x = pack2(__uint_as_float(v[8 * i + 0]), __uint_as_float(v[8 * i + 1]));
-                                o.y = pack2(__uint_as_float(v[8 * i + 2]), __uint_as_float(v[8 * i + 3]));
-                                o.z = pack2(__uint_as_float(v[8 * i + 4]), __uint_as_float(v[8 * i + 5]));
-                                o.w = pack2(__uint_as_float(v[8 * i + 6]), __uint_as_float(v[8 * i + 7]));
-                                reinterpret_cast<uint4*>(dst)[i] = o;
-                            }
-                        } else {
-                            for (int i = 0; i < 32 && col + i < N; ++i)
-                                dst[i] = __float2bfloat16_rn(__uint_as_float(v[i]));
-                        }
+                        for (int i = 0; i < 32; ++i) o[i] = __uint_as_float(v[i]);
+                        store_row32(Y + (int64_t)row * ldy + col, o, N - col, aligned);
                     }
                 }
             } else {
@@ -233,32 +270,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                     tmem_ld_wait();
                     const int col = f0 + c * 32;
                     if (row < M && col < n_half) {
-                        bf16* dst = Y + (int64_t)row * ldy + col;
                         float o[32];
 #pragma unroll
                         for (int i = 0; i < 32; ++i) {
                             // gate and up are rounded to bfloat16 first, as the unfused path does
                             const float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(gv[i])));
                             const float u = __bfloat162float(__float2bfloat16_rn(__uint_as_float(uv[i])));
-                            o[i] = g / (1.0f + expf(-g)) * u;
+                            o[i] = g / (1.0f + __expf(-g)) * u;
                         }
-                        if (col + 32 <= n_half && ((ldy & 7) == 0)) {
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                uint4 q;
-                                q.x = pack2(o[8 * i + 0], o[8 * i + 1]);
-                                q.y = pack2(o[8 * i + 2], o[8 * i + 3]);
-                                q.z = pack2(o[8 * i + 4], o[8 * i + 5]);
-                                q.w = pack2(o[8 * i + 6], o[8 * i + 7]);
-                                reinterpret_cast<uint4*>(dst)[i] = q;
-                            }
-                        } else {
-                            for (int i = 0; i < 32 && col + i < n_half; ++i)
-                                dst[i] = __float2bfloat16_rn(o[i]);
-                        }
+                        store_row32(Y + (int64_t)row * ldy + col, o, n_half - col, aligned);
                     }
                 }
             }
+            // this warp has read its part of the buffer: hand it back to the MMA warp
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);
         }
     }
     tc_fence_before();
@@ -266,7 +293,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n"
-                     ::"r"(tmem_base), "r"(256u) : "memory");
+                     ::"r"(tmem_base), "r"(512u) : "memory");
     }
 }
 
@@ -305,7 +332,8 @@ static bool make_map(CUtensorMap* map, const void* base, int rows, int K, int64_
 using namespace sllm;
 
 // The first error a bounded wait recorded since the last call (0 = none): 1 = producer waiting
-// for a free stage, 2 = MMA issuer waiting for data, 3 = epilogue waiting for the accumulator.
+// for a free stage, 2 = MMA issuer waiting for data, 3 = epilogue waiting for the accumulator,
+// 4 = MMA issuer waiting for a drained accumulator buffer.
 // Synchronises the device.
 SLLM_EXPORT int sllm_gemm_tc_error() {
     int code = 0, zero = 0;
@@ -329,21 +357,30 @@ SLLM_EXPORT int sllm_gemm_tc(const void* X, const void* W, void* Y, int M, int N
         return (int)cudaErrorNotSupported;
     const int n_half = N / 2;
     const int tiles_n = swiglu ? (n_half + 127) / 128 : (N + TN - 1) / TN;
-    dim3 grid((M + TM - 1) / TM, tiles_n);
-    if (grid.y > 65535) return (int)cudaErrorInvalidValue;
+    const int tiles_m = (M + TM - 1) / TM;
+    if ((int64_t)tiles_m * tiles_n > 0x7fffffff) return (int)cudaErrorInvalidValue;
+    static int n_sm = 0;
+    if (!n_sm) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+            return (int)cudaErrorUnknown;
+    }
+    const int total = tiles_m * tiles_n;
+    dim3 grid(total < n_sm ? total : n_sm);
     cudaError_t e;
     if (swiglu) {
         e = cudaFuncSetAttribute(gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)TC_SMEM);
         if (e != cudaSuccess) return (int)e;
         gemm_tc_kernel<true><<<grid, TC_THREADS, TC_SMEM, stream>>>(map_x, map_w, (bf16*)Y, M, N, K,
-                                                                  ldy, n_half);
+                                                                  ldy, n_half, tiles_m, tiles_n);
     } else {
         e = cudaFuncSetAttribute(gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)TC_SMEM);
         if (e != cudaSuccess) return (int)e;
         gemm_tc_kernel<false><<<grid, TC_THREADS, TC_SMEM, stream>>>(map_x, map_w, (bf16*)Y, M, N, K,
-                                                                   ldy, n_half);
+                                                                   ldy, n_half, tiles_m, tiles_n);
     }
     SLLM_LAUNCH_CHECK();
     return 0;

@@ -16,6 +16,10 @@ from ..kernels import ops
 
 #: up to this many tokens the streaming small-batch kernel runs instead of the library product
 SMALL_BATCH = 8
+#: from this many tokens on, gate/up + SwiGLU run on the fused tcgen05 kernel (below it the
+#: 128-token tiles leave too many of the 148 SMs idle and the library product plus a separate
+#: activation kernel is faster)
+FUSED_GEMM_MIN_TOKENS = 768
 
 
 class Linear:
@@ -47,7 +51,12 @@ class Linear:
         w = self.weight
         half = self.out_features // 2
         out = torch.empty((x.shape[0], half), dtype=x.dtype, device=x.device)
-        if (w.dtype == torch.bfloat16 and x.shape[0] <= SMALL_BATCH and self.in_features % 8 == 0
-                and x.stride(0) % 8 == 0):
+        fits = (w.dtype == torch.bfloat16 and self.in_features % 8 == 0
+                and x.stride(0) % 8 == 0)
+        if fits and x.shape[0] <= SMALL_BATCH:
             return ops.gemv_mma(x, w, out, swiglu=True)
+        if fits and x.shape[0] >= FUSED_GEMM_MIN_TOKENS and half % 8 == 0:
+            # tcgen05 kernel with the activation in its epilogue: the [tokens, 2F] intermediate
+            # is never written
+            return ops.gemm_tc(x, w, out, swiglu=True)
         return ops.swiglu(self(x), out)
