@@ -211,8 +211,10 @@ __global__ void __launch_bounds__(THREADS, SPLIT ? 3 : 2) attn_mma_kernel(const 
         qpos[h] = pos0 + (qvalid[h] ? p / GS : 0);
     }
     // tiles that lie wholly before the warp's first query need no mask
-    const bool warp_full = q0 + wq + 15 < n_packed && a.window <= 0;
-    const int warp_first_pos = pos0 + (q0 + wq) / GS;
+    // (rows past the last packed query hold zeros, see the query load above: whatever they
+    // compute stays finite and is never stored, so they do not force the masked path)
+    const bool warp_full = a.window <= 0;
+    const int warp_first_pos = pos0 + min(q0 + wq, n_packed - 1) / GS;
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
     float o[DTILES][4];
 #pragma unroll
@@ -295,10 +297,14 @@ __global__ void __launch_bounds__(THREADS, SPLIT ? 3 : 2) attn_mma_kernel(const 
             pa[nt >> 1][(nt & 1) * 2 + 0] = pack_bf16(p[0], p[1]);
             pa[nt >> 1][(nt & 1) * 2 + 1] = pack_bf16(p[2], p[3]);
         }
+        // the running maximum settles after the first tiles; skip the rescaling when no row
+        // of the warp moved
+        if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {
 #pragma unroll
-        for (int dn = 0; dn < DTILES; ++dn) {
-            o[dn][0] *= corr[0]; o[dn][1] *= corr[0];
-            o[dn][2] *= corr[1]; o[dn][3] *= corr[1];
+            for (int dn = 0; dn < DTILES; ++dn) {
+                o[dn][0] *= corr[0]; o[dn][1] *= corr[0];
+                o[dn][2] *= corr[1]; o[dn][3] *= corr[1];
+            }
         }
         // ---- o += p v
 #pragma unroll

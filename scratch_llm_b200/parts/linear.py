@@ -38,7 +38,10 @@ class Linear:
             out = torch.empty((x.shape[0], self.out_features), dtype=torch.float32,
                               device=x.device)
             return ops.gemm_simt(x, w, out)
-        if x.shape[0] <= SMALL_BATCH and self.in_features % 8 == 0 and x.stride(0) % 8 == 0:
+        # every CTA of the streaming kernel re-reads all activations, which costs as much as the
+        # weights once the output is very wide and several tokens are in flight
+        streams = x.shape[0] <= SMALL_BATCH and (x.shape[0] <= 2 or self.out_features <= 65536)
+        if streams and self.in_features % 8 == 0 and x.stride(0) % 8 == 0:
             out = torch.empty((x.shape[0], self.out_features), dtype=out_dtype, device=x.device)
             return ops.gemv_mma(x, w, out)
         if out_dtype == torch.float32:

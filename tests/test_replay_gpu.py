@@ -98,3 +98,27 @@ def test_cutting_does_not_change_logits_beyond_rounding(model_dirs, expected):
     for key in a:
         torch.testing.assert_close(a[key], b[key], rtol=1e-5, atol=2e-6)
         torch.testing.assert_close(a[key], c[key], rtol=1e-5, atol=2e-6)
+
+
+def test_long_prompt_takes_the_fused_tensor_core_path(tmp_path):
+    """A prompt of more than 768 tokens in one step runs gate/up + SwiGLU on the tcgen05 kernel
+    (shorter ones use other kernels); its logits still match the plain implementation."""
+    from scratch_llm_b200.config import config_from_dict
+    from scratch_llm_b200.kernels import ops
+    from scratch_llm_b200.parts import linear
+    from scratch_llm_b200.weights import write_random_model
+    raw = {**CONFIGS["C"], "max_position_embeddings": 1100}
+    d = write_random_model(config_from_dict(raw), tmp_path / "long", 5)
+    cfg, w = P.read_model_dir(d)
+    w = {k: v.to(torch.bfloat16).float() for k, v in w.items()}
+    reqs = T.make_requests(cfg["vocab_size"], [1000], seed=4)
+    assert 1000 >= linear.FUSED_GEMM_MIN_TOKENS
+    want = {rid: P.forward(cfg, w, toks) for rid, toks in reqs.items()}
+    steps = T.whole(reqs)
+    for s in steps:   # logits at a few places only: the first, one in the middle, the last 40
+        s["entries"][0]["want"] = [0, 500] + list(range(960, 1000))
+    runner = make_runner(d, "bfloat16", 16, 1024, max_requests=1)
+    with torch.no_grad():
+        got = T.run_in_process(runner, steps)
+    assert ops.gemm_tc_error() == 0
+    compare(got, want, "bfloat16")
