@@ -26,6 +26,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Hashable, Sequence
 
+import numpy as np
 import torch
 
 from ..parts.base import KVSpec, StateSpec
@@ -47,6 +48,9 @@ class RequestCache:
     n_tokens: int = 0                      # tokens whose keys are cached (committed)
     n_reserved: int = 0                    # tokens that pages have been reserved for
     tables: list[list[int]] = field(default_factory=list)  # per group: logical -> physical, -1 freed
+    # the same tables as int32 arrays (filled with -1 beyond the pages held), kept in step with
+    # ``tables`` so that a step's descriptor copies rows instead of converting lists
+    tables_np: list = field(default_factory=list)
 
 
 class CacheManager:
@@ -101,7 +105,8 @@ class CacheManager:
         if not self._free_slots:
             return None
         slot = self._free_slots.pop()
-        rc = RequestCache(request_id, slot, tables=[[] for _ in self.groups])
+        rc = RequestCache(request_id, slot, tables=[[] for _ in self.groups],
+                          tables_np=[np.full(16, -1, dtype=np.int32) for _ in self.groups])
         self.requests[request_id] = rc
         for state in self.states:
             if state is not None:
@@ -118,12 +123,22 @@ class CacheManager:
         """Hold pages for the next ``n_new`` tokens in every group, or change nothing and
         return False if some group has too few free pages."""
         rc = self.requests[request_id]
+        if rc.n_tokens + n_new <= rc.n_reserved and all(
+                len(t) * self.page_size >= rc.n_tokens + n_new for t in rc.tables):
+            return True   # an earlier call already holds the pages
         need = self.pages_needed(request_id, n_new)
         if any(n > g.pool.n_free for n, g in zip(need, self.groups)):
             return False
-        for n, g, table in zip(need, self.groups, rc.tables):
+        for gi, (n, g, table) in enumerate(zip(need, self.groups, rc.tables)):
             got = g.pool.alloc(n, request_id)
             assert got is not None
+            if n:
+                arr = rc.tables_np[gi]
+                if len(table) + n > arr.size:
+                    grown = np.full(max(2 * arr.size, len(table) + n), -1, dtype=np.int32)
+                    grown[:arr.size] = arr
+                    arr = rc.tables_np[gi] = grown
+                arr[len(table):len(table) + n] = got
             table.extend(got)
         rc.n_reserved = max(rc.n_reserved, rc.n_tokens + n_new)
         return True
@@ -137,7 +152,7 @@ class CacheManager:
             raise ValueError(f"request {request_id!r}: {n_new} tokens stored but pages were "
                              f"reserved for {rc.n_reserved - rc.n_tokens}")
         rc.n_tokens += n_new
-        for g, table in zip(self.groups, rc.tables):
+        for gi, (g, table) in enumerate(zip(self.groups, rc.tables)):
             if g.spec.window is None:
                 continue
             last_dead = rc.n_tokens - g.spec.window  # positions <= last_dead are never read again
@@ -147,6 +162,7 @@ class CacheManager:
                 g.pool.free(dead, request_id)
                 for i in range(min(n_dead_pages, len(table))):
                     table[i] = -1
+                rc.tables_np[gi][:min(n_dead_pages, len(table))] = -1
 
     def release(self, request_id: Hashable) -> None:
         """The request has ended (or is set back): give its pages and its slot back."""
@@ -159,6 +175,11 @@ class CacheManager:
 
     def table_of(self, request_id: Hashable, group: int) -> list[int]:
         return self.requests[request_id].tables[group]
+
+    def table_array(self, request_id: Hashable, group: int) -> np.ndarray:
+        """The block table as an int32 array of exactly the pages' count (a view)."""
+        rc = self.requests[request_id]
+        return rc.tables_np[group][:len(rc.tables[group])]
 
     def entry_pages(self, entry: int) -> tuple[torch.Tensor | None, int | None]:
         """(pages tensor of this entry, its group index)."""

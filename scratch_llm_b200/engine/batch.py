@@ -137,56 +137,68 @@ def build_batch(cache, stager: BatchStager, rows: Sequence[RowInput], vocab_size
     step that replays a captured CUDA graph, every array must keep its size and address)."""
     n_rows = len(rows)
     lens = [len(r.tokens) for r in rows]
-    n_tokens = sum(lens)
-    token_ids = np.empty(n_tokens, dtype=np.int32)
-    positions = np.empty(n_tokens, dtype=np.int32)
-    token_row = np.empty(n_tokens, dtype=np.int32)
-    row_start = np.zeros(n_rows + 1, dtype=np.int32)
-    row_pos0 = np.empty(n_rows, dtype=np.int32)
-    row_slot = np.empty(n_rows, dtype=np.int32)
-    logit_index: list[int] = []
-    seen: set[Hashable] = set()
-    t = 0
-    for i, row in enumerate(rows):
-        n = lens[i]
-        if n < 1:
-            raise ValueError(f"request {row.request_id!r}: a row needs at least one token")
-        if row.request_id in seen:
-            raise ValueError(f"request {row.request_id!r} appears twice in one step")
-        seen.add(row.request_id)
-        rc = cache.requests.get(row.request_id)
+    if n_rows and min(lens) < 1:
+        bad = rows[lens.index(min(lens))]
+        raise ValueError(f"request {bad.request_id!r}: a row needs at least one token")
+    if len({r.request_id for r in rows}) != n_rows:
+        seen: set[Hashable] = set()
+        for r in rows:
+            if r.request_id in seen:
+                raise ValueError(f"request {r.request_id!r} appears twice in one step")
+            seen.add(r.request_id)
+    caches = []
+    for r in rows:
+        rc = cache.requests.get(r.request_id)
         if rc is None:
-            raise KeyError(f"request {row.request_id!r} is not live: admit it first")
-        if rc.n_tokens + n > max_position:
-            raise ValueError(f"request {row.request_id!r}: position {rc.n_tokens + n - 1} "
-                             f"is beyond max_position {max_position}")
-        ids = np.asarray(row.tokens, dtype=np.int64)
-        if ids.min() < 0 or ids.max() >= vocab_size:
-            raise ValueError(f"request {row.request_id!r}: token id out of range "
-                             f"[0, {vocab_size})")
-        token_ids[t:t + n] = ids
-        positions[t:t + n] = np.arange(rc.n_tokens, rc.n_tokens + n)
-        token_row[t:t + n] = i
-        row_pos0[i], row_slot[i] = rc.n_tokens, rc.slot
-        for w in row.want:
-            if not 0 <= w < n:
-                raise ValueError(f"request {row.request_id!r}: wanted place {w} is not "
-                                 f"among its {n} tokens")
-            logit_index.append(t + w)
-        t += n
-        row_start[i + 1] = t
+            raise KeyError(f"request {r.request_id!r} is not live: admit it first")
+        caches.append(rc)
+    n_tokens = sum(lens)
+    # everything below is whole-array work: a decode step has one token per row, and a Python
+    # loop over rows would cost more than the kernels it feeds
+    lens_np = np.asarray(lens, dtype=np.int64)
+    row_pos0 = np.fromiter((rc.n_tokens for rc in caches), dtype=np.int32, count=n_rows)
+    row_slot = np.fromiter((rc.slot for rc in caches), dtype=np.int32, count=n_rows)
+    row_start = np.zeros(n_rows + 1, dtype=np.int32)
+    np.cumsum(lens_np, out=row_start[1:])
+    over = row_pos0.astype(np.int64) + lens_np > max_position
+    if over.any():
+        i = int(np.argmax(over))
+        raise ValueError(f"request {rows[i].request_id!r}: position "
+                         f"{int(row_pos0[i]) + lens[i] - 1} is beyond max_position "
+                         f"{max_position}")
+    if n_tokens == n_rows:
+        flat = np.fromiter((r.tokens[0] for r in rows), dtype=np.int64, count=n_rows)
+    else:
+        flat = np.concatenate([np.asarray(r.tokens, dtype=np.int64) for r in rows])
+    if flat.size and (flat.min() < 0 or flat.max() >= vocab_size):
+        i = int(np.searchsorted(row_start[1:], int(np.argmax((flat < 0) | (flat >= vocab_size))),
+                                side="right"))
+        raise ValueError(f"request {rows[i].request_id!r}: token id out of range "
+                         f"[0, {vocab_size})")
+    token_ids = flat.astype(np.int32)
+    token_row = np.repeat(np.arange(n_rows, dtype=np.int32), lens_np)
+    positions = (np.arange(n_tokens, dtype=np.int32) - row_start[token_row] + row_pos0[token_row])
+    logit_index: list[int] = []
+    for i, row in enumerate(rows):
+        if row.want:
+            n, t = lens[i], int(row_start[i])
+            for w in row.want:
+                if not 0 <= w < n:
+                    raise ValueError(f"request {row.request_id!r}: wanted place {w} is not "
+                                     f"among its {n} tokens")
+                logit_index.append(t + w)
     tables = []
     for g in range(len(cache.groups)):
-        width = max(len(cache.table_of(r.request_id, g)) for r in rows)
+        arrays = [rc.tables_np[g][:len(rc.tables[g])] for rc in caches]
+        width = max(a.size for a in arrays)
         if table_width is not None:
             if width > table_width:
                 raise ValueError(f"a block table of {width} pages exceeds the fixed width "
                                  f"{table_width}")
             width = table_width
         tab = np.full((n_rows, max(width, 1)), -1, dtype=np.int32)
-        for i, r in enumerate(rows):
-            pages = cache.table_of(r.request_id, g)
-            tab[i, :len(pages)] = pages
+        for i, a in enumerate(arrays):
+            tab[i, :a.size] = a
         tables.append(tab)
     li = np.asarray(logit_index, dtype=np.int32)
     single = [i for i, n in enumerate(lens) if n == 1]
@@ -194,13 +206,14 @@ def build_batch(cache, stager: BatchStager, rows: Sequence[RowInput], vocab_size
     dev = stager.upload([token_ids, positions, token_row, row_start, row_pos0, row_slot, li,
                          np.asarray(single, dtype=np.int32), np.asarray(multi, dtype=np.int32),
                          *tables])
+    single_np = np.asarray(single, dtype=np.int32)
+    ctx_single = int(row_pos0[single_np].max()) + 1 if single else 0
     return StepBatch(
         n_tokens=n_tokens, n_rows=n_rows, n_out=len(logit_index), max_new=max(lens),
-        max_context=int(max(p + n for p, n in zip(row_pos0.tolist(), lens))),
+        max_context=int((row_pos0.astype(np.int64) + lens_np).max()),
         token_ids=dev[0], positions=dev[1], token_row=dev[2], row_start=dev[3],
         row_pos0=dev[4], row_slot=dev[5], logit_index=dev[6], single_rows=dev[7],
         multi_rows=dev[8], block_tables=dev[9:], n_single=len(single), n_multi=len(multi),
         max_new_multi=max((lens[i] for i in multi), default=0),
-        max_context_single=max((int(row_pos0[i]) + 1 for i in single), default=0),
-        context_bucket=context_bucket(max((int(row_pos0[i]) + 1 for i in single), default=0)),
+        max_context_single=ctx_single, context_bucket=context_bucket(ctx_single),
         host_row_new=lens, host_row_pos0=row_pos0.tolist())

@@ -44,7 +44,7 @@ class Request:
     params: SamplingParams = field(default_factory=lambda: SamplingParams(temperature=0.0))
 
 
-@dataclass
+@dataclass(eq=False)
 class Sequence_:
     request: Request
     tokens: list[int]                 # prompt + generated so far
@@ -60,7 +60,7 @@ class Sequence_:
         return self.tokens[self.n_prompt:]
 
 
-@dataclass
+@dataclass(eq=False)
 class PlannedRow:
     seq: Sequence_
     start: int        # index of the first token fed (= tokens cached before the step)
@@ -161,9 +161,11 @@ class Scheduler:
         """Decide the next step's batch.  Reserves the pages its rows need."""
         budget = self.max_batch_tokens
         rows: list[PlannedRow] = []
+        planned: set[int] = set()      # id() of the sequences that have a row in this step
+        gone: set[int] = set()         # id() of the sequences set back while planning
         # 1. decoding requests, oldest first; a page shortage sets back the newest request
         for seq in list(self.running):
-            if seq not in self.running:      # set back while serving an older one
+            if id(seq) in gone:        # set back while serving an older one
                 continue
             cached = self._cached(seq)
             if cached != len(seq.tokens) - 1 or budget < 1:
@@ -171,23 +173,26 @@ class Scheduler:
             rid = seq.request.request_id
             while not self.cache.reserve(rid, 1):
                 victim = max(self.running, key=lambda s: s.order)
-                planned = [r for r in rows if r.seq is victim]
-                for r in planned:
-                    rows.remove(r)
-                    budget += r.n
+                if id(victim) in planned:
+                    for r in [r for r in rows if r.seq is victim]:
+                        rows.remove(r)
+                        budget += r.n
+                    planned.discard(id(victim))
                 self._preempt(victim)
+                gone.add(id(victim))
                 if victim is seq:
                     break
             else:
                 rows.append(PlannedRow(seq, cached, 1, True))
+                planned.add(id(seq))
                 budget -= 1
         # 2. prompts in progress, oldest first
         for seq in self.running:
+            if id(seq) in planned or budget < 1:
+                continue
             cached = self._cached(seq)
             rest = len(seq.tokens) - cached
-            if rest <= 1 and any(r.seq is seq for r in rows):
-                continue
-            if rest < 1 or budget < 1 or any(r.seq is seq for r in rows):
+            if rest < 1:
                 continue
             n = min(rest, budget, self.chunk_size or rest)
             m = self._fits(seq, n)
@@ -195,6 +200,7 @@ class Scheduler:
                 self.stats.stalled_portions += 1
                 continue
             rows.append(PlannedRow(seq, cached, m, cached + m == len(seq.tokens)))
+            planned.add(id(seq))
             budget -= m
         # 3. admissions, first come first served, no skipping ahead
         while self.queue and budget >= 1 and self.cache.n_free_slots > 0:

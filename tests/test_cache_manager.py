@@ -121,6 +121,8 @@ def test_random_orders_keep_the_accounting_whole(seed):
         for rid, n in live.items():
             assert m.requests[rid].n_tokens == n
             assert len(m.table_of(rid, 0)) >= -(-n // 4)
+            for g in range(len(m.groups)):   # the array copy of a table never drifts from it
+                assert m.table_array(rid, g).tolist() == m.table_of(rid, g)
     assert refused > 0  # the pool did run out
     for rid in list(live):
         m.release(rid)
