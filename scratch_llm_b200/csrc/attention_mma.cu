@@ -113,6 +113,7 @@ __global__ void __launch_bounds__(THREADS, SPLIT ? 3 : 2) attn_mma_kernel(const 
     bf16* Ks = Qs + M::BQ * LDS;               // NSTAGE stages of [BKV][LDS]
     bf16* Vs = Ks + M::NSTAGE * BKV * LDS;     // NSTAGE stages of [BKV][LDS]
 
+    pdl_wait();
     pdl_trigger();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n_splits = SPLIT ? a.n_splits : 1;
@@ -399,6 +400,7 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o,
                                   const int* __restrict__ row_start,
                                   const int* __restrict__ row_list, bf16* __restrict__ out,
                                   int64_t out_stride, int H) {
+    pdl_wait();
     pdl_trigger();
     const int r = row_list ? row_list[blockIdx.x] : blockIdx.x;
     const int head = blockIdx.y;
@@ -466,9 +468,7 @@ SLLM_EXPORT int sllm_attn_mma(const void* q, int64_t q_stride, const void* pages
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         dim3 grid(((int64_t)max_new * GS + 63) / 64, n_list, G);
-        attn_mma_kernel<false><<<grid, THREADS, smem, stream>>>(a);
-        SLLM_LAUNCH_CHECK();
-        return 0;
+        return (int)sllm_launch_pdl(attn_mma_kernel<false>, grid, dim3(THREADS), smem, stream, a);
     }
     if (n_splits < 1) return (int)cudaErrorInvalidValue;
     if (n_splits > 1) {
@@ -482,13 +482,14 @@ SLLM_EXPORT int sllm_attn_mma(const void* q, int64_t q_stride, const void* pages
                              (int)smem);
     if (e != cudaSuccess) return (int)e;
     dim3 grid((((int64_t)max_new * GS + 15) / 16) * n_splits, n_list, G);
-    attn_mma_kernel<true><<<grid, THREADS, smem, stream>>>(a);
-    SLLM_LAUNCH_CHECK();
+    e = sllm_launch_pdl(attn_mma_kernel<true>, grid, dim3(THREADS), smem, stream, a);
+    if (e != cudaSuccess) return (int)e;
     if (n_splits > 1) {
         dim3 mgrid(n_list, H);
-        attn_merge_kernel<<<mgrid, HD >= 128 ? 128 : 32, 0, stream>>>(
-            a.part_o, a.part_lse, n_splits, row_start, row_list, (bf16*)out, out_stride, H);
-        SLLM_LAUNCH_CHECK();
+        e = sllm_launch_pdl(attn_merge_kernel, mgrid, dim3(HD >= 128 ? 128 : 32), 0, stream,
+                            (const float*)a.part_o, (const float*)a.part_lse, n_splits, row_start,
+                            row_list, (bf16*)out, out_stride, H);
+        if (e != cudaSuccess) return (int)e;
     }
     return 0;
 }

@@ -12,6 +12,7 @@ namespace sllm {
 template <typename T>
 __global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ table,
                              float* __restrict__ out, int d) {
+    pdl_wait();
     pdl_trigger();
     const int64_t n = blockIdx.x;
     const T* src = table + (int64_t)ids[n] * d;
@@ -27,6 +28,7 @@ template <typename T>
 __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const T* __restrict__ delta,
                                    const int* __restrict__ index, const float* __restrict__ w,
                                    float eps, T* __restrict__ out, int d) {
+    pdl_wait();
     pdl_trigger();
     __shared__ float scratch[33];
     const int64_t o = blockIdx.x;
@@ -60,6 +62,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const T* __restric
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int64_t n_rows,
                               int F) {
+    pdl_wait();
     pdl_trigger();
     const int64_t total = n_rows * F;
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
@@ -98,6 +101,7 @@ template <typename T>
 __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const T* __restrict__ delta,
                                        const int* __restrict__ index, const float* __restrict__ w,
                                        float eps, T* __restrict__ out, int d) {
+    pdl_wait();
     pdl_trigger();
     __shared__ float scratch[33];
     const int64_t o = blockIdx.x;
@@ -137,6 +141,7 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const T* __res
 template <typename T>
 __global__ void swiglu_vec_kernel(const T* __restrict__ gu, T* __restrict__ out, int64_t n_rows,
                                   int F) {
+    pdl_wait();
     pdl_trigger();
     const int per_row = F / 8;
     const int64_t total = n_rows * per_row;
@@ -193,14 +198,15 @@ SLLM_EXPORT int sllm_add_rmsnorm(float* resid, const void* delta, const int* ind
     if (d % 4 == 0 && d <= 4 * VEC_CHUNKS * 1024 && dtype >= 0 && dtype <= 1) {
         int vt = 32;
         while (vt < 1024 && vt * 4 * (d > 4096 ? VEC_CHUNKS : 1) < d) vt <<= 1;
+        cudaError_t e;
         if (dtype == 0)
-            add_rmsnorm_vec_kernel<float><<<n_out, vt, 0, stream>>>(
-                resid, (const float*)delta, index, w, eps, (float*)out, d);
+            e = sllm_launch_pdl(add_rmsnorm_vec_kernel<float>, dim3(n_out), dim3(vt), 0, stream,
+                                resid, (const float*)delta, index, w, eps, (float*)out, d);
         else
-            add_rmsnorm_vec_kernel<__nv_bfloat16><<<n_out, vt, 0, stream>>>(
-                resid, (const __nv_bfloat16*)delta, index, w, eps, (__nv_bfloat16*)out, d);
-        SLLM_LAUNCH_CHECK();
-        return 0;
+            e = sllm_launch_pdl(add_rmsnorm_vec_kernel<__nv_bfloat16>, dim3(n_out), dim3(vt), 0,
+                                stream, resid, (const __nv_bfloat16*)delta, index, w, eps,
+                                (__nv_bfloat16*)out, d);
+        return (int)e;
     }
     const int threads = norm_threads(d);
     if (dtype == 0)

@@ -124,9 +124,9 @@ gemv_mma_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, TOut* __
     };
     // The weights of the first steps are requested before the wait for earlier kernels: nothing
     // writes weights, so this part of the stream overlaps the previous kernel's tail.
-    pdl_trigger();
     if (step_begin < step_end) load_w(step_begin);
     pdl_wait();
+    pdl_trigger();
     if (step_begin < step_end) {
         load_x(step_begin);
         multiply();

@@ -23,6 +23,7 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
                                      const int* __restrict__ block_table, int table_stride,
                                      int page_size, int H, int G, int hd, int rotate,
                                      int interleaved, int write, int heads_per_block) {
+    pdl_wait();
     pdl_trigger();
     const int64_t n = blockIdx.x;
     const int half = hd >> 1;
@@ -82,16 +83,14 @@ SLLM_EXPORT int sllm_rope_kv_write(void* qkv, const int* positions, const int* t
     dim3 grid(n_tokens, (n_heads + heads_per_block - 1) / heads_per_block);
     if (grid.y > 65535) return (int)cudaErrorInvalidValue;
     if (dtype == 0)
-        rope_kv_write_kernel<float><<<grid, threads, 0, stream>>>(
-            (float*)qkv, positions, token_row, cos_t, sin_t, (float*)pages, block_table,
-            table_stride, page_size, H, G, hd, rotate, interleaved, write, heads_per_block);
-    else if (dtype == 1)
-        rope_kv_write_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(
-            (__nv_bfloat16*)qkv, positions, token_row, cos_t, sin_t, (__nv_bfloat16*)pages,
-            block_table, table_stride, page_size, H, G, hd, rotate, interleaved, write,
-            heads_per_block);
-    else
-        return (int)cudaErrorInvalidValue;
-    SLLM_LAUNCH_CHECK();
-    return 0;
+        return (int)sllm_launch_pdl(rope_kv_write_kernel<float>, grid, dim3(threads), 0, stream,
+                                    (float*)qkv, positions, token_row, cos_t, sin_t, (float*)pages,
+                                    block_table, table_stride, page_size, H, G, hd, rotate,
+                                    interleaved, write, heads_per_block);
+    if (dtype == 1)
+        return (int)sllm_launch_pdl(rope_kv_write_kernel<__nv_bfloat16>, grid, dim3(threads), 0,
+                                    stream, (__nv_bfloat16*)qkv, positions, token_row, cos_t, sin_t,
+                                    (__nv_bfloat16*)pages, block_table, table_stride, page_size, H,
+                                    G, hd, rotate, interleaved, write, heads_per_block);
+    return (int)cudaErrorInvalidValue;
 }

@@ -120,6 +120,14 @@ def compile_library(name: str, sources: Sequence[str], defines: Iterable[str] = 
             raise BuildError(f"nvcc failed for {name}:\n{' '.join(cmd)}\n{proc.stdout}\n"
                              f"{proc.stderr}")
         os.replace(tmp, out)
+        # builds of earlier versions of this library's sources are of no more use
+        prefix = out.name[:out.name.rfind("_") + 1]
+        for old in out.parent.glob(prefix + "*.so"):
+            if old != out and ".tmp" not in old.name:
+                try:
+                    old.unlink()
+                except OSError:
+                    pass
     with _lock:
         _done[key] = out
     return out
