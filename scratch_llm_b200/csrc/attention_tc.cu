@@ -1,0 +1,489 @@
+// Causal attention of prompt portions over the paged cache on the tcgen05 tensor cores:
+// S = Q K^T and O += P V are tcgen05.mma instructions with S, P and O in tensor memory, keys
+// and values arrive page by page through TMA, and the softmax runs with one thread per query
+// row (a thread reads its own lane of tensor memory, so row maxima and sums need no shuffles).
+//
+// Same mathematics as attention_mma.cu (src/scratch_llm/model.py:172-182, :330-345 of the
+// reference: scaled scores, causal mask, softmax in 32-bit, probabilities rounded to bfloat16
+// before they multiply v, query head h reads kv head h / (H/G)); same packing of a kv head's
+// GS = H/G query heads into one tile (packed index p = token * GS + j).
+//
+//   CTA = 128 packed queries of one (row, kv head), 192 threads:
+//     warp 0     TMA producer: the query tile once, then per 128-key tile the pages of K and V
+//                (boxes of page_size rows x 64 columns, 128-byte swizzle), 2 stages
+//     warp 1     MMA issuer: QK^T (M 128, N 128, K = head size) into S; P V (M 128, N = head
+//                size, K 128; A = P from tensor memory, B = V in its stored [key][dim] layout,
+//                i.e. MN-major) into O
+//     warps 2-5  softmax: S -> registers, mask, running maximum and sum, P -> tensor memory as
+//                bfloat16; O is rescaled in tensor memory only when a row's maximum grew by
+//                more than 2^8 (the stale reference maximum is exact as long as the final
+//                division uses the matching sum); at the end O / l -> global memory
+//   tensor memory: S columns 0..127, P 128..191 (two bfloat16 per column), O 256..256+HD-1.
+//
+// Takes head sizes that are multiples of 64 up to 256, group sizes that divide 128, page sizes
+// that divide 128, no window; other shapes use attention_mma.cu.  Cache memory beyond a
+// request's context must hold finite values (the cache manager zero-fills the pool once and
+// only finite keys and values are ever stored): such values are multiplied by probabilities
+// that are exactly zero.  Every mbarrier wait is bounded; errors land in g_attn_tc_error.
+#include <cuda.h>
+
+#include "common.cuh"
+
+#ifndef SLLM_HEAD_DIM
+#error "compile with -DSLLM_HEAD_DIM=<head size>"
+#endif
+
+namespace sllm {
+
+typedef __nv_bfloat16 bf16;
+constexpr int HD = SLLM_HEAD_DIM;
+static_assert(HD % 64 == 0 && HD >= 64 && HD <= 256, "head size: 64, 128, 192 or 256");
+constexpr int TQ = 128, TKV = 128, NCB = HD / 64;            // column blocks of 64 (128 bytes)
+constexpr int SUB_BYTES = 128 * 128;                          // 128 rows x 128 bytes
+constexpr int Q_BYTES = NCB * SUB_BYTES, KV_BYTES = NCB * SUB_BYTES;
+constexpr int KV_STAGES = HD <= 128 ? 2 : 1;
+constexpr int ATC_THREADS = 192;
+constexpr uint32_t S_COL = 0, P_COL = 128, O_COL = 256;
+constexpr uint32_t ATC_WAIT_LIMIT = 1u << 24;
+constexpr size_t ATC_SMEM = (size_t)Q_BYTES + (size_t)KV_STAGES * 2 * KV_BYTES + 1024 + 256;
+constexpr float RESCALE_THRESHOLD = 8.0f;                     // log2 units
+
+__device__ int g_attn_tc_error = 0;
+
+__device__ __forceinline__ uint32_t atc_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void atc_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(atc_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void atc_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n"
+                 ::"r"(atc_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void atc_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(atc_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool atc_wait(uint64_t* bar, uint32_t parity, int code) {
+    const uint32_t addr = atc_u32(bar);
+    for (uint32_t i = 0; i < ATC_WAIT_LIMIT; ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n.reg .pred p;\n"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+            "selp.u32 %0, 1, 0, p;\n}\n"
+            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+        if (i > 4096) __nanosleep(32);
+    }
+    atomicCAS(&g_attn_tc_error, 0, code);
+    return false;
+}
+__device__ __forceinline__ void atc_tma_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x,
+                                           int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4}], [%2];\n"
+        ::"r"(atc_u32(dst)), "l"(map), "r"(atc_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void atc_tma_3d(void* dst, const CUtensorMap* map, uint64_t* bar, int x,
+                                           int y, int z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5}], [%2];\n"
+        ::"r"(atc_u32(dst)), "l"(map), "r"(atc_u32(bar)), "r"(x), "r"(y), "r"(z) : "memory");
+}
+// shared-memory matrix descriptor, 128-byte swizzle: lbo / sbo in bytes
+__device__ __forceinline__ uint64_t atc_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+    return (uint64_t)((addr >> 4) & 0x3FFF) | ((uint64_t)((lbo >> 4) & 0x3FFF) << 16) |
+           ((uint64_t)((sbo >> 4) & 0x3FFF) << 32) | (1ull << 46) | (2ull << 61);
+}
+__device__ __forceinline__ void atc_mma_ss(uint32_t d, uint64_t da, uint64_t db, uint32_t idesc,
+                                           uint32_t acc) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n}\n"
+        ::"r"(d), "l"(da), "l"(db), "r"(idesc), "r"(acc), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+        : "memory");
+}
+__device__ __forceinline__ void atc_mma_ts(uint32_t d, uint32_t a_tmem, uint64_t db, uint32_t idesc,
+                                           uint32_t acc) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %6, %7, %8}, p;\n}\n"
+        ::"r"(d), "r"(a_tmem), "l"(db), "r"(idesc), "r"(acc), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+        : "memory");
+}
+__device__ __forceinline__ void atc_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n"
+                 ::"r"(atc_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void atc_ld32(uint32_t taddr, float (&r)[32]) {
+    uint32_t v[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+          "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
+          "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]),
+          "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]),
+          "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) r[i] = __uint_as_float(v[i]);
+}
+__device__ __forceinline__ void atc_st32(uint32_t taddr, const uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};\n"
+        ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]),
+          "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]),
+          "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]),
+          "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]),
+          "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+        : "memory");
+}
+__device__ __forceinline__ void atc_st_wait() {
+    asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void atc_fence_before() {
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+}
+__device__ __forceinline__ void atc_fence_after() {
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+}
+__device__ __forceinline__ uint32_t atc_pack(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+struct AtcArgs {
+    const int* block_table; int table_stride; int page_size;
+    const int* row_start; const int* row_pos0; const int* row_list;
+    bf16* out; int64_t out_stride;
+    int H, G; float scale_log2;
+};
+
+__global__ void __launch_bounds__(ATC_THREADS, 1)
+attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
+               const AtcArgs a) {
+    extern __shared__ unsigned char atc_smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>(
+        ((uintptr_t)atc_smem_raw + 1023) & ~(uintptr_t)1023);
+    unsigned char* q_s = smem;
+    unsigned char* kv_s = smem + Q_BYTES;                    // stage s: K at s*2*KV_BYTES, V after
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Q_BYTES + (size_t)KV_STAGES * 2 * KV_BYTES);
+    uint64_t* q_full = bars;
+    uint64_t* kv_full = bars + 1;                            // [KV_STAGES]
+    uint64_t* kv_empty = kv_full + KV_STAGES;                // [KV_STAGES]
+    uint64_t* s_full = kv_empty + KV_STAGES;
+    uint64_t* p_full = s_full + 1;
+    uint64_t* pv_done = p_full + 1;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r = a.row_list ? a.row_list[blockIdx.y] : blockIdx.y;
+    const int g = blockIdx.z;
+    const int GS = a.H / a.G;
+    const int t0 = a.row_start[r];
+    const int n_new = a.row_start[r + 1] - t0;
+    const int pos0 = a.row_pos0[r];
+    const int n_packed = n_new * GS;
+    // heavy (late) query tiles first
+    const int q_tile = (int)gridDim.x - 1 - (int)blockIdx.x;
+    const int q0 = q_tile * TQ;
+    if (q0 >= n_packed) return;
+    const int tok_first = q0 / GS;
+    const int last_pos = pos0 + min(n_packed - 1, q0 + TQ - 1) / GS;
+    const int n_tiles = last_pos / TKV + 1;
+
+    if (threadIdx.x == 0) {
+        atc_init(q_full, 1);
+        for (int s = 0; s < KV_STAGES; ++s) {
+            atc_init(&kv_full[s], 1);
+            atc_init(&kv_empty[s], 1);
+        }
+        atc_init(s_full, 1);
+        atc_init(p_full, 4);
+        atc_init(pv_done, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
+                     ::"r"(atc_u32(tmem_slot)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    atc_fence_before();
+    __syncthreads();
+    atc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // queries: box (64 columns, GS heads, 128 / GS tokens) per 64-column block
+            atc_expect_tx(q_full, Q_BYTES);
+            for (int c = 0; c < NCB; ++c)
+                atc_tma_3d(q_s + c * SUB_BYTES, &map_q, q_full, c * 64, g * GS, t0 + tok_first);
+            const int pages_per_tile = TKV / a.page_size;
+            const int64_t rows_per_page = (int64_t)2 * a.G * a.page_size;
+            const int* table = a.block_table + (int64_t)r * a.table_stride;
+            const int n_pages_held = last_pos / a.page_size + 1;
+            const int spare = table[0];   // a page that certainly holds finite values
+            for (int t = 0; t < n_tiles; ++t) {
+                const int s = t % KV_STAGES;
+                if (!atc_wait(&kv_empty[s], ((t / KV_STAGES) & 1) ^ 1, 1)) break;
+                atc_expect_tx(&kv_full[s], 2 * KV_BYTES);
+                unsigned char* k_dst = kv_s + (size_t)s * 2 * KV_BYTES;
+                unsigned char* v_dst = k_dst + KV_BYTES;
+                for (int i = 0; i < pages_per_tile; ++i) {
+                    const int lp = t * pages_per_tile + i;
+                    int page = lp < n_pages_held ? table[lp] : spare;
+                    if (page < 0) page = spare;
+                    const int64_t row_k = ((int64_t)page * rows_per_page) + (int64_t)g * a.page_size;
+                    const int64_t row_v = row_k + (int64_t)a.G * a.page_size;
+                    for (int c = 0; c < NCB; ++c) {
+                        atc_tma_2d(k_dst + c * SUB_BYTES + i * a.page_size * 128, &map_kv,
+                                   &kv_full[s], c * 64, (int)row_k);
+                        atc_tma_2d(v_dst + c * SUB_BYTES + i * a.page_size * 128, &map_kv,
+                                   &kv_full[s], c * 64, (int)row_v);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // instruction descriptors: D f32, A and B bf16; QK^T: both K-major, N = 128;
+            // P V: B (= V) MN-major, N = head size
+            const uint32_t idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) |
+                                      ((uint32_t)(TKV >> 3) << 17) | ((uint32_t)(TQ >> 4) << 24);
+            const uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) |
+                                      ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(TQ >> 4) << 24);
+            bool ok = atc_wait(q_full, 0, 2);
+            for (int t = 0; t < n_tiles && ok; ++t) {
+                const int s = t % KV_STAGES;
+                ok = atc_wait(&kv_full[s], (t / KV_STAGES) & 1, 3);
+                if (!ok) break;
+                atc_fence_after();
+                const uint32_t k_addr = atc_u32(kv_s + (size_t)s * 2 * KV_BYTES);
+                const uint32_t v_addr = k_addr + KV_BYTES;
+                // S = Q K^T: K steps of 16 over the head size
+#pragma unroll
+                for (int kk = 0; kk < HD / 16; ++kk) {
+                    const uint64_t dq = atc_desc(atc_u32(q_s) + (kk / 4) * SUB_BYTES, 16, 1024) +
+                                        2 * (kk % 4);
+                    const uint64_t dk = atc_desc(k_addr + (kk / 4) * SUB_BYTES, 16, 1024) +
+                                        2 * (kk % 4);
+                    atc_mma_ss(tmem + S_COL, dq, dk, idesc_qk, kk > 0);
+                }
+                atc_commit(s_full);
+                // O += P V once the softmax warps have written P: K steps of 16 keys
+                ok = atc_wait(p_full, t & 1, 4);
+                if (!ok) break;
+                atc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < TKV / 16; ++kk) {
+                    // V: rows = keys (128 bytes = 64 dims each), 8-key groups 1024 bytes apart,
+                    // 64-dim blocks SUB_BYTES apart; 16 keys further = 2048 bytes
+                    const uint64_t dv = atc_desc(v_addr + kk * 2048, SUB_BYTES, 1024);
+                    atc_mma_ts(tmem + O_COL, tmem + P_COL + kk * 8, dv, idesc_pv, (t | kk) != 0);
+                }
+                atc_commit(&kv_empty[s]);
+                atc_commit(pv_done);
+            }
+        }
+    } else {
+        const int quad = warp & 3;
+        const int row = quad * 32 + lane;                    // packed query within the tile
+        const uint32_t lane_base = tmem + ((uint32_t)(quad * 32) << 16);
+        const int p = q0 + row;
+        const bool valid = p < n_packed;
+        const int tok = valid ? p / GS : 0, j = valid ? p - tok * GS : 0;
+        const int qpos = pos0 + tok;
+        float m_ref = -INFINITY, l_sum = 0.f;
+        bool ok = true;
+        for (int t = 0; t < n_tiles; ++t) {
+            ok = atc_wait(s_full, t & 1, 5);
+            if (!ok) break;
+            atc_fence_after();
+            const int kt = t * TKV;
+            // pass 1: the row's maximum over the tile (scaled to log2 units, masked)
+            float sv[4][32];
+            float mx = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                atc_ld32(lane_base + S_COL + c * 32, sv[c]);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const int kpos = kt + c * 32 + i;
+                    const float x = (valid && kpos <= qpos) ? sv[c][i] * a.scale_log2 : -INFINITY;
+                    sv[c][i] = x;
+                    mx = fmaxf(mx, x);
+                }
+            }
+            // the reference maximum moves only when it must (first keys, or growth beyond 2^8)
+            float corr = 1.f;
+            if (mx > m_ref + RESCALE_THRESHOLD || (m_ref == -INFINITY && mx != -INFINITY)) {
+                corr = m_ref == -INFINITY ? 0.f : exp2f(m_ref - mx);
+                m_ref = mx;
+                l_sum *= corr;
+            }
+            // P and O are free once the previous tile's P V has finished
+            if (t > 0) {
+                ok = atc_wait(pv_done, (t - 1) & 1, 6);
+                if (!ok) break;
+                atc_fence_after();
+                if (__any_sync(0xffffffffu, corr != 1.f)) {
+#pragma unroll 1
+                    for (int c = 0; c < HD / 32; ++c) {
+                        float ov[32];
+                        atc_ld32(lane_base + O_COL + c * 32, ov);
+                        uint32_t w[32];
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) w[i] = __float_as_uint(ov[i] * corr);
+                        atc_st32(lane_base + O_COL + c * 32, w);
+                    }
+                }
+            }
+            // pass 2: probabilities, their sum, P as bfloat16 pairs
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                uint32_t w[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const int k0 = c * 64 + 2 * i;           // keys k0, k0 + 1 of the tile
+                    const float x0 = sv[k0 / 32][k0 % 32], x1 = sv[(k0 + 1) / 32][(k0 + 1) % 32];
+                    const float p0 = x0 == -INFINITY ? 0.f : exp2f(x0 - m_ref);
+                    const float p1 = x1 == -INFINITY ? 0.f : exp2f(x1 - m_ref);
+                    l_sum += p0 + p1;
+                    w[i] = atc_pack(p0, p1);
+                }
+                atc_st32(lane_base + P_COL + c * 32, w);
+            }
+            atc_st_wait();
+            atc_fence_before();
+            __syncwarp();
+            if (lane == 0) atc_arrive(p_full);
+        }
+        if (ok && atc_wait(pv_done, (n_tiles - 1) & 1, 7)) {
+            atc_fence_after();
+            const float inv = l_sum > 0.f ? 1.0f / l_sum : 0.f;
+            bf16* dst = a.out + (int64_t)(t0 + tok) * a.out_stride + (int64_t)(g * GS + j) * HD;
+#pragma unroll 1
+            for (int c = 0; c < HD / 32; ++c) {
+                float ov[32];
+                atc_ld32(lane_base + O_COL + c * 32, ov);
+                if (valid) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        uint4 q4;
+                        q4.x = atc_pack(ov[8 * i + 0] * inv, ov[8 * i + 1] * inv);
+                        q4.y = atc_pack(ov[8 * i + 2] * inv, ov[8 * i + 3] * inv);
+                        q4.z = atc_pack(ov[8 * i + 4] * inv, ov[8 * i + 5] * inv);
+                        q4.w = atc_pack(ov[8 * i + 6] * inv, ov[8 * i + 7] * inv);
+                        reinterpret_cast<uint4*>(dst + c * 32)[i] = q4;
+                    }
+                }
+            }
+        }
+    }
+    atc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        atc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n"
+                     ::"r"(tmem), "r"(512u) : "memory");
+    }
+}
+
+typedef CUresult (*AtcEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static AtcEncodeFn atc_encode_fn() {
+    static AtcEncodeFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) ==
+                cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = (AtcEncodeFn)p;
+    }
+    return fn;
+}
+
+}  // namespace sllm
+
+using namespace sllm;
+
+SLLM_EXPORT int sllm_attn_tc_head_dim() { return HD; }
+
+// 1 if this kernel takes the shape, 0 if attention_mma.cu must serve it.
+SLLM_EXPORT int sllm_attn_tc_supports(int H, int G, int page_size, int window) {
+    if (H <= 0 || G <= 0 || H % G) return 0;
+    const int GS = H / G;
+    return (128 % GS == 0) && page_size > 0 && (128 % page_size == 0) && window == 0;
+}
+
+SLLM_EXPORT int sllm_attn_tc_error() {
+    int code = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&code, g_attn_tc_error, sizeof(int)) != cudaSuccess) return -1;
+    if (code) cudaMemcpyToSymbol(g_attn_tc_error, &zero, sizeof(int));
+    return code;
+}
+
+// q / out: [n_tokens, stride] bfloat16, head h at columns [h*HD, (h+1)*HD).  pages:
+// [n_pages, 2, G, page_size, HD] bfloat16, finite everywhere.  row_list: the n_list rows served
+// (nullptr: rows 0..n_list-1); max_new: the largest number of new tokens among them.
+SLLM_EXPORT int sllm_attn_tc(const void* q, int64_t q_stride, int64_t n_tokens, const void* pages,
+                             int64_t n_pages, const int* block_table, int table_stride,
+                             int page_size, const int* row_start, const int* row_pos0,
+                             const int* row_list, int n_list, int max_new, void* out,
+                             int64_t out_stride, int H, int G, float scale, cudaStream_t stream) {
+    if (n_list <= 0 || max_new <= 0) return 0;
+    if (!sllm_attn_tc_supports(H, G, page_size, 0) || n_list > 65535 || G > 65535 ||
+        (q_stride % 8) || (out_stride % 8) || ((uintptr_t)q & 15) || ((uintptr_t)pages & 15) ||
+        ((uintptr_t)out & 15))
+        return (int)cudaErrorInvalidValue;
+    if (n_pages * 2 * G * page_size > 0x7fffffffLL || n_tokens > 0x7fffffffLL)
+        return (int)cudaErrorInvalidValue;
+    AtcEncodeFn fn = atc_encode_fn();
+    if (!fn) return (int)cudaErrorNotSupported;
+    const int GS = H / G;
+    CUtensorMap map_q, map_kv;
+    {   // q as (column, head, token)
+        cuuint64_t dims[3] = {(cuuint64_t)HD, (cuuint64_t)H, (cuuint64_t)n_tokens};
+        cuuint64_t strides[2] = {(cuuint64_t)HD * 2, (cuuint64_t)q_stride * 2};
+        cuuint32_t box[3] = {64u, (cuuint32_t)GS, (cuuint32_t)(TQ / GS)};
+        cuuint32_t elem[3] = {1u, 1u, 1u};
+        if (fn(&map_q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(q), dims, strides,
+               box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return (int)cudaErrorInvalidValue;
+    }
+    {   // the cache as rows of HD columns: row = ((page * 2 + kv) * G + g) * page_size + offset
+        cuuint64_t dims[2] = {(cuuint64_t)HD, (cuuint64_t)(n_pages * 2 * G * page_size)};
+        cuuint64_t strides[1] = {(cuuint64_t)HD * 2};
+        cuuint32_t box[2] = {64u, (cuuint32_t)page_size};
+        cuuint32_t elem[2] = {1u, 1u};
+        if (fn(&map_kv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pages), dims,
+               strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return (int)cudaErrorInvalidValue;
+    }
+    AtcArgs a;
+    a.block_table = block_table; a.table_stride = table_stride; a.page_size = page_size;
+    a.row_start = row_start; a.row_pos0 = row_pos0; a.row_list = row_list;
+    a.out = (bf16*)out; a.out_stride = out_stride; a.H = H; a.G = G;
+    a.scale_log2 = scale * 1.4426950408889634f;
+    cudaError_t e = cudaFuncSetAttribute(attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)ATC_SMEM);
+    if (e != cudaSuccess) return (int)e;
+    dim3 grid(((int64_t)max_new * GS + TQ - 1) / TQ, n_list, G);
+    attn_tc_kernel<<<grid, ATC_THREADS, ATC_SMEM, stream>>>(map_q, map_kv, a);
+    SLLM_LAUNCH_CHECK();
+    return 0;
+}

@@ -47,6 +47,20 @@ def attention_mma_library(head_dim: int) -> tuple[str, tuple[str, ...], tuple[st
             (f"SLLM_HEAD_DIM={head_dim}",))
 
 
+def attention_tc_library(head_dim: int) -> tuple[str, tuple[str, ...], tuple[str, ...]]:
+    return (f"sllm_attention_tc_hd{head_dim}", ("attention_tc.cu",),
+            (f"SLLM_HEAD_DIM={head_dim}",))
+
+
+def attention_tc_supports(n_heads: int, n_kv_heads: int, head_dim: int, page_size: int,
+                          window: int | None) -> bool:
+    """Whether the tcgen05 attention kernel takes this shape (else attention_mma serves it)."""
+    if head_dim % 64 or not 64 <= head_dim <= 256 or window:
+        return False
+    gs = n_heads // n_kv_heads
+    return n_heads % n_kv_heads == 0 and 128 % gs == 0 and page_size > 0 and 128 % page_size == 0
+
+
 #: the tensor-core attention kernels take head sizes up to this; larger ones use the CUDA cores
 MMA_MAX_HEAD_DIM = 256
 
@@ -74,6 +88,8 @@ def prepare(head_dims: Sequence[int] = (), verbose: bool = True) -> None:
     jobs = [(n, s, d) for n, (s, d) in CORE_LIBRARIES.items()]
     jobs += [attention_library(hd) for hd in sorted(set(head_dims))]
     jobs += [attention_mma_library(hd) for hd in sorted(set(head_dims)) if hd <= MMA_MAX_HEAD_DIM]
+    jobs += [attention_tc_library(hd) for hd in sorted(set(head_dims))
+             if hd % 64 == 0 and hd <= 256]
     build.compile_many(jobs, verbose=verbose)
     for n, s, d in jobs:
         _load(n, s, d)
@@ -357,6 +373,43 @@ def attention_mma(q: torch.Tensor, pages: torch.Tensor, block_table: torch.Tenso
         c_int(int(split)), c_int(n_splits), _ptr(scratch), c_int64(n_tokens), _stream()),
         "attention_mma")
     return out
+
+
+def attention_tc(q: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor, page_size: int,
+                 row_start: torch.Tensor, row_pos0: torch.Tensor, out: torch.Tensor,
+                 row_list: torch.Tensor | None, n_list: int, max_new: int, n_heads: int,
+                 n_kv_heads: int, head_dim: int, scale: float) -> torch.Tensor:
+    """Causal attention of the listed rows (prompt portions) over the paged cache on tcgen05
+    tensor cores with S, P and O in tensor memory.  The cache must hold finite values
+    everywhere (also in places no request uses)."""
+    _need(q, torch.bfloat16, "q", contiguous=False)
+    _need(pages, torch.bfloat16, "pages")
+    _need(out, torch.bfloat16, "out", contiguous=False)
+    _need(block_table, torch.int32, "block_table", contiguous=False)
+    _need(row_start, torch.int32, "row_start")
+    _need(row_pos0, torch.int32, "row_pos0")
+    if row_list is not None:
+        _need(row_list, torch.int32, "row_list")
+    if not attention_tc_supports(n_heads, n_kv_heads, head_dim, page_size, None):
+        raise KernelError("attention_tc does not take this shape")
+    if q.stride(1) != 1 or out.stride(1) != 1 or q.shape[1] != n_heads * head_dim \
+            or out.shape != q.shape:
+        raise KernelError("attention q/out layout")
+    if pages.shape[1:] != (2, n_kv_heads, page_size, head_dim):
+        raise KernelError(f"pages must be [n_pages, 2, {n_kv_heads}, {page_size}, {head_dim}], "
+                          f"got {list(pages.shape)}")
+    lib = _load(*attention_tc_library(head_dim))
+    _check(lib.sllm_attn_tc(
+        _ptr(q), c_int64(q.stride(0)), c_int64(q.shape[0]), _ptr(pages), c_int64(pages.shape[0]),
+        _ptr(block_table), c_int(block_table.stride(0)), c_int(page_size), _ptr(row_start),
+        _ptr(row_pos0), _ptr(row_list), c_int(n_list), c_int(max_new), _ptr(out),
+        c_int64(out.stride(0)), c_int(n_heads), c_int(n_kv_heads), c_float(scale), _stream()),
+        "attention_tc")
+    return out
+
+
+def attention_tc_error(head_dim: int) -> int:
+    return int(_load(*attention_tc_library(head_dim)).sllm_attn_tc_error())
 
 
 def attention_mma_scratch_floats(n_tokens: int, n_heads: int, head_dim: int, n_splits: int) -> int:

@@ -249,6 +249,31 @@ def test_attention_on_tensor_cores(ops, H, G, hd, page, window, n_splits):
         check_attention(case, out.cpu().float(), every, "bfloat16", H, hd, window)
 
 
+@pytest.mark.parametrize("H, G, hd, page", [(8, 2, 64, 16), (32, 8, 128, 16), (8, 1, 128, 32),
+                                           (4, 4, 64, 8), (2, 1, 128, 128)])
+def test_attention_tcgen05(ops, H, G, hd, page):
+    """Prompt portions on the tcgen05 kernel: long rows (several key tiles, several query
+    tiles), rows that start deep in a context, short rows; unused cache places hold large
+    finite values (the kernel's contract) that must not reach a result."""
+    ops.prepare([hd], verbose=False)
+    rows = [(0, 300), (450, 40), (0, 17), (127, 2), (128, 129), (1000, 30)]
+    global ATTN_ROWS
+    saved = ATTN_ROWS
+    ATTN_ROWS = rows
+    try:
+        case = attention_case("bfloat16", H, G, hd, page)
+        pages = torch.nan_to_num(case["pages"].float(), nan=3e4).to(torch.bfloat16)
+        q = case["wide"][:, :H * hd]
+        out = torch.full((q.shape[0], H * hd), float("nan"), dtype=torch.bfloat16, device="cuda")
+        every = list(range(len(rows)))
+        ops.attention_tc(q, pages, case["table"], page, case["row_start"], case["row_pos0"], out,
+                         None, len(rows), max(n for _, n in rows), H, G, hd, 1.0 / math.sqrt(hd))
+        assert ops.attention_tc_error(hd) == 0
+        check_attention(case, out.cpu().float(), every, "bfloat16", H, hd, None)
+    finally:
+        ATTN_ROWS = saved
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("interleaved", [True, False])
 def test_rope_and_cache_write(ops, dtype, interleaved):
