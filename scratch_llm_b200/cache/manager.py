@@ -82,7 +82,10 @@ class CacheManager:
         if self.device is not None:
             for group in self.groups:
                 s = group.spec
-                group.pages = torch.empty((len(group.entries), n_pages, 2, s.n_kv_heads,
+                # zero-filled once: the contents of a reused page never matter, but the
+                # tcgen05 attention kernel multiplies values beyond a request's context by
+                # probabilities that are exactly zero, which needs them to be finite
+                group.pages = torch.zeros((len(group.entries), n_pages, 2, s.n_kv_heads,
                                            page_size, s.head_dim), dtype=dtype,
                                           device=self.device)
             for entry, st in enumerate(self.state_specs):

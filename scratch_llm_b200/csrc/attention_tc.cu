@@ -117,6 +117,25 @@ __device__ __forceinline__ void atc_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n"
                  ::"r"(atc_u32(bar)) : "memory");
 }
+// the load alone; atc_ld_wait() must follow before the values are used
+__device__ __forceinline__ void atc_ld32_nowait(uint32_t taddr, float (&r)[32]) {
+    uint32_t v[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+          "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
+          "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]),
+          "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]),
+          "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr));
+#pragma unroll
+    for (int i = 0; i < 32; ++i) r[i] = __uint_as_float(v[i]);
+}
+__device__ __forceinline__ void atc_ld_wait() {
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+}
 __device__ __forceinline__ void atc_ld32(uint32_t taddr, float (&r)[32]) {
     uint32_t v[32];
     asm volatile(
@@ -222,34 +241,49 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     const uint32_t tmem = *tmem_slot;
 
     if (warp == 0) {
+        // The whole warp produces: lane 0 owns the barriers, every lane looks up and copies the
+        // pages lane, lane + 32, ... of a tile, so the page lookups of a tile overlap.
         if (lane == 0) {
             // queries: box (64 columns, GS heads, 128 / GS tokens) per 64-column block
             atc_expect_tx(q_full, Q_BYTES);
             for (int c = 0; c < NCB; ++c)
                 atc_tma_3d(q_s + c * SUB_BYTES, &map_q, q_full, c * 64, g * GS, t0 + tok_first);
-            const int pages_per_tile = TKV / a.page_size;
-            const int64_t rows_per_page = (int64_t)2 * a.G * a.page_size;
-            const int* table = a.block_table + (int64_t)r * a.table_stride;
-            const int n_pages_held = last_pos / a.page_size + 1;
-            const int spare = table[0];   // a page that certainly holds finite values
-            for (int t = 0; t < n_tiles; ++t) {
-                const int s = t % KV_STAGES;
-                if (!atc_wait(&kv_empty[s], ((t / KV_STAGES) & 1) ^ 1, 1)) break;
-                atc_expect_tx(&kv_full[s], 2 * KV_BYTES);
-                unsigned char* k_dst = kv_s + (size_t)s * 2 * KV_BYTES;
-                unsigned char* v_dst = k_dst + KV_BYTES;
-                for (int i = 0; i < pages_per_tile; ++i) {
-                    const int lp = t * pages_per_tile + i;
-                    int page = lp < n_pages_held ? table[lp] : spare;
-                    if (page < 0) page = spare;
-                    const int64_t row_k = ((int64_t)page * rows_per_page) + (int64_t)g * a.page_size;
-                    const int64_t row_v = row_k + (int64_t)a.G * a.page_size;
-                    for (int c = 0; c < NCB; ++c) {
-                        atc_tma_2d(k_dst + c * SUB_BYTES + i * a.page_size * 128, &map_kv,
-                                   &kv_full[s], c * 64, (int)row_k);
-                        atc_tma_2d(v_dst + c * SUB_BYTES + i * a.page_size * 128, &map_kv,
-                                   &kv_full[s], c * 64, (int)row_v);
-                    }
+        }
+        const int pages_per_tile = TKV / a.page_size;
+        const int64_t rows_per_page = (int64_t)2 * a.G * a.page_size;
+        const int* table = a.block_table + (int64_t)r * a.table_stride;
+        const int n_pages_held = last_pos / a.page_size + 1;
+        const int spare = table[0];   // a page that certainly holds finite values
+        for (int t = 0; t < n_tiles; ++t) {
+            const int s = t % KV_STAGES;
+            // next tile's page numbers are requested before the wait for a free stage
+            int my_page[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = lane + 32 * u, lp = t * pages_per_tile + i;
+                my_page[u] = (i < pages_per_tile && lp < n_pages_held) ? table[lp] : spare;
+                if (my_page[u] < 0) my_page[u] = spare;
+            }
+            int ok = 1;
+            if (lane == 0) {
+                ok = atc_wait(&kv_empty[s], ((t / KV_STAGES) & 1) ^ 1, 1) ? 1 : 0;
+                if (ok) atc_expect_tx(&kv_full[s], 2 * KV_BYTES);
+            }
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) break;
+            unsigned char* k_dst = kv_s + (size_t)s * 2 * KV_BYTES;
+            unsigned char* v_dst = k_dst + KV_BYTES;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = lane + 32 * u;
+                if (i >= pages_per_tile) break;
+                const int64_t row_k = (int64_t)my_page[u] * rows_per_page + (int64_t)g * a.page_size;
+                const int64_t row_v = row_k + (int64_t)a.G * a.page_size;
+                for (int c = 0; c < NCB; ++c) {
+                    atc_tma_2d(k_dst + c * SUB_BYTES + i * a.page_size * 128, &map_kv, &kv_full[s],
+                               c * 64, (int)row_k);
+                    atc_tma_2d(v_dst + c * SUB_BYTES + i * a.page_size * 128, &map_kv, &kv_full[s],
+                               c * 64, (int)row_v);
                 }
             }
         }
@@ -309,20 +343,27 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             if (!ok) break;
             atc_fence_after();
             const int kt = t * TKV;
-            // pass 1: the row's maximum over the tile (scaled to log2 units, masked)
+            // pass 1: the row's maximum over the tile.  Raw scores: the scale is positive, so it
+            // commutes with the maximum and is folded into the exponent below.  Only tiles that
+            // reach past the row's own position (or rows that do not exist) need the mask.
             float sv[4][32];
-            float mx = -INFINITY;
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                atc_ld32(lane_base + S_COL + c * 32, sv[c]);
+            for (int c = 0; c < 4; ++c) atc_ld32_nowait(lane_base + S_COL + c * 32, sv[c]);
+            atc_ld_wait();
+            const bool masked = !valid || kt + TKV - 1 > qpos;
+            if (masked) {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const int kpos = kt + c * 32 + i;
-                    const float x = (valid && kpos <= qpos) ? sv[c][i] * a.scale_log2 : -INFINITY;
-                    sv[c][i] = x;
-                    mx = fmaxf(mx, x);
-                }
+                for (int c = 0; c < 4; ++c)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (!valid || kt + c * 32 + i > qpos) sv[c][i] = -INFINITY;
             }
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+#pragma unroll
+                for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], sv[c][i]);
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * a.scale_log2;
             // the reference maximum moves only when it must (first keys, or growth beyond 2^8)
             float corr = 1.f;
             if (mx > m_ref + RESCALE_THRESHOLD || (m_ref == -INFINITY && mx != -INFINITY)) {
@@ -347,21 +388,24 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                     }
                 }
             }
-            // pass 2: probabilities, their sum, P as bfloat16 pairs
+            // pass 2: probabilities p = 2^(s * scale - m_ref) (one fused multiply-add and one
+            // exponential each; a masked score is -inf and gives 0), their sum, P as bfloat16
+            const float neg_ref = m_ref == -INFINITY ? 0.f : -m_ref;   // all masked: p = 0 anyway
+            float l4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
                 uint32_t w[32];
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
                     const int k0 = c * 64 + 2 * i;           // keys k0, k0 + 1 of the tile
-                    const float x0 = sv[k0 / 32][k0 % 32], x1 = sv[(k0 + 1) / 32][(k0 + 1) % 32];
-                    const float p0 = x0 == -INFINITY ? 0.f : exp2f(x0 - m_ref);
-                    const float p1 = x1 == -INFINITY ? 0.f : exp2f(x1 - m_ref);
-                    l_sum += p0 + p1;
+                    const float p0 = exp2f(fmaf(sv[k0 / 32][k0 % 32], a.scale_log2, neg_ref));
+                    const float p1 = exp2f(fmaf(sv[(k0 + 1) / 32][(k0 + 1) % 32], a.scale_log2, neg_ref));
+                    l4[i & 3] += p0 + p1;
                     w[i] = atc_pack(p0, p1);
                 }
                 atc_st32(lane_base + P_COL + c * 32, w);
             }
+            l_sum += (l4[0] + l4[1]) + (l4[2] + l4[3]);
             atc_st_wait();
             atc_fence_before();
             __syncwarp();

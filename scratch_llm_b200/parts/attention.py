@@ -21,6 +21,11 @@ from .linear import Linear
 from .registry import register_mixer
 
 
+#: rows with several new tokens go to the tcgen05 attention kernel when the longest of them
+#: fills at least one of its 128-query tiles (packed queries = new tokens x group size)
+TC_MIN_PACKED_QUERIES = 128
+
+
 def decode_splits(base_ctas: int, context: int, slots: int = 3 * 148) -> int:
     """How many CTAs share the keys of one (row, kv head) in the split decode kernel: the count
     that minimises waves x (key tiles per CTA + fixed cost), a function of the batch's shape
@@ -99,8 +104,15 @@ class GQAttention(Mixer):
         common = (q, cache.pages, cache.block_table, cache.page_size, batch.row_start,
                   batch.row_pos0, out)
         if batch.n_multi:
-            ops.attention_mma(*common, batch.multi_rows, batch.n_multi, batch.max_new_multi,
-                              H, G, hd, self.scale, self.window, split=False)
+            if ops.attention_tc_supports(H, G, hd, cache.page_size, self.window) \
+                    and batch.max_new_multi * (H // G) >= TC_MIN_PACKED_QUERIES:
+                # tcgen05 kernel: scores, probabilities and output in tensor memory
+                ops.attention_tc(*common, batch.multi_rows, batch.n_multi, batch.max_new_multi,
+                                 H, G, hd, self.scale)
+            else:
+                ops.attention_mma(*common, batch.multi_rows, batch.n_multi,
+                                  batch.max_new_multi, H, G, hd, self.scale, self.window,
+                                  split=False)
         if batch.n_single:
             n_splits = decode_splits(batch.n_single * G * (-(-(H // G) // 16)),
                                      batch.context_bucket if self.window is None
