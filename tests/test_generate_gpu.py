@@ -56,14 +56,15 @@ def test_greedy_generation_matches_plain(name, dtype, slack, model_dirs):
         assert_greedy_consistent(cfg, w, prompts[1], alone, slack)
 
 
-def test_long_decoding(model_dirs):
+@pytest.mark.parametrize("dtype, slack", [("float32", 2e-5), ("bfloat16", 6e-2)])
+def test_long_decoding(dtype, slack, model_dirs):
     from scratch_llm_b200 import LLM, SamplingParams
-    cfg, w = plain_weights(model_dirs["C"], "float32")
+    cfg, w = plain_weights(model_dirs["C"], dtype)
     prompt = prompts_for(331, [21])[0]
-    llm = LLM(model_dirs["C"], dtype="float32", max_tokens=640, page_size=16)
+    llm = LLM(model_dirs["C"], dtype=dtype, max_tokens=640, page_size=16)
     got = llm.generate(prompt, SamplingParams(temperature=0.0, max_tokens=600))
     assert len(got) == 600
-    assert_greedy_consistent(cfg, w, prompt, got, 2e-5)
+    assert_greedy_consistent(cfg, w, prompt, got, slack)
 
 
 @pytest.mark.parametrize("dtype, tol", [("float32", dict(rtol=2e-5, atol=5e-6)),

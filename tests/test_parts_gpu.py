@@ -111,6 +111,55 @@ def test_attention_part_in_portions(dtype, window):
         assert any(p < 0 for p in cache.table_of("r", 0))  # pages behind the window went back
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_block_part(dtype):
+    """The pre-norm arrangement alone: x + Mixer(Norm(x)), then x + FeedForward(Norm(x)), with
+    the last delta handed on as pending."""
+    from scratch_llm_b200.cache import CacheManager
+    from scratch_llm_b200.engine.batch import BatchStager, RowInput, build_batch
+    from scratch_llm_b200.parts import BLOCKS, CacheView
+    from scratch_llm_b200.parts.attention import GQAttention
+    from scratch_llm_b200.parts.feed_forward import SwiGLU
+    from scratch_llm_b200.parts.norm import RMSNorm
+    from scratch_llm_b200.parts.position import Rotary
+    d, H, G, hd, F, S, eps = 96, 4, 2, 16, 136, 21, 1e-4
+    w = {"input_layernorm.weight": rand(d, seed=1) * 0.1 + 1,
+         "post_attention_layernorm.weight": rand(d, seed=2) * 0.1 + 1,
+         "self_attn.q_proj.weight": rand(H * hd, d, seed=3, scale=0.1),
+         "self_attn.k_proj.weight": rand(G * hd, d, seed=4, scale=0.1),
+         "self_attn.v_proj.weight": rand(G * hd, d, seed=5, scale=0.1),
+         "self_attn.o_proj.weight": rand(d, H * hd, seed=6, scale=0.1),
+         "mlp.gate_proj.weight": rand(F, d, seed=7, scale=0.1),
+         "mlp.up_proj.weight": rand(F, d, seed=8, scale=0.1),
+         "mlp.down_proj.weight": rand(d, F, seed=9, scale=0.1)}
+    c = ctx(dtype)
+    att = GQAttention(d, H, G, hd, scale=1 / math.sqrt(hd))
+    att.load({k.split(".", 1)[1]: v for k, v in w.items() if k.startswith("self_attn")}, c)
+    ff = SwiGLU(d, F)
+    ff.load({k.split(".", 1)[1]: v for k, v in w.items() if k.startswith("mlp")}, c)
+    n1, n2 = RMSNorm(d, eps), RMSNorm(d, eps)
+    n1.load({"weight": w["input_layernorm.weight"]}, c)
+    n2.load({"weight": w["post_attention_layernorm.weight"]}, c)
+    rot = Rotary(hd, 10000.0, 64)
+    rot.load({}, c)
+    block = BLOCKS["pre_norm"](att, ff, n1, n2, rot)
+    cache = CacheManager([att.kv_spec()], [None], 8, 8, 1, dtype=dtype, device="cuda")
+    cache.admit("r")
+    cache.reserve("r", S)
+    batch = build_batch(cache, BatchStager(torch.device("cuda")), [RowInput("r", [0] * S)], 4, 64)
+    pages, g = cache.entry_pages(0)
+    x, pending_in = rand(S, d, seed=10), rand(S, d, seed=11, scale=0.3).to(dtype)
+    resid = x.cuda()
+    pending = block.forward(resid, pending_in.cuda(), batch,
+                            CacheView(pages=pages, block_table=batch.block_tables[g], page_size=8), True)
+    tw = {f"model.layers.0.{k}": v.to(dtype).float() for k, v in w.items()}
+    cfgd = dict(num_attention_heads=H, num_key_value_heads=G, head_dim=hd, hidden_size=d, rms_norm_eps=eps)
+    cos, sin = P.rope_tables(hd, 64, 10000.0)
+    want, _ = P.block(x + pending_in.float(), torch.arange(S), tw, 0, cfgd, cos, sin)
+    got = resid.cpu() + pending.cpu().float()     # the stream plus the delta still pending
+    torch.testing.assert_close(got, want, **TOL[dtype])
+
+
 # ----------------------------------------------------------------- a toy mixer with state
 
 def make_toy():
