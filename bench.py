@@ -24,7 +24,7 @@ from pathlib import Path
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
-# BASELINE.json configs[2]: Llama-3-8B sizes
+# the headline configuration: Llama-3-8B layer sizes
 SIZES = dict(hidden_size=4096, num_hidden_layers=32, num_attention_heads=32,
              num_key_value_heads=8, head_dim=128, intermediate_size=14336, vocab_size=128256,
              rope_theta=500000.0, rms_norm_eps=1e-5, tie_word_embeddings=False,

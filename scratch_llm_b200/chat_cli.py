@@ -7,10 +7,10 @@ the reply.
         [--temperature 0.0] [--top-p 1.0] [--seed N] [--dtype bfloat16|float32]
         [--random-weights CONFIG.json]
 
-``--model`` takes the place of the reference's ``--ckpt`` (a model folder instead of a pickle);
-``--data-dir`` is the folder with ``tokenizer.json`` as in the reference (default: the model
-folder) and ``--max-tokens`` keeps its meaning and default; the reference's ``--device`` is
-gone because the engine runs on the GPU only.  Without a tokenizer (a random-weights folder) the
+``--model`` takes the place of the reference's ``--ckpt`` (a model folder instead of a pickle;
+``--ckpt`` is accepted as another spelling); ``--data-dir`` is the folder with
+``tokenizer.json`` as in the reference (default: the model folder) and ``--max-tokens`` keeps
+its meaning and default; ``--device`` is accepted but can only be ``cuda``.  Without a tokenizer (a random-weights folder) the
 loop reads and prints token ids.  ``--random-weights CONFIG.json`` first writes ``--model`` from
 that configuration with seeded random weights.
 
@@ -133,7 +133,11 @@ def repl(llm, tokenizer, args) -> None:
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description="Chat with a model folder on one B200.")
-    ap.add_argument("--model", required=True, help="folder with config.json and model.safetensors")
+    ap.add_argument("--model", "--ckpt", dest="model", required=True,
+                    help="folder with config.json and model.safetensors (--ckpt, the reference's "
+                         "name for its checkpoint option, is accepted too)")
+    ap.add_argument("--device", default="cuda",
+                    help="kept from the reference's command line; only 'cuda' is possible")
     ap.add_argument("--data-dir", default=None, help="dir with tokenizer.json (default: --model)")
     ap.add_argument("--max-tokens", type=int, default=256)
     ap.add_argument("--temperature", type=float, default=0.0)
@@ -143,6 +147,8 @@ def main(argv=None) -> int:
     ap.add_argument("--random-weights", metavar="CONFIG.json", default=None,
                     help="write --model from this configuration with seeded random weights first")
     args = ap.parse_args(argv)
+    if not str(args.device).startswith("cuda"):
+        ap.error("this engine runs on a CUDA device only (--device cuda)")
 
     if args.random_weights:
         from .config import config_from_dict
