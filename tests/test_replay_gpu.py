@@ -122,3 +122,60 @@ def test_long_prompt_takes_the_fused_tensor_core_path(tmp_path):
         got = T.run_in_process(runner, steps)
     assert ops.gemm_tc_error() == 0
     compare(got, want, "bfloat16")
+
+
+@pytest.fixture(scope="module")
+def llama8b_layers(tmp_path_factory):
+    """Two layers at Llama-3-8B layer sizes (width 4096, 32 heads over 8 kv heads of size 128,
+    feed-forward 14336) with a smaller vocabulary that is no power of two; weights stored in
+    bfloat16, so both precisions start from the same values."""
+    from scratch_llm_b200.config import config_from_dict
+    from scratch_llm_b200.weights import write_random_model
+    raw = dict(architectures=["LlamaForCausalLM"], hidden_size=4096, num_hidden_layers=2,
+               num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+               intermediate_size=14336, vocab_size=16001, rope_theta=500000.0, rms_norm_eps=1e-5,
+               tie_word_embeddings=False, max_position_embeddings=2048, torch_dtype="bfloat16")
+    d = write_random_model(config_from_dict(raw), tmp_path_factory.mktemp("llama8b_layers"), 8)
+    cfg, w = P.read_model_dir(d)
+    reqs = T.make_requests(cfg["vocab_size"], [900, 70], seed=21)
+    want = {rid: P.forward(cfg, w, toks) for rid, toks in reqs.items()}
+    return d, reqs, want
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_llama8b_layer_sizes(dtype, llama8b_layers):
+    """The kernels at the sizes they are tuned for: the long request's prompt runs through the
+    tcgen05 attention and the fused tcgen05 gate/up product (bfloat16), its last tokens and the
+    short request through the decode kernels, mixed in one batch."""
+    from scratch_llm_b200.kernels import ops
+    d, reqs, want = llama8b_layers
+    long_id, short_id = list(reqs)
+    a, b = reqs[long_id], reqs[short_id]
+    steps = [
+        {"step": 0, "entries": [{"id": long_id, "tokens": a[:850], "want": [0, 400, 849]}], "end": []},
+        {"step": 1, "entries": [{"id": long_id, "tokens": a[850:880], "want": list(range(30))},
+                                {"id": short_id, "tokens": b[:40], "want": [39]}], "end": []}]
+    for i in range(20):   # both requests decode side by side
+        steps.append({"step": 2 + i, "entries": [
+            {"id": long_id, "tokens": a[880 + i:881 + i], "want": [0]},
+            {"id": short_id, "tokens": b[40 + i:41 + i], "want": [0]}], "end": []})
+    steps.append({"step": 22, "entries": [{"id": short_id, "tokens": b[60:], "want": list(range(10))}],
+                  "end": [long_id, short_id]})
+    runner = make_runner(d, dtype, 16, 1024, max_requests=2)
+    with torch.no_grad():
+        got = T.run_in_process(runner, steps)
+    assert ops.gemm_tc_error() == 0 and ops.attention_tc_error(128) == 0
+    # 32-bit: at these reduction lengths (4096 and 14336) the plain implementation itself moves
+    # by 1.5e-5 between one and eight CPU threads and is 1.1e-5 away from its float64 run, on
+    # logits up to 6.4; the bound leaves room for both sides' rounding and no more
+    # bfloat16: with reductions over 4096 and 14336 rounded operands every path of the engine
+    # (tensor-core prefill, library product, streaming decode kernels, token by token) lands
+    # 1.2-2.0 % of the row's largest logit away from the plain 32-bit model, the same positions
+    # being worst on every path: that is the precision of the format at this width.  The bound
+    # is twice the worst seen.
+    for (rid, pos), row in sorted(got.items()):
+        ref = want[rid][pos]
+        tol = dict(rtol=2e-4, atol=6e-5) if dtype == "float32" else \
+            dict(rtol=3e-2, atol=0.04 * float(ref.abs().max()))
+        torch.testing.assert_close(row, ref, **tol,
+                                   msg=lambda m: f"request {rid} position {pos}: {m}")
