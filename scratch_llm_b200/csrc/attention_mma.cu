@@ -21,6 +21,10 @@
 //   split (SPLIT = true):  BQ = 16; the 4 warps share the 16 packed queries and each takes
 //                          16 keys of a tile; the key range is also split over `n_splits`
 //                          CTAs whose partial results a merge kernel combines.  For decode.
+//   column split (attn_decode_cs_kernel, head sizes that are multiples of 64): as split, but
+//                          the probabilities of a tile meet in shared memory and each warp
+//                          accumulates a quarter of the output columns over all 64 keys.
+//                          The launcher uses it in place of split where it applies.
 // Compiled once per head size: -DSLLM_HEAD_DIM=<multiple of 16, at most 256>.
 #include "common.cuh"
 
@@ -393,6 +397,267 @@ __global__ void __launch_bounds__(THREADS, SPLIT ? 3 : 2) attn_mma_kernel(const 
     }
 }
 
+// Decode variant for head sizes that are multiples of 64.  Like the split kernel the four warps
+// of a CTA share 16 packed queries and each computes the scores of 16 keys of a tile; but then
+// the probabilities meet in shared memory and each warp accumulates ITS QUARTER OF THE OUTPUT
+// COLUMNS over all 64 keys.  A warp therefore holds 16 x HD/4 of the output instead of 16 x HD
+// (a quarter of the accumulator registers and of the rescaling work), the running maximum is
+// common to the CTA, and no merge of four partial outputs is needed at the end.  The kernel
+// is bound by instruction issue, and this is about a third of the split kernel's instructions.
+#if SLLM_HEAD_DIM % 64 == 0
+constexpr int CS_LDP = BKV + 8;        // row stride of the probability tile (elements)
+constexpr int CS_OC = HD / NWARP;      // output columns per warp
+constexpr int CS_OT = CS_OC / 8 > 0 ? CS_OC / 8 : 1;   // 8-wide output tiles per warp
+
+__global__ void __launch_bounds__(THREADS, 3) attn_decode_cs_kernel(const AttnArgs a) {
+    using M = Mode<true>;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* Qs = reinterpret_cast<bf16*>(smem_raw);
+    bf16* Ks = Qs + M::BQ * LDS;
+    bf16* Vs = Ks + M::NSTAGE * BKV * LDS;
+    __shared__ long long key_off[2][BKV];
+    // The probability tile takes the place of the queries once they are in registers (three
+    // CTAs fit on an SM only if the static part stays small); the row sums reuse the maxima's.
+    bf16* Ps = Qs;
+    static_assert(CS_LDP <= LDS, "the probability tile must fit in the query tile");
+    __shared__ float red_max[NWARP][16];
+    float (*red_l)[16] = red_max;
+
+    pdl_wait();
+    pdl_trigger();
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n_splits = a.n_splits;
+    const int q_tile = (int)(gridDim.x / n_splits) - 1 - (int)(blockIdx.x / n_splits);
+    const int split = blockIdx.x % n_splits;
+    const int r = a.row_list ? a.row_list[blockIdx.y] : blockIdx.y;
+    const int g = blockIdx.z;
+    const int GS = a.H / a.G;
+    const int t0 = a.row_start[r];
+    const int n_new = a.row_start[r + 1] - t0;
+    const int pos0 = a.row_pos0[r];
+    const int n_packed = n_new * GS;
+    const int q0 = q_tile * M::BQ;
+    if (q0 >= n_packed) return;
+    const int first_pos = pos0 + q0 / GS;
+    const int last_pos = pos0 + min(n_packed - 1, q0 + M::BQ - 1) / GS;
+    int k_lo = 0;
+    if (a.window > 0) k_lo = max(0, first_pos - a.window + 1) / BKV * BKV;
+    const int n_tiles = (last_pos - k_lo) / BKV + 1;
+    const int per_split = (n_tiles + n_splits - 1) / n_splits;
+    const int tile_begin = split * per_split;
+    const int tile_end = min(n_tiles, tile_begin + per_split);
+
+    for (int idx = tid; idx < M::BQ * CHUNKS; idx += THREADS) {
+        const int i = idx / CHUNKS, c = idx - i * CHUNKS;
+        const int p = q0 + i;
+        const bool valid = p < n_packed;
+        const int tok = valid ? p / GS : 0, j = valid ? p - tok * GS : 0;
+        const bf16* src = a.q + (int64_t)(t0 + tok) * a.q_stride + (int64_t)(g * GS + j) * HD + c * 8;
+        cp_async16(Qs + i * LDS + c * 8, src, valid);
+    }
+    cp_async_commit();
+
+    const int64_t v_off = (int64_t)a.G * a.page_size * HD;
+    auto locate_tile = [&](int tile, int slot) {
+        if (tid < BKV) {
+            const int kpos = k_lo + tile * BKV + tid;
+            long long off = -1;
+            if (tile < tile_end && kpos <= last_pos) {
+                const int page = a.block_table[(int64_t)r * a.table_stride + kpos / a.page_size];
+                if (page >= 0)
+                    off = (((long long)page * 2 * a.G + g) * a.page_size + kpos % a.page_size) * HD;
+            }
+            key_off[slot][tid] = off;
+        }
+    };
+    constexpr int PIECES = BKV * CHUNKS / THREADS;
+    auto load_tile = [&](int tile, int stage, int slot) {
+        bf16* ks = Ks + stage * BKV * LDS;
+        bf16* vs = Vs + stage * BKV * LDS;
+#pragma unroll
+        for (int i = 0; i < PIECES; ++i) {
+            const int idx = tid + i * THREADS;
+            const int j = idx / CHUNKS, c = idx - j * CHUNKS;
+            const long long off = key_off[slot][j];
+            const bool ok = off >= 0;
+            const bf16* src = ok ? a.pages + off + c * 8 : a.pages;
+            cp_async16(ks + j * LDS + c * 8, src, ok);
+            cp_async16(vs + j * LDS + c * 8, ok ? src + v_off : src, ok);
+        }
+    };
+    locate_tile(tile_begin, 0);
+    __syncthreads();
+    if (tile_begin < tile_end) load_tile(tile_begin, 0, 0);
+    cp_async_commit();
+    locate_tile(tile_begin + 1, 1);
+    cp_async_wait<1>();
+    __syncthreads();
+
+    uint32_t qf[KSTEPS][4];
+#pragma unroll
+    for (int ks = 0; ks < KSTEPS; ++ks)
+        ldsm_x4(qf[ks], Qs + (lane & 15) * LDS + ks * 16 + (lane >> 4) * 8);
+    const int key_lo_w = warp * M::WKEYS;
+    int qpos[2];
+    bool qvalid[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int p = q0 + (lane >> 2) + 8 * h;
+        qvalid[h] = p < n_packed;
+        qpos[h] = pos0 + (qvalid[h] ? p / GS : 0);
+    }
+    const bool no_window = a.window <= 0;
+    const int first_q_pos = pos0 + min(q0, n_packed - 1) / GS;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    float o[CS_OT][4];
+#pragma unroll
+    for (int dn = 0; dn < CS_OT; ++dn)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[dn][e] = 0.f;
+
+    for (int tile = tile_begin; tile < tile_end; ++tile) {
+        const int stage = (tile - tile_begin) & 1;
+        if (tile + 1 < tile_end) load_tile(tile + 1, stage ^ 1, stage ^ 1);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        locate_tile(tile + 2, stage);
+        const bf16* ks_s = Ks + stage * BKV * LDS + key_lo_w * LDS;
+        const bf16* vs_s = Vs + stage * BKV * LDS;
+        const int kt = k_lo + tile * BKV + key_lo_w;
+
+        // scores of this warp's 16 keys
+        float s[2][4];
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) s[nt][e] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks) {
+            uint32_t b[4];
+            ldsm_x4(b, ks_s + ((lane & 7) + (lane >> 4) * 8) * LDS + ks * 16 + ((lane >> 3) & 1) * 8);
+            mma_bf16(s[0], qf[ks], b[0], b[1]);
+            mma_bf16(s[1], qf[ks], b[2], b[3]);
+        }
+        float mx[2] = {-INFINITY, -INFINITY};
+        if (no_window && kt + M::WKEYS - 1 <= first_q_pos) {
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    s[nt][e] *= a.scale_log2;
+                    mx[e >> 1] = fmaxf(mx[e >> 1], s[nt][e]);
+                }
+        } else {
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int h = e >> 1;
+                    const int kpos = kt + nt * 8 + (lane & 3) * 2 + (e & 1);
+                    const bool ok = qvalid[h] && kpos <= qpos[h] &&
+                                    (a.window <= 0 || kpos > qpos[h] - a.window);
+                    s[nt][e] = ok ? s[nt][e] * a.scale_log2 : -INFINITY;
+                    mx[h] = fmaxf(mx[h], s[nt][e]);
+                }
+        }
+        mx[0] = quad_max(mx[0]);
+        mx[1] = quad_max(mx[1]);
+        if ((lane & 3) == 0) {
+            red_max[warp][lane >> 2] = mx[0];
+            red_max[warp][(lane >> 2) + 8] = mx[1];
+        }
+        __syncthreads();   // the four warps' maxima of this tile are in place
+        float corr[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int row = (lane >> 2) + 8 * h;
+            const float mt = fmaxf(fmaxf(red_max[0][row], red_max[1][row]),
+                                   fmaxf(red_max[2][row], red_max[3][row]));
+            const float m_new = fmaxf(m_run[h], mt);
+            corr[h] = m_new == -INFINITY ? 1.f : exp2f(m_run[h] - m_new);
+            m_run[h] = m_new;
+            l_run[h] *= corr[h];
+        }
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+            float p[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int h = e >> 1;
+                p[e] = m_run[h] == -INFINITY ? 0.f : exp2f(s[nt][e] - m_run[h]);
+                l_run[h] += p[e];
+            }
+            bf16* dst = Ps + (lane >> 2) * CS_LDP + key_lo_w + nt * 8 + (lane & 3) * 2;
+            *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(p[0], p[1]);
+            *reinterpret_cast<__nv_bfloat162*>(dst + 8 * CS_LDP) = __floats2bfloat162_rn(p[2], p[3]);
+        }
+        if (corr[0] != 1.f || corr[1] != 1.f) {   // same in every thread of a row's quad
+#pragma unroll
+            for (int dn = 0; dn < CS_OT; ++dn) {
+                o[dn][0] *= corr[0]; o[dn][1] *= corr[0];
+                o[dn][2] *= corr[1]; o[dn][3] *= corr[1];
+            }
+        }
+        __syncthreads();   // the probabilities of all 64 keys are in place
+        // this warp's columns of the output over all 64 keys
+#pragma unroll
+        for (int kk = 0; kk < BKV / 16; ++kk) {
+            uint32_t pa[4];
+            ldsm_x4(pa, Ps + (lane & 15) * CS_LDP + kk * 16 + (lane >> 4) * 8);
+#pragma unroll
+            for (int dn = 0; dn < CS_OT; dn += 2) {
+                uint32_t b[4];
+                ldsm_x4_trans(b, vs_s + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDS +
+                                     warp * CS_OC + dn * 8 + (lane >> 4) * 8);
+                mma_bf16(o[dn], pa, b[0], b[1]);
+                mma_bf16(o[dn + 1], pa, b[2], b[3]);
+            }
+        }
+        __syncthreads();   // stage, probabilities and maxima are reused by the next tile
+    }
+    cp_async_wait<0>();
+
+    // the sum of the probabilities over the four warps' keys
+    l_run[0] = quad_sum(l_run[0]);
+    l_run[1] = quad_sum(l_run[1]);
+    if ((lane & 3) == 0) {
+        red_l[warp][lane >> 2] = l_run[0];
+        red_l[warp][(lane >> 2) + 8] = l_run[1];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int row = (lane >> 2) + 8 * h;
+        const int p = q0 + row;
+        if (p >= n_packed) continue;
+        const float l_tot = (red_l[0][row] + red_l[1][row]) + (red_l[2][row] + red_l[3][row]);
+        const float inv = l_tot > 0.f ? 1.0f / l_tot : 0.f;
+        const int tok = p / GS, j = p - tok * GS;
+        const int col0 = warp * CS_OC + (lane & 3) * 2;
+        if (n_splits == 1) {
+            bf16* dst = a.out + (int64_t)(t0 + tok) * a.out_stride + (int64_t)(g * GS + j) * HD + col0;
+#pragma unroll
+            for (int dn = 0; dn < CS_OT; ++dn)
+                *reinterpret_cast<__nv_bfloat162*>(dst + dn * 8) =
+                    __floats2bfloat162_rn(o[dn][2 * h] * inv, o[dn][2 * h + 1] * inv);
+        } else {
+            const int64_t qh = (int64_t)(t0 + tok) * a.H + g * GS + j;
+            float* dst = a.part_o + (qh * n_splits + split) * HD + col0;
+#pragma unroll
+            for (int dn = 0; dn < CS_OT; ++dn) {
+                dst[dn * 8] = o[dn][2 * h] * inv;
+                dst[dn * 8 + 1] = o[dn][2 * h + 1] * inv;
+            }
+            if (warp == 0 && (lane & 3) == 0)
+                a.part_lse[qh * n_splits + split] =
+                    l_tot > 0.f ? m_run[h] + log2f(l_tot) : -INFINITY;
+        }
+    }
+}
+
+#endif  // SLLM_HEAD_DIM % 64 == 0
+
 // Combines the partial results of the splits: o = sum_s 2^(lse_s - m) o_s / sum_s 2^(lse_s - m).
 // grid (listed rows, H); a block walks the row's tokens.
 __global__ void attn_merge_kernel(const float* __restrict__ part_o,
@@ -482,7 +747,14 @@ SLLM_EXPORT int sllm_attn_mma(const void* q, int64_t q_stride, const void* pages
                              (int)smem);
     if (e != cudaSuccess) return (int)e;
     dim3 grid((((int64_t)max_new * GS + 15) / 16) * n_splits, n_list, G);
+#if SLLM_HEAD_DIM % 64 == 0
+    e = cudaFuncSetAttribute(attn_decode_cs_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    e = sllm_launch_pdl(attn_decode_cs_kernel, grid, dim3(THREADS), smem, stream, a);
+#else
     e = sllm_launch_pdl(attn_mma_kernel<true>, grid, dim3(THREADS), smem, stream, a);
+#endif
     if (e != cudaSuccess) return (int)e;
     if (n_splits > 1) {
         dim3 mgrid(n_list, H);
