@@ -165,7 +165,8 @@ def paged_cache(k, v, page_size, n_pages, seed, dtype):
 
 
 ATTN_SHAPES = [(4, 2, 16, 16, None), (6, 3, 48, 8, None), (8, 1, 128, 32, None),
-               (5, 5, 80, 4, None), (4, 2, 16, 16, 37), (6, 2, 48, 8, 5), (40, 2, 16, 16, None)]
+               (5, 5, 80, 4, None), (4, 2, 16, 16, 37), (6, 2, 48, 8, 5), (40, 2, 16, 16, None),
+               (8, 2, 64, 16, 37), (6, 3, 128, 8, 70), (4, 2, 192, 16, None)]
 # rows: (cached before this step, new tokens): a whole prompt, portions, single tokens
 ATTN_ROWS = [(0, 70), (33, 1), (64, 18), (100, 2), (0, 1), (255, 1), (17, 47), (63, 1), (64, 1)]
 FAR = 5  # the row with 255 cached keys
