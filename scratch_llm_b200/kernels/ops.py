@@ -34,6 +34,7 @@ CORE_LIBRARIES: dict[str, tuple[tuple[str, ...], tuple[str, ...]]] = {
     "sllm_sampling": (("sampling.cu",), ()),
     "sllm_gemv_mma": (("gemv_mma.cu",), ()),
     "sllm_gemm_tcgen05": (("gemm_tcgen05.cu",), ()),
+    "sllm_gemv_tma": (("gemv_tma.cu",), ()),
 }
 
 
@@ -232,6 +233,73 @@ def gemv_mma(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool =
         c_int64(w.stride(0)), c_int64(out.stride(0)), c_int(int(swiglu)),
         c_int(_code(out.dtype)), _stream()), "gemv_mma")
     return out
+
+
+#: workspaces of the persistent small-batch product, per device: partial sums and tickets.  A
+#: workspace that has been handed to a launch is never freed (a captured CUDA graph may hold its
+#: address), so a larger one is made beside it when a wider matrix comes.
+_gemv_workspaces: dict[int, list[torch.Tensor]] = {}
+_sm_counts: dict[int, int] = {}
+
+
+def _sm_count(device: torch.device | int | None = None) -> int:
+    index = device.index if isinstance(device, torch.device) else device
+    if index is None:
+        index = torch.cuda.current_device()
+    if index not in _sm_counts:
+        _sm_counts[index] = torch.cuda.get_device_properties(index).multi_processor_count
+    return _sm_counts[index]
+
+
+def gemv_tma_supports(m: int, n: int, k: int, swiglu: bool = False) -> bool:
+    """Whether :func:`gemv_tma` takes a product of these sizes (on the current device)."""
+    return bool(_core("sllm_gemv_tma").sllm_gemv_tma_supports(
+        c_int(m), c_int(n), c_int(k), c_int(int(swiglu)), c_int(_sm_count())))
+
+
+def gemv_tma_reserve(n: int, k: int, swiglu: bool, device: torch.device) -> torch.Tensor:
+    """A zeroed workspace on ``device`` that is large enough for a weight [n, k].  Called when a
+    model is built, so that no step allocates it."""
+    lib = _core("sllm_gemv_tma")
+    lib.sllm_gemv_tma_workspace_bytes.restype = ctypes.c_int64
+    need = int(lib.sllm_gemv_tma_workspace_bytes(c_int(n), c_int(k), c_int(int(swiglu)),
+                                                 c_int(_sm_count(device))))
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    held = _gemv_workspaces.setdefault(index, [])
+    if not held or held[-1].numel() < need:
+        held.append(torch.zeros(need, dtype=torch.uint8, device=device))
+    return held[-1]
+
+
+def gemv_tma(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool = False
+             ) -> torch.Tensor:
+    """out[M, N] = x[M, K] @ w[N, K]^T for M <= 8 tokens by the persistent kernel that streams w
+    through shared memory with bulk copies (one CTA per SM, four ranges of K whose partial sums
+    the last CTA of a row tile adds in a fixed order).  ``swiglu`` as in :func:`gemv_mma`.
+    Launches share one workspace per device and must be ordered by their stream."""
+    _need(x, torch.bfloat16, "x", contiguous=False)
+    _need(w, torch.bfloat16, "w", contiguous=False)
+    _need(out, None, "out", contiguous=False)
+    (m, k), (n, k2) = x.shape, w.shape
+    n_out = n // 2 if swiglu else n
+    if k != k2 or out.shape != (m, n_out) or x.stride(1) != 1 or w.stride(1) != 1 \
+            or out.stride(1) != 1:
+        raise KernelError(f"gemv shapes/strides: x {list(x.shape)}, w {list(w.shape)}, "
+                          f"out {list(out.shape)}")
+    if not gemv_tma_supports(m, n, k, swiglu) or x.stride(0) % 8 or w.stride(0) % 8:
+        raise KernelError(f"gemv_tma takes 1 to 8 tokens, K a multiple of 256 and at least 1024, "
+                          f"and rows that are multiples of 8 elements; got M={m}, N={n}, K={k}")
+    workspace = gemv_tma_reserve(n, k, swiglu, x.device)
+    _check(_core("sllm_gemv_tma").sllm_gemv_tma(
+        _ptr(x), _ptr(w), _ptr(out), _ptr(workspace), c_int(m), c_int(n), c_int(k),
+        c_int64(x.stride(0)), c_int64(w.stride(0)), c_int64(out.stride(0)), c_int(int(swiglu)),
+        c_int(_code(out.dtype)), c_int(_sm_count(x.device)), _stream()), "gemv_tma")
+    return out
+
+
+def gemv_tma_error() -> int:
+    """The first error a gemv_tma kernel recorded since the last call (0 = none)."""
+    return int(_core("sllm_gemv_tma").sllm_gemv_tma_error())
 
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool = False

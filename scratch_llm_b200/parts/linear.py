@@ -28,6 +28,15 @@ class Linear:
             raise ValueError("a Linear weight is a contiguous [out, in] matrix")
         self.weight = weight
         self.out_features, self.in_features = weight.shape
+        # the persistent small-batch kernel takes this matrix (plain and as [gate; up]): its
+        # workspace is made now, so that no step allocates it
+        self._persistent = self._persistent_swiglu = False
+        if weight.dtype == torch.bfloat16 and weight.is_cuda:
+            n, k = self.out_features, self.in_features
+            self._persistent = ops.gemv_tma_supports(1, n, k, False)
+            self._persistent_swiglu = n % 2 == 0 and ops.gemv_tma_supports(1, n, k, True)
+            if self._persistent or self._persistent_swiglu:
+                ops.gemv_tma_reserve(n, k, False, weight.device)
 
     def __call__(self, x: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
         w = self.weight
@@ -40,6 +49,9 @@ class Linear:
             return ops.gemm_simt(x, w, out)
         # every CTA of the streaming kernel re-reads all activations, which costs as much as the
         # weights once the output is very wide and several tokens are in flight
+        if self._persistent and x.shape[0] <= SMALL_BATCH and x.stride(0) % 8 == 0:
+            out = torch.empty((x.shape[0], self.out_features), dtype=out_dtype, device=x.device)
+            return ops.gemv_tma(x, w, out)
         streams = x.shape[0] <= SMALL_BATCH and (x.shape[0] <= 2 or self.out_features <= 65536)
         if streams and self.in_features % 8 == 0 and x.stride(0) % 8 == 0:
             out = torch.empty((x.shape[0], self.out_features), dtype=out_dtype, device=x.device)
@@ -57,6 +69,8 @@ class Linear:
         fits = (w.dtype == torch.bfloat16 and self.in_features % 8 == 0
                 and x.stride(0) % 8 == 0)
         if fits and x.shape[0] <= SMALL_BATCH:
+            if self._persistent_swiglu:
+                return ops.gemv_tma(x, w, out, swiglu=True)
             return ops.gemv_mma(x, w, out, swiglu=True)
         if fits and x.shape[0] >= FUSED_GEMM_MIN_TOKENS and half % 8 == 0:
             # tcgen05 kernel with the activation in its epilogue: the [tokens, 2F] intermediate

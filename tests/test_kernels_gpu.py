@@ -119,6 +119,47 @@ def test_gemv_streams_weights_once(ops, m, n, k):
                                    **TOL["bfloat16"])
 
 
+@pytest.mark.parametrize("m, n, k", [(1, 16, 1024), (3, 100, 1536), (8, 4096 + 8, 4096),
+                                     (5, 512, 14336), (8, 6144, 4096), (2, 44, 5120),
+                                     (7, 9000, 2048), (4, 40000, 1024)])
+def test_gemv_persistent_bulk_copies(ops, m, n, k):
+    """The persistent small-batch product (weights through shared memory by bulk copies, four
+    ranges of K combined by ticket): values, launches in a row on the shared workspace, bitwise
+    independence of the number of tokens, and the fused SwiGLU."""
+    assert ops.gemv_tma_supports(m, n, k)
+    assert not ops.gemv_tma_supports(9, n, k) and not ops.gemv_tma_supports(m, n, k + 8)
+    x = rand(m, k, dtype=torch.bfloat16, seed=1)
+    w = rand(n, k, dtype=torch.bfloat16, seed=2, scale=0.05)
+    want = x.float() @ w.float().T
+    for dt in (torch.float32, torch.bfloat16):
+        for _ in range(3):   # the tickets are back at zero after every launch
+            out = torch.full((m, n), float("nan"), dtype=dt, device="cuda")
+            ops.gemv_tma(x.cuda(), w.cuda(), out)
+            tol = dict(rtol=2e-3, atol=2e-3) if dt == torch.float32 else TOL["bfloat16"]
+            torch.testing.assert_close(out.cpu().float(), want, **tol)
+    full = torch.empty(m, n, dtype=torch.float32, device="cuda")
+    ops.gemv_tma(x.cuda(), w.cuda(), full)
+    one = torch.empty(1, n, dtype=torch.float32, device="cuda")
+    ops.gemv_tma(x[m - 1:].cuda(), w.cuda(), one)
+    assert torch.equal(one.cpu()[0], full.cpu()[m - 1])
+    if n % 2 == 0:
+        half = n // 2
+        out = torch.full((m, half), float("nan"), dtype=torch.bfloat16, device="cuda")
+        ops.gemv_tma(x.cuda(), w.cuda(), out, swiglu=True)
+        gate, up = want[:, :half].to(torch.bfloat16).float(), want[:, half:].to(torch.bfloat16).float()
+        torch.testing.assert_close(out.cpu().float(), gate * torch.sigmoid(gate) * up,
+                                   **TOL["bfloat16"])
+    # rows of x and w inside wider buffers
+    xw = torch.zeros(m, k + 64, dtype=torch.bfloat16)
+    xw[:, :k] = x
+    ww = torch.zeros(n, k + 8, dtype=torch.bfloat16)
+    ww[:, :k] = w
+    out = torch.empty(m, n, dtype=torch.float32, device="cuda")
+    ops.gemv_tma(xw.cuda()[:, :k], ww.cuda()[:, :k], out)
+    assert torch.equal(out.cpu(), full.cpu())
+    assert ops.gemv_tma_error() == 0
+
+
 @pytest.mark.parametrize("m, n, k", [(128, 256, 64), (128, 256, 256), (256, 512, 192), (300, 600, 200),
                                      (5, 40, 72), (2048, 1024, 512), (130, 6144, 4096)])
 def test_gemm_tcgen05(ops, m, n, k):
