@@ -73,15 +73,19 @@ class BatchStager:
 
     def __init__(self, device: torch.device, capacity_ints: int = 1 << 16) -> None:
         self.device = device
-        self._host = [self._pinned(capacity_ints) for _ in range(2)]
-        self._events: list[torch.cuda.Event | None] = [None, None]
-        self._dev = torch.empty(capacity_ints, dtype=torch.int32, device=device)
         self._turn = 0
         self.bytes_uploaded = 0   # host-to-device bytes so far
+        self._allocate(capacity_ints)
 
-    @staticmethod
-    def _pinned(n: int) -> torch.Tensor:
-        return torch.empty(n, dtype=torch.int32, pin_memory=True)
+    def _allocate(self, n: int) -> None:
+        self._host = [torch.empty(n, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self._host_np = [h.numpy() for h in self._host]
+        self._events = [torch.cuda.Event(), torch.cuda.Event()]
+        self._dev = torch.empty(n, dtype=torch.int32, device=self.device)
+        # per tuple of array shapes: offsets, total, the device views and the slices to copy.
+        # Decode steps repeat their shapes, and making a dozen tensor views costs more host
+        # time than packing the arrays.
+        self._layouts: dict[tuple, tuple] = {}
 
     def reserve(self, n: int) -> None:
         """Make room for ``n`` ints now, so that later uploads keep their device addresses."""
@@ -93,34 +97,39 @@ class BatchStager:
         while cap < n:
             cap *= 2
         torch.cuda.current_stream().synchronize()
-        self._host = [self._pinned(cap) for _ in range(2)]
-        self._events = [None, None]
-        self._dev = torch.empty(cap, dtype=torch.int32, device=self.device)
+        self._allocate(cap)
+
+    def _layout(self, shapes: tuple) -> tuple:
+        offsets, total = [], 0
+        for shape in shapes:
+            size = int(np.prod(shape))
+            offsets.append((total, size))
+            total += (size + 3) // 4 * 4
+        if total > self._dev.numel():
+            self._grow(total)
+        views = [self._dev[o:o + size].view(shape) for (o, size), shape in zip(offsets, shapes)]
+        layout = (offsets, total, views, self._dev[:total], [h[:total] for h in self._host])
+        self._layouts[shapes] = layout
+        return layout
 
     def upload(self, parts: Sequence[np.ndarray]) -> list[torch.Tensor]:
         """Copy the int32 arrays to the device; returns one device view per array (each view
-        starts on a 16-byte boundary)."""
-        offsets, total = [], 0
-        for a in parts:
-            offsets.append(total)
-            total += (a.size + 3) // 4 * 4
-        if total > self._dev.numel():
-            self._grow(total)
+        starts on a 16-byte boundary).  The views of equal shapes are the same tensors from
+        call to call: they are valid until the next upload."""
+        shapes = tuple(a.shape for a in parts)
+        layout = self._layouts.get(shapes) or self._layout(shapes)
+        offsets, total, views, dev_slice, host_slices = layout
         turn = self._turn
         self._turn ^= 1
-        if self._events[turn] is not None:
-            self._events[turn].synchronize()
-        host = self._host[turn]
-        hnp = host.numpy()
-        for a, o in zip(parts, offsets):
-            hnp[o:o + a.size] = a.reshape(-1)
+        self._events[turn].synchronize()   # the copy that last read this buffer is done
+        hnp = self._host_np[turn]
+        for a, (o, size) in zip(parts, offsets):
+            hnp[o:o + size] = a.reshape(-1)
         if total:
-            self._dev[:total].copy_(host[:total], non_blocking=True)
+            dev_slice.copy_(host_slices[turn], non_blocking=True)
             self.bytes_uploaded += 4 * total
-        ev = torch.cuda.Event()
-        ev.record()
-        self._events[turn] = ev
-        return [self._dev[o:o + a.size].view(a.shape) for a, o in zip(parts, offsets)]
+        self._events[turn].record()
+        return list(views)
 
 
 def context_bucket(context: int) -> int:
