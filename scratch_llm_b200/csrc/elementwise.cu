@@ -8,14 +8,17 @@
 
 namespace sllm {
 
-// out[n, :] = table[ids[n], :] as float.  One block per token.
+// out[n, :] = table[ids[n], :] as float.  One block per token.  An id -1 - j stands for
+// pending[j]: a token that an earlier kernel of the stream chose and the host has not read yet.
 template <typename T>
-__global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ table,
-                             float* __restrict__ out, int d) {
+__global__ void embed_kernel(const int* __restrict__ ids, const int* __restrict__ pending,
+                             const T* __restrict__ table, float* __restrict__ out, int d) {
     pdl_wait();
     pdl_trigger();
     const int64_t n = blockIdx.x;
-    const T* src = table + (int64_t)ids[n] * d;
+    int id = ids[n];
+    if (id < 0) id = pending[-1 - id];
+    const T* src = table + (int64_t)id * d;
     float* dst = out + n * d;
     for (int i = threadIdx.x; i < d; i += blockDim.x) dst[i] = to_float(src[i]);
 }
@@ -174,16 +177,18 @@ static int norm_threads(int d) {
 }
 
 // dtype: 0 = float32, 1 = bfloat16 (of table / delta / out / gu).
-SLLM_EXPORT int sllm_embed(const int* ids, const void* table, float* out, int n_tokens, int d,
-                           int dtype, cudaStream_t stream) {
+// `pending` may be null if no id is negative.
+SLLM_EXPORT int sllm_embed(const int* ids, const int* pending, const void* table, float* out,
+                           int n_tokens, int d, int dtype, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (d <= 0) return (int)cudaErrorInvalidValue;
     const int threads = norm_threads(d);
     if (dtype == 0)
-        embed_kernel<float><<<n_tokens, threads, 0, stream>>>(ids, (const float*)table, out, d);
+        embed_kernel<float><<<n_tokens, threads, 0, stream>>>(ids, pending, (const float*)table, out,
+                                                              d);
     else if (dtype == 1)
         embed_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(
-            ids, (const __nv_bfloat16*)table, out, d);
+            ids, pending, (const __nv_bfloat16*)table, out, d);
     else
         return (int)cudaErrorInvalidValue;
     SLLM_LAUNCH_CHECK();

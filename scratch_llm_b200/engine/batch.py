@@ -35,6 +35,9 @@ class RowInput:
     request_id: Hashable
     tokens: Sequence[int]
     want: Sequence[int] = ()
+    #: the row's one token is not on the host yet: it is entry ``pending`` of the device buffer
+    #: that the step is given (``tokens`` then holds one placeholder)
+    pending: int | None = None
 
 
 @dataclass
@@ -56,6 +59,8 @@ class StepBatch:
     # device lists, with what a part needs to plan its launches for them
     single_rows: torch.Tensor | None = None
     multi_rows: torch.Tensor | None = None
+    # tokens chosen on the device that the host has not read yet (ids -1 - j in token_ids)
+    pending_tokens: torch.Tensor | None = None
     n_single: int = 0
     n_multi: int = 0
     max_new_multi: int = 0
@@ -179,12 +184,20 @@ def build_batch(cache, stager: BatchStager, rows: Sequence[RowInput], vocab_size
         flat = np.fromiter((r.tokens[0] for r in rows), dtype=np.int64, count=n_rows)
     else:
         flat = np.concatenate([np.asarray(r.tokens, dtype=np.int64) for r in rows])
+    pending = [(i, r.pending) for i, r in enumerate(rows) if r.pending is not None]
+    for i, j in pending:
+        if lens[i] != 1 or j < 0:
+            raise ValueError(f"request {rows[i].request_id!r}: a pending token is a row's only "
+                             "token")
+        flat[row_start[i]] = 0
     if flat.size and (flat.min() < 0 or flat.max() >= vocab_size):
         i = int(np.searchsorted(row_start[1:], int(np.argmax((flat < 0) | (flat >= vocab_size))),
                                 side="right"))
         raise ValueError(f"request {rows[i].request_id!r}: token id out of range "
                          f"[0, {vocab_size})")
     token_ids = flat.astype(np.int32)
+    for i, j in pending:
+        token_ids[row_start[i]] = -1 - j
     token_row = np.repeat(np.arange(n_rows, dtype=np.int32), lens_np)
     positions = (np.arange(n_tokens, dtype=np.int32) - row_start[token_row] + row_pos0[token_row])
     logit_index: list[int] = []

@@ -19,9 +19,10 @@ from typing import Hashable, Sequence
 import torch
 
 from ..sampling import Sampler, SamplingParams
+from ..sampling.sampler import PendingSample
 from .batch import RowInput
 from .runner import ModelRunner, load_model
-from .scheduler import Request, Scheduler, SchedulerStats, Sequence_
+from .scheduler import PlannedRow, Request, Scheduler, SchedulerStats, Sequence_
 
 
 @dataclass(frozen=True)
@@ -43,6 +44,15 @@ class ServeResult:
     wall_s: float
 
 
+@dataclass
+class _InFlight:
+    """A step that was launched and whose tokens the host has not read yet."""
+
+    rows: list[PlannedRow]
+    sampling: list[Sequence_]
+    pending: PendingSample | None
+
+
 def _seed_of(request: Request) -> int:
     if request.params.seed is not None:
         return int(request.params.seed)
@@ -53,12 +63,18 @@ class LLM:
     """``max_tokens`` is the cache capacity in tokens (the page pool holds that many);
     ``max_requests`` the number of requests that can be live at once; ``max_batch_tokens`` the
     token budget of one step; ``chunk_size`` the largest prompt portion per request and step
-    (None: the budget alone cuts prompts)."""
+    (None: the budget alone cuts prompts).
+
+    ``lookahead``: while a decode step runs, the next one is planned, packed and launched with
+    its input tokens still on the device (the sampler's output feeds the embedding directly), and
+    only then does the host wait for the tokens of the first.  The device then never waits for
+    the host between decode steps.  What a step computes does not change; a request that a stop
+    token ends has one more row in flight, whose result is dropped."""
 
     def __init__(self, model: str | Path, dtype: str = "bfloat16", max_tokens: int = 65536,
                  page_size: int = 16, max_requests: int = 64, max_batch_tokens: int = 2048,
                  chunk_size: int | None = None, admission: str = "optimistic",
-                 verbose: bool = False) -> None:
+                 verbose: bool = False, lookahead: bool = True) -> None:
         self.model = load_model(model, dtype, verbose=verbose) if isinstance(model, (str, Path)) \
             else model
         self.runner = ModelRunner(self.model, page_size, max(1, -(-max_tokens // page_size)),
@@ -67,6 +83,8 @@ class LLM:
         self.max_batch_tokens, self.chunk_size, self.admission = (max_batch_tokens, chunk_size,
                                                                   admission)
         self._sched: Scheduler | None = None
+        self.lookahead = lookahead
+        self._in_flight: _InFlight | None = None
 
     def _scheduler(self) -> Scheduler:
         return Scheduler(self.runner.cache, self.runner.max_position, self.max_batch_tokens,
@@ -86,27 +104,50 @@ class LLM:
     def has_work(self) -> bool:
         return self._sched is not None and self._sched.has_work
 
+    def _launch(self, rows: list[PlannedRow], places: Sequence[int] | None,
+                want_logprobs: bool) -> "_InFlight":
+        """Run ``rows`` and choose their next tokens, without waiting for either.  ``places``:
+        for rows planned ahead, where each row's input token lies in the pending buffer."""
+        if places is None:
+            inputs = [RowInput(r.seq.request.request_id, r.seq.tokens[r.start:r.start + r.n],
+                               [r.n - 1] if r.samples else []) for r in rows]
+        else:
+            inputs = [RowInput(r.seq.request.request_id, [0], [0], pending=j)
+                      for r, j in zip(rows, places)]
+        ahead = 0 if places is None else 1     # tokens of the request the host has not seen
+        logits = self.runner.step(inputs)
+        sampling = [r.seq for r in rows if r.samples]
+        pending = None
+        if sampling:
+            pending = self.sampler.sample_async(
+                logits, [s.request.params for s in sampling],
+                [_seed_of(s.request) for s in sampling],
+                [len(s.generated) + ahead for s in sampling], want_logprobs,
+                out=self.runner.pending_tokens[:len(sampling)])
+        return _InFlight(rows, sampling, pending)
+
     @torch.no_grad()
     def step(self, want_logprobs: bool = False) -> dict[Hashable, int]:
         """One scheduler step: plan a batch, run it, choose the next tokens.  Returns the token
         each request produced in this step ({request id: token}, on the host)."""
         sched = self._sched
-        rows = sched.plan()
-        inputs = [RowInput(r.seq.request.request_id, r.seq.tokens[r.start:r.start + r.n],
-                           [r.n - 1] if r.samples else []) for r in rows]
-        logits = self.runner.step(inputs)
-        sampling = [r.seq for r in rows if r.samples]
-        tokens, lps = [], None
-        if sampling:
-            tokens, lps = self.sampler.sample(
-                logits, [s.request.params for s in sampling],
-                [_seed_of(s.request) for s in sampling],
-                [len(s.generated) for s in sampling], want_logprobs)
-        sched.complete(rows, tokens, lps)
-        return {s.request.request_id: t for s, t in zip(sampling, tokens)}
+        cur = self._in_flight
+        if cur is None:
+            cur = self._launch(sched.plan(), None, want_logprobs)
+        self._in_flight = None
+        if self.lookahead and cur.pending is not None:
+            ahead = sched.plan_ahead(cur.rows)
+            if ahead is not None:
+                self._in_flight = self._launch([r for r, _ in ahead], [j for _, j in ahead],
+                                               want_logprobs)
+        tokens, lps = cur.pending.result() if cur.pending is not None else ([], None)
+        alive = [not s.finish_reason for s in cur.sampling]
+        sched.complete(cur.rows, tokens, lps)
+        return {s.request.request_id: t for s, t, a in zip(cur.sampling, tokens, alive) if a}
 
     def abort_all(self) -> None:
         """Drop every queued and live request and give back what they hold."""
+        self._in_flight = None
         if self._sched is not None:
             for seq in list(self._sched.running):
                 self.runner.cache.release(seq.request.request_id)
@@ -126,6 +167,7 @@ class LLM:
             while self.has_work:
                 self.step(want_logprobs)
             sched = self._sched
+            self._in_flight = None   # rows planned ahead for requests that have all ended
         except BaseException:
             self.abort_all()   # an error leaves nothing held
             raise

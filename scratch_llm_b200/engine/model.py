@@ -107,7 +107,7 @@ class DecoderModel:
         s = self.spec
         resid = torch.empty((batch.n_tokens, s.hidden_size), dtype=torch.float32,
                             device=self.ctx.device)
-        ops.embed(batch.token_ids, self.embedding, resid)
+        ops.embed(batch.token_ids, self.embedding, resid, batch.pending_tokens)
         pending = None
         for run in s.order:
             pages, group = cache.entry_pages(run.cache)

@@ -72,6 +72,11 @@ class ModelRunner:
         self._captured: dict[tuple[int, int], _CapturedStep] = {}
         self.replayed_kernels = 0   # kernels of this package launched through graph replays
         self._seen_sizes: set[tuple[int, int]] = set()
+        # tokens that a sampler chose and the host has not read yet: a row may name one of them
+        # as its input (RowInput.pending), so that the next step can be launched before the
+        # host has seen the tokens of this one
+        self.pending_tokens = torch.zeros(max(1, max_requests), dtype=torch.int32,
+                                          device=self.device)
         # room for the widest decode step, so that captured addresses stay valid
         self._stager.reserve(8 * (max_requests + 4) + 4 * max(1, len(self.cache.groups)) +
                              max_requests * (self._table_width + 4) * max(1, len(self.cache.groups)))
@@ -89,8 +94,15 @@ class ModelRunner:
 
     # --------------------------------------------------------------------------- step
 
-    def build_batch(self, rows: Sequence[RowInput]) -> StepBatch:
-        return build_batch(self.cache, self._stager, rows, self.vocab_size, self.max_position)
+    def build_batch(self, rows: Sequence[RowInput], table_width: int | None = None) -> StepBatch:
+        for row in rows:
+            if row.pending is not None and row.pending >= self.pending_tokens.numel():
+                raise ValueError(f"request {row.request_id!r}: pending token {row.pending} is "
+                                 f"beyond the buffer's {self.pending_tokens.numel()} entries")
+        batch = build_batch(self.cache, self._stager, rows, self.vocab_size, self.max_position,
+                            table_width=table_width)
+        batch.pending_tokens = self.pending_tokens
+        return batch
 
     def step(self, rows: Sequence[RowInput]) -> torch.Tensor | None:
         """Run exactly the tokens of ``rows`` as one batch from the cache that earlier steps
@@ -115,8 +127,7 @@ class ModelRunner:
     def _decode_step(self, rows: Sequence[RowInput]) -> torch.Tensor:
         """Replay (or, at a size's second use, capture) the decode step for len(rows) rows."""
         n = len(rows)
-        batch = build_batch(self.cache, self._stager, rows, self.vocab_size, self.max_position,
-                            table_width=self._table_width)
+        batch = self.build_batch(rows, table_width=self._table_width)
         pointers = (batch.token_ids.data_ptr(), batch.logit_index.data_ptr(),
                     tuple(t.data_ptr() for t in batch.block_tables))
         key = (n, batch.context_bucket)   # launch shapes depend on these two alone

@@ -235,6 +235,39 @@ class Scheduler:
             return self.plan()
         return rows
 
+    def plan_ahead(self, in_flight: Sequence[PlannedRow]) -> list[tuple[PlannedRow, int]] | None:
+        """The step after ``in_flight``, planned while ``in_flight`` still runs and its tokens
+        are unknown: every live request decodes the token it is about to get.  Returns rows with,
+        for each, the place of its request among the sampling rows of ``in_flight`` (where its
+        pending token will lie), or None if the next step is not that simple (requests are
+        queued, a prompt is half read, pages are short): then :meth:`plan` decides, after
+        :meth:`complete`.  A request that its pending token ends for certain (length) is left
+        out; one that it may end (a stop token) is planned, and its row is dropped by
+        :meth:`complete` if it did end."""
+        if self.queue or not self.running:
+            return None
+        place: dict[int, int] = {}
+        k = 0
+        for r in in_flight:
+            if r.samples:
+                place[id(r.seq)] = k
+                k += 1
+        chosen: list[tuple[Sequence_, int]] = []
+        for seq in self.running:
+            j = place.get(id(seq))
+            if j is None:
+                return None
+            after = len(seq.tokens) + 1        # with the pending token
+            if after - seq.n_prompt >= seq.request.params.max_tokens or after >= self.max_position:
+                continue
+            chosen.append((seq, j))
+        if not chosen or len(chosen) > self.max_batch_tokens:
+            return None
+        for seq, _ in chosen:
+            if not self.cache.reserve(seq.request.request_id, 1):
+                return None
+        return [(PlannedRow(seq, self._cached(seq), 1, True), j) for seq, j in chosen]
+
     # -------------------------------------------------------------------------- complete
 
     def commit_rows(self, rows: Sequence[PlannedRow]) -> None:
@@ -256,17 +289,21 @@ class Scheduler:
         st.peak_live = max(st.peak_live, len(self.running))
         for r in rows:
             rid = r.seq.request.request_id
-            if r.n == 1 and r.start >= r.seq.n_prompt:
+            if r.seq.finish_reason:
+                pass
+            elif r.n == 1 and r.start >= r.seq.n_prompt:
                 st.decode_tokens += 1
             else:
                 st.prefill_tokens += r.n
             if not r.samples:
                 continue
             token = int(sampled[k])
-            if logprobs is not None:
-                r.seq.logprobs.append(float(logprobs[k]))
             k += 1
             seq = r.seq
+            if seq.finish_reason:        # planned ahead, and the token before this one ended it
+                continue
+            if logprobs is not None:
+                seq.logprobs.append(float(logprobs[k - 1]))
             seq.tokens.append(token)
             p = seq.request.params
             if token in p.stop_ids:

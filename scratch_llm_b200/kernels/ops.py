@@ -134,17 +134,22 @@ def _code(dtype: torch.dtype) -> int:
 
 # ------------------------------------------------------------------------------ elementwise
 
-def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """out[n] = table[ids[n]] widened to 32-bit.  ids int32 [N]; table [V, d]; out f32 [N, d]."""
+def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor,
+          pending: torch.Tensor | None = None) -> torch.Tensor:
+    """out[n] = table[ids[n]] widened to 32-bit.  ids int32 [N]; table [V, d]; out f32 [N, d].
+    An id ``-1 - j`` stands for ``pending[j]`` (int32, on the device): a token that an earlier
+    kernel of the stream chose and the host has not read yet."""
     _need(ids, torch.int32, "ids")
+    if pending is not None:
+        _need(pending, torch.int32, "pending")
     _need(table, None, "table")
     _need(out, torch.float32, "out")
     n, d = ids.numel(), table.shape[1]
     if out.shape != (n, d):
         raise KernelError(f"out must be [{n}, {d}], got {list(out.shape)}")
     _check(_core("sllm_elementwise").sllm_embed(
-        _ptr(ids), _ptr(table), _ptr(out), c_int(n), c_int(d), c_int(_code(table.dtype)),
-        _stream()), "embed")
+        _ptr(ids), _ptr(pending) if pending is not None else c_void_p(0), _ptr(table), _ptr(out),
+        c_int(n), c_int(d), c_int(_code(table.dtype)), _stream()), "embed")
     return out
 
 

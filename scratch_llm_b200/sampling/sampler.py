@@ -18,19 +18,58 @@ from ..kernels import ops
 from .params import SamplingParams
 
 
+class PendingSample:
+    """Tokens that were chosen on the device and are on their way to the host."""
+
+    def __init__(self, n: int, host_tokens: torch.Tensor, host_lp: torch.Tensor | None,
+                 event: torch.cuda.Event) -> None:
+        self._n, self._tokens, self._lp, self._event = n, host_tokens, host_lp, event
+
+    def result(self) -> tuple[list[int], list[float] | None]:
+        """Waits for the copy and returns host lists: the tokens and, if they were asked for,
+        their log-probabilities."""
+        self._event.synchronize()
+        tokens = self._tokens[:self._n].tolist()
+        return tokens, (self._lp[:self._n].tolist() if self._lp is not None else None)
+
+
 class Sampler:
+    #: pinned host buffers that take turns; at most this many samples may be in flight
+    IN_FLIGHT = 4
+
     def __init__(self, device: torch.device) -> None:
         self.device = device
         self.bytes_read = 0   # device-to-host bytes so far
         self._argmax_scratch: dict[int, torch.Tensor] = {}
+        self._host: list[tuple[torch.Tensor, torch.Tensor, torch.cuda.Event]] = []
+        self._turn = 0
+
+    def _host_buffers(self, n: int) -> tuple[torch.Tensor, torch.Tensor, torch.cuda.Event]:
+        if not self._host or self._host[0][0].numel() < n:
+            size = max(64, 1 << (n - 1).bit_length())
+            self._host = [(torch.empty(size, dtype=torch.int32, pin_memory=True),
+                           torch.empty(size, dtype=torch.float32, pin_memory=True),
+                           torch.cuda.Event()) for _ in range(self.IN_FLIGHT)]
+        self._turn = (self._turn + 1) % self.IN_FLIGHT
+        return self._host[self._turn]
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams],
                seeds: Sequence[int], counters: Sequence[int], want_logprobs: bool = False
                ) -> tuple[list[int], list[float] | None]:
         """One token per row of ``logits`` [n, vocab] (32-bit, on the device).  Returns host
         lists: the tokens and, if asked for, log_softmax(logits)[token] at temperature 1."""
+        return self.sample_async(logits, params, seeds, counters, want_logprobs).result()
+
+    def sample_async(self, logits: torch.Tensor, params: Sequence[SamplingParams],
+                     seeds: Sequence[int], counters: Sequence[int], want_logprobs: bool = False,
+                     out: torch.Tensor | None = None) -> PendingSample:
+        """Like :meth:`sample`, but returns at once: the tokens are written to ``out`` (int32
+        [n] on the device, if given) and copied to pinned host memory behind the kernels;
+        ``result()`` of the returned object waits for that copy (the one device-to-host read
+        of a step)."""
         n = logits.shape[0]
-        out = torch.empty(n, dtype=torch.int32, device=self.device)
+        if out is None:
+            out = torch.empty(n, dtype=torch.int32, device=self.device)
         lp = torch.empty(n, dtype=torch.float32, device=self.device) if want_logprobs else None
         if all(p.temperature == 0.0 for p in params) and lp is None:
             scratch = self._argmax_scratch.get(n)
@@ -48,6 +87,10 @@ class Sampler:
             fd = torch.from_numpy(f).to(self.device, non_blocking=True)
             idv = torch.from_numpy(i).to(self.device, non_blocking=True)
             ops.sample(logits, out, fd[0], fd[1], idv[0], idv[1], logprob_out=lp)
-        tokens = out.tolist()  # the one device-to-host read of a step
+        host_tokens, host_lp, event = self._host_buffers(n)
+        host_tokens[:n].copy_(out, non_blocking=True)
+        if lp is not None:
+            host_lp[:n].copy_(lp, non_blocking=True)
+        event.record()
         self.bytes_read += 4 * n * (2 if lp is not None else 1)
-        return tokens, (lp.tolist() if lp is not None else None)
+        return PendingSample(n, host_tokens, host_lp if lp is not None else None, event)

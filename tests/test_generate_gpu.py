@@ -99,6 +99,56 @@ def test_small_pool_sets_requests_back_and_results_do_not_change(model_dirs):
     assert not small.runner.cache.requests
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_steps_launched_ahead_change_nothing(dtype, model_dirs):
+    """With ``lookahead`` the next decode step is launched before the host has read the tokens
+    of the one in flight (they reach the embedding on the device).  Tokens, log-probabilities,
+    finish reasons and the cache's accounts are those of the plain loop: greedy and sampled,
+    with stop tokens that end requests while a row of theirs is in flight, and with a pool so
+    small that requests are set back."""
+    from scratch_llm_b200 import LLM, Request, SamplingParams
+    prompts = prompts_for(256, [30, 5, 28, 9, 17, 21])
+    base = LLM(model_dirs["A"], dtype=dtype, max_tokens=2048, page_size=16, lookahead=False)
+    greedy = base.generate(prompts, SamplingParams(temperature=0.0, max_tokens=24))
+    params = [SamplingParams(temperature=0.0, max_tokens=24, stop_ids=(greedy[0][3],)),
+              SamplingParams(temperature=0.0, max_tokens=24, stop_ids=(greedy[1][10], greedy[1][0])),
+              SamplingParams(temperature=0.8, top_p=0.9, max_tokens=19, seed=7),
+              SamplingParams(temperature=0.0, max_tokens=1),
+              SamplingParams(temperature=1.0, max_tokens=30, seed=8, stop_ids=(greedy[4][2],)),
+              SamplingParams(temperature=0.0, max_tokens=2)]
+    reqs = [Request(i, p, sp) for i, (p, sp) in enumerate(zip(prompts, params))]
+    want = base.serve(reqs, want_logprobs=True)
+    for kw in (dict(max_tokens=2048), dict(max_tokens=96, max_requests=4)):
+        ahead = LLM(model_dirs["A"], dtype=dtype, page_size=16, lookahead=True, **kw)
+        got = ahead.serve(reqs, want_logprobs=True)
+        for a, b in zip(got.completed, want.completed):
+            assert a.token_ids == b.token_ids and a.finish_reason == b.finish_reason
+            assert a.logprobs == b.logprobs
+        ahead.runner.cache.check()
+        assert not ahead.runner.cache.requests
+    assert any(c.finish_reason == "stop" for c in want.completed)
+    # a pool so small that requests are set back while steps are launched ahead
+    long = [Request(i, p, SamplingParams(temperature=0.0, max_tokens=40))
+            for i, p in enumerate(prompts_for(256, [30, 25, 28, 9, 33, 20]))]
+    want_long = base.serve(long)
+    small = LLM(model_dirs["A"], dtype=dtype, max_tokens=160, page_size=16, max_requests=4,
+                lookahead=True)
+    got_long = small.serve(long)
+    assert got_long.stats.preemptions > 0
+    assert [c.token_ids for c in got_long.completed] == [c.token_ids for c in want_long.completed]
+    small.runner.cache.check()
+    assert not small.runner.cache.requests
+    # step by step through submit()/step(): every token is reported once, by its own step
+    llm = LLM(model_dirs["A"], dtype=dtype, max_tokens=2048, page_size=16, lookahead=True)
+    for r in reqs:
+        llm.submit(r)
+    seen = {r.request_id: [] for r in reqs}
+    while llm.has_work:
+        for rid, tok in llm.step().items():
+            seen[rid].append(tok)
+    assert [tuple(seen[r.request_id]) for r in reqs] == [c.token_ids for c in want.completed]
+
+
 def test_sampling_through_the_entry_point(model_dirs):
     from scratch_llm_b200 import LLM, SamplingParams
     llm = LLM(model_dirs["A"], dtype="float32", max_tokens=1024, page_size=16)

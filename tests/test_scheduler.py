@@ -195,3 +195,96 @@ def test_random_traffic_small_pool(seed):
     for r in reqs:
         assert sched.finished[r.request_id].generated == oracle(r.prompt_ids, r.params, 80)
     assert sched.stats.steps == len(sched.stats.tokens_per_step)
+
+
+def run_ahead(sched, cache, limit=10_000):
+    """The loop of the entry point with a step planned ahead: the next step is planned (and its
+    rows committed) before the tokens of the step in flight are known."""
+    in_flight, n_ahead = None, 0
+    for _ in range(limit):
+        if not sched.has_work:
+            break
+        cur = in_flight
+        if cur is None:
+            cur = sched.plan()
+            assert cur
+            sched.commit_rows(cur)
+        in_flight = None
+        # the tokens of `cur`: each from the tokens its request had when the row ran (rows planned
+        # ahead ran with the pending token in place, which complete() has appended by now)
+        alive_before = [not r.seq.finish_reason for r in cur]
+        ahead = sched.plan_ahead(cur)
+        if ahead is not None:
+            rows = [r for r, _ in ahead]
+            sampling = [r.seq for r in cur if r.samples]
+            for r, j in ahead:
+                assert sampling[j] is r.seq and r.n == 1 and r.samples
+                assert r.start == cache.requests[r.seq.request.request_id].n_tokens == len(r.seq.tokens)
+            sched.commit_rows(rows)
+            in_flight = rows
+            n_ahead += 1
+        sampled = [next_token(r.seq.tokens) if a else -1
+                   for r, a in zip(cur, alive_before) if r.samples]
+        sched.complete(cur, sampled)
+        cache.check()
+    else:
+        raise AssertionError("the scheduler did not finish")
+    assert not cache.requests
+    assert cache.free_pages() == [g.pool.n_pages for g in cache.groups]
+    return n_ahead
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_steps_planned_ahead_give_the_same_tokens(seed):
+    rng = random.Random(100 + seed)
+    sched, cache = make(n_pages=rng.choice([30, 60, 200]), page_size=rng.choice([2, 4, 8]),
+                        max_requests=rng.choice([2, 3, 5]),
+                        max_batch_tokens=rng.choice([8, 24, 100]),
+                        chunk_size=rng.choice([None, 3, 16]), max_position=80)
+    reqs = []
+    pool_tokens = cache.groups[0].pool.n_pages * cache.page_size
+    for i in range(12):
+        n_p, n_g = rng.randint(1, 30), rng.randint(1, 20)
+        if n_p + n_g - 1 > pool_tokens or n_p + n_g > 80:
+            continue
+        stop = (rng.randrange(VOCAB),) if rng.random() < 0.5 else ()
+        reqs.append(Request(i, [rng.randrange(VOCAB) for _ in range(n_p)],
+                            SamplingParams(temperature=0.0, max_tokens=n_g, stop_ids=stop)))
+        sched.submit(reqs[-1])
+    n_ahead = run_ahead(sched, cache)
+    for r in reqs:
+        assert sched.finished[r.request_id].generated == oracle(r.prompt_ids, r.params, 80)
+    assert n_ahead > 0
+
+
+def test_plan_ahead_decisions():
+    sched, cache = make(n_pages=50, max_batch_tokens=64)
+    sched.submit(Request("a", [1, 2, 3], greedy(3)))
+    sched.submit(Request("b", [4, 5], SamplingParams(temperature=0.0, max_tokens=8, stop_ids=(7,))))
+    rows = sched.plan()
+    sched.commit_rows(rows)
+    ahead = sched.plan_ahead(rows)
+    # both requests decode their pending token next; places follow the order of the sampling rows
+    assert [(r.seq.request.request_id, r.start, r.n, j) for r, j in ahead] == [("a", 3, 1, 0),
+                                                                               ("b", 2, 1, 1)]
+    sched.commit_rows([r for r, _ in ahead])
+    sched.complete(rows, [9, 7])          # b's pending token was its stop token
+    assert "b" in sched.finished and sched.finished["b"].generated == [7]
+    rows2 = [r for r, _ in ahead]
+    # a's second token ends it for certain (max_tokens = 3 would be reached by the third), so
+    # the step after rows2 still holds a; then nothing is left to plan ahead
+    ahead2 = sched.plan_ahead(rows2)
+    assert [(r.seq.request.request_id, j) for r, j in ahead2] == [("a", 0)]
+    sched.commit_rows([r for r, _ in ahead2])
+    sched.complete(rows2, [11, 12])       # b's row is dropped: it had ended
+    assert sched.finished["b"].generated == [7]
+    assert sched.plan_ahead([r for r, _ in ahead2]) is None   # a's pending token is its last
+    sched.complete([r for r, _ in ahead2], [13])
+    assert sched.finished["a"].generated == [9, 11, 13] and not sched.has_work
+    # a queued request, or a prompt that is half read, sends the decision back to plan()
+    sched2, cache2 = make(n_pages=50, max_batch_tokens=4, max_requests=1)
+    sched2.submit(Request("x", [1, 2, 3], greedy(4)))
+    sched2.submit(Request("y", [1], greedy(2)))
+    rows = sched2.plan()
+    sched2.commit_rows(rows)
+    assert sched2.plan_ahead(rows) is None
