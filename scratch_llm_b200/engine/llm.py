@@ -18,6 +18,7 @@ from typing import Hashable, Sequence
 
 import torch
 
+from ..kernels import ops
 from ..sampling import Sampler, SamplingParams
 from ..sampling.sampler import PendingSample
 from .batch import RowInput
@@ -168,6 +169,7 @@ class LLM:
                 self.step(want_logprobs)
             sched = self._sched
             self._in_flight = None   # rows planned ahead for requests that have all ended
+            ops.check_kernel_errors()
         except BaseException:
             self.abort_all()   # an error leaves nothing held
             raise

@@ -485,6 +485,22 @@ def attention_tc_error(head_dim: int) -> int:
     return int(_load(*attention_tc_library(head_dim)).sllm_attn_tc_error())
 
 
+def check_kernel_errors() -> None:
+    """Raise if a kernel of a loaded library gave up a bounded wait since the last check (the
+    kernels that use mbarriers or flags record a code instead of hanging).  Synchronises the
+    device: call it where the host waits anyway (the end of a request batch, of a trace)."""
+    found = []
+    for name, lib in list(_loaded.items()):
+        for symbol in ("sllm_gemm_tc_error", "sllm_gemv_tma_error", "sllm_attn_tc_error"):
+            if hasattr(lib, symbol):
+                code = int(getattr(lib, symbol)())
+                if code:
+                    found.append(f"{name}: code {code}")
+    if found:
+        raise KernelError("a kernel gave up waiting (its results are not valid): " +
+                          "; ".join(found))
+
+
 def attention_mma_scratch_floats(n_tokens: int, n_heads: int, head_dim: int, n_splits: int) -> int:
     return n_tokens * n_heads * n_splits * (head_dim + 1) if n_splits > 1 else 0
 
