@@ -100,7 +100,13 @@ __device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
     *reinterpret_cast<uint2*>(p) = raw;
 }
 
-template <typename T>
+// SPREAD = false: a thread adds up its chunks itself (d up to 4 * VEC_CHUNKS * blockDim.x).
+// SPREAD = true: for d <= 4 * VEC_CHUNKS * blockDim.x <= 4096 and many rows.  A thread's chunk c
+// stands for thread threadIdx.x + c * blockDim.x of the kernel with SPREAD = false and
+// VEC_CHUNKS times as many threads, and the sums are added in exactly that kernel's order, so
+// that a row's result is bitwise the same whichever of the two ran it; but blocks are a quarter
+// as large, more of them fit on an SM, and their load, sum and store phases overlap.
+template <typename T, bool SPREAD>
 __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const T* __restrict__ delta,
                                        const int* __restrict__ index, const float* __restrict__ w,
                                        float eps, T* __restrict__ out, int d) {
@@ -113,10 +119,11 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const T* __res
     const T* dl = delta ? delta + row * d : nullptr;
     T* y = out + o * d;
     float4 v[VEC_CHUNKS];
-    float ss = 0.f;
+    float ss[VEC_CHUNKS];
 #pragma unroll
     for (int c = 0; c < VEC_CHUNKS; ++c) {
         const int i = (threadIdx.x + c * blockDim.x) * 4;
+        ss[c] = 0.f;
         if (i < d) {
             v[c] = load4(x + i);
             if (dl) {
@@ -124,10 +131,32 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const T* __res
                 v[c].x += a.x; v[c].y += a.y; v[c].z += a.z; v[c].w += a.w;
                 if (!index) store4(x + i, v[c]);
             }
-            ss += v[c].x * v[c].x + v[c].y * v[c].y + v[c].z * v[c].z + v[c].w * v[c].w;
+            ss[c] = v[c].x * v[c].x + v[c].y * v[c].y + v[c].z * v[c].z + v[c].w * v[c].w;
         }
     }
-    const float total = block_sum(ss, scratch);
+    float total;
+    if (SPREAD) {
+        // warp w's chunk c is warp w + c * (blockDim.x / 32) of the wide kernel
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+#pragma unroll
+        for (int c = 0; c < VEC_CHUNKS; ++c) {
+            const float s = warp_sum(ss[c]);
+            if (lane == 0) scratch[warp + c * n_warps] = s;
+        }
+        __syncthreads();
+        if (warp == 0) {
+            float t = lane < VEC_CHUNKS * n_warps ? scratch[lane] : 0.f;
+            t = warp_sum(t);
+            if (lane == 0) scratch[32] = t;
+        }
+        __syncthreads();
+        total = scratch[32];
+    } else {
+        float s = 0.f;
+#pragma unroll
+        for (int c = 0; c < VEC_CHUNKS; ++c) s += ss[c];
+        total = block_sum(s, scratch);
+    }
     const float inv = 1.0f / sqrtf(total / (float)d + eps);
 #pragma unroll
     for (int c = 0; c < VEC_CHUNKS; ++c) {
@@ -204,13 +233,23 @@ SLLM_EXPORT int sllm_add_rmsnorm(float* resid, const void* delta, const int* ind
         int vt = 32;
         while (vt < 1024 && vt * 4 * (d > 4096 ? VEC_CHUNKS : 1) < d) vt <<= 1;
         cudaError_t e;
+        // many rows: blocks a quarter as wide with the same (bitwise) result, see the kernel
+        const bool spread = d <= 4096 && vt >= 32 * VEC_CHUNKS && n_out >= 296;
+        if (spread) vt /= VEC_CHUNKS;
         if (dtype == 0)
-            e = sllm_launch_pdl(add_rmsnorm_vec_kernel<float>, dim3(n_out), dim3(vt), 0, stream,
-                                resid, (const float*)delta, index, w, eps, (float*)out, d);
+            e = spread
+                ? sllm_launch_pdl(add_rmsnorm_vec_kernel<float, true>, dim3(n_out), dim3(vt), 0,
+                                  stream, resid, (const float*)delta, index, w, eps, (float*)out, d)
+                : sllm_launch_pdl(add_rmsnorm_vec_kernel<float, false>, dim3(n_out), dim3(vt), 0,
+                                  stream, resid, (const float*)delta, index, w, eps, (float*)out, d);
         else
-            e = sllm_launch_pdl(add_rmsnorm_vec_kernel<__nv_bfloat16>, dim3(n_out), dim3(vt), 0,
-                                stream, resid, (const __nv_bfloat16*)delta, index, w, eps,
-                                (__nv_bfloat16*)out, d);
+            e = spread
+                ? sllm_launch_pdl(add_rmsnorm_vec_kernel<__nv_bfloat16, true>, dim3(n_out),
+                                  dim3(vt), 0, stream, resid, (const __nv_bfloat16*)delta, index, w,
+                                  eps, (__nv_bfloat16*)out, d)
+                : sllm_launch_pdl(add_rmsnorm_vec_kernel<__nv_bfloat16, false>, dim3(n_out),
+                                  dim3(vt), 0, stream, resid, (const __nv_bfloat16*)delta, index, w,
+                                  eps, (__nv_bfloat16*)out, d);
         return (int)e;
     }
     const int threads = norm_threads(d);

@@ -62,6 +62,24 @@ def test_add_rmsnorm(ops, dtype, d, eps):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("d", [4096, 1000, 520])
+def test_add_rmsnorm_same_bits_for_few_and_many_rows(ops, dtype, d):
+    """With many rows the norm runs in narrower blocks; a row's result is bitwise the one it
+    has among few rows (the sums are added in the same order)."""
+    n = 400
+    resid, delta = rand(n, d, seed=4), rand(n, d, dtype=DT[dtype], seed=5)
+    w = rand(d, seed=6) + 1.0
+    many_r, few_r = resid.cuda(), resid[:5].cuda()
+    many = torch.empty(n, d, dtype=DT[dtype], device="cuda")
+    few = torch.empty(5, d, dtype=DT[dtype], device="cuda")
+    ops.add_rmsnorm(many_r, delta.cuda(), w.cuda(), 1e-5, many)
+    ops.add_rmsnorm(few_r, delta[:5].cuda(), w.cuda(), 1e-5, few)
+    assert torch.equal(many.cpu()[:5], few.cpu()) and torch.equal(many_r.cpu()[:5], few_r.cpu())
+    torch.testing.assert_close(many.cpu().float(), P.rmsnorm(resid + delta.float(), w, 1e-5),
+                               **TOL[dtype])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_swiglu(ops, dtype):
     gu = rand(13, 2 * 301, dtype=DT[dtype], scale=3.0)
     out = torch.empty(13, 301, dtype=DT[dtype], device="cuda")
