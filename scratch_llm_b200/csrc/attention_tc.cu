@@ -10,7 +10,7 @@
 //
 //   CTA = 128 packed queries of one (row, kv head), 192 threads:
 //     warp 0     TMA producer: the query tile once, then per 128-key tile the pages of K and V
-//                (boxes of page_size rows x 64 columns, 128-byte swizzle), 2 stages
+//                (boxes of page_size rows x 64 columns, 128-byte swizzle), 3 stages (1 above head size 128)
 //     warp 1     MMA issuer: QK^T (M 128, N 128, K = head size) into S; P V (M 128, N = head
 //                size, K 128; A = P from tensor memory, B = V in its stored [key][dim] layout,
 //                i.e. MN-major) into O
@@ -18,7 +18,9 @@
 //                bfloat16; O is rescaled in tensor memory only when a row's maximum grew by
 //                more than 2^8 (the stale reference maximum is exact as long as the final
 //                division uses the matching sum); at the end O / l -> global memory
-//   tensor memory: S columns 0..127, P 128..191 (two bfloat16 per column), O 256..256+HD-1.
+//   tensor memory: two S/P buffers at columns 0..127 and 128..255 (P(t), two bfloat16 per column,
+//   takes the place of S(t) in buffer t % 2), O 256..256+HD-1.  While the softmax warps work on
+//   S(t) the tensor pipe computes S(t+1), and P(t) V runs beside the softmax of S(t+1).
 //
 // Takes head sizes that are multiples of 64 up to 256, group sizes that divide 128, page sizes
 // that divide 128, no window; other shapes use attention_mma.cu.  Cache memory beyond a
@@ -41,14 +43,22 @@ static_assert(HD % 64 == 0 && HD >= 64 && HD <= 256, "head size: 64, 128, 192 or
 constexpr int TQ = 128, TKV = 128, NCB = HD / 64;            // column blocks of 64 (128 bytes)
 constexpr int SUB_BYTES = 128 * 128;                          // 128 rows x 128 bytes
 constexpr int Q_BYTES = NCB * SUB_BYTES, KV_BYTES = NCB * SUB_BYTES;
-constexpr int KV_STAGES = HD <= 128 ? 2 : 1;
+constexpr int KV_STAGES = HD <= 128 ? 3 : 1;
+// With at least two key/value stages Q K(t+1)^T is issued before P(t) V (two S/P buffers in
+// tensor memory take turns); with one stage the next keys arrive only after P(t) V and one
+// buffer serves.
+constexpr bool EARLY_QK = KV_STAGES >= 2;
 constexpr int ATC_THREADS = 192;
-constexpr uint32_t S_COL = 0, P_COL = 128, O_COL = 256;
+constexpr uint32_t SP_COLS = 128, O_COL = 256;   // S/P buffer b at columns 128 b; O behind them
 constexpr uint32_t ATC_WAIT_LIMIT = 1u << 24;
 constexpr size_t ATC_SMEM = (size_t)Q_BYTES + (size_t)KV_STAGES * 2 * KV_BYTES + 1024 + 256;
 constexpr float RESCALE_THRESHOLD = 8.0f;                     // log2 units
 
 __device__ int g_attn_tc_error = 0;
+
+// S/P buffer of key tile t and the parity of its use of that buffer's barriers.
+__device__ __forceinline__ int atc_buf(int t) { return EARLY_QK ? (t & 1) : 0; }
+__device__ __forceinline__ uint32_t atc_phase(int t) { return (uint32_t)((EARLY_QK ? (t >> 1) : t) & 1); }
 
 __device__ __forceinline__ uint32_t atc_u32(const void* p) {
     return (uint32_t)__cvta_generic_to_shared(p);
@@ -197,10 +207,11 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     uint64_t* q_full = bars;
     uint64_t* kv_full = bars + 1;                            // [KV_STAGES]
     uint64_t* kv_empty = kv_full + KV_STAGES;                // [KV_STAGES]
-    uint64_t* s_full = kv_empty + KV_STAGES;
-    uint64_t* p_full = s_full + 1;
-    uint64_t* pv_done = p_full + 1;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 1);
+    uint64_t* s_full = kv_empty + KV_STAGES;                 // [2], one per S/P buffer
+    uint64_t* p_full = s_full + 2;                           // [2]
+    uint64_t* pv_done = p_full + 2;
+    uint64_t* o_done = pv_done + 1;                          // the last P V is over
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = a.row_list ? a.row_list[blockIdx.y] : blockIdx.y;
@@ -224,9 +235,12 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             atc_init(&kv_full[s], 1);
             atc_init(&kv_empty[s], 1);
         }
-        atc_init(s_full, 1);
-        atc_init(p_full, 4);
+        for (int b = 0; b < 2; ++b) {
+            atc_init(&s_full[b], 1);
+            atc_init(&p_full[b], 4);
+        }
         atc_init(pv_done, 1);
+        atc_init(o_done, 1);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     }
@@ -296,37 +310,58 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             const uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) |
                                       ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(TQ >> 4) << 24);
             bool ok = atc_wait(q_full, 0, 2);
-            for (int t = 0; t < n_tiles && ok; ++t) {
+            // S(t) = Q K(t)^T into the tile's buffer, which the P before it (two tiles back with
+            // two buffers, one tile back with one) has left once its P V is done.  A wait on
+            // pv_done names the phase by its parity, so the waiter must know that the phase before
+            // is over: here the call for the tile before waited for it.
+            auto issue_qk = [&](int t) -> bool {
                 const int s = t % KV_STAGES;
-                ok = atc_wait(&kv_full[s], (t / KV_STAGES) & 1, 3);
-                if (!ok) break;
+                if (!atc_wait(&kv_full[s], (t / KV_STAGES) & 1, 3)) return false;
+                const int back = EARLY_QK ? 2 : 1;
+                if (t >= back && !atc_wait(pv_done, (t - back) & 1, 8)) return false;
                 atc_fence_after();
                 const uint32_t k_addr = atc_u32(kv_s + (size_t)s * 2 * KV_BYTES);
-                const uint32_t v_addr = k_addr + KV_BYTES;
-                // S = Q K^T: K steps of 16 over the head size
 #pragma unroll
                 for (int kk = 0; kk < HD / 16; ++kk) {
                     const uint64_t dq = atc_desc(atc_u32(q_s) + (kk / 4) * SUB_BYTES, 16, 1024) +
                                         2 * (kk % 4);
                     const uint64_t dk = atc_desc(k_addr + (kk / 4) * SUB_BYTES, 16, 1024) +
                                         2 * (kk % 4);
-                    atc_mma_ss(tmem + S_COL, dq, dk, idesc_qk, kk > 0);
+                    atc_mma_ss(tmem + SP_COLS * atc_buf(t), dq, dk, idesc_qk, kk > 0);
                 }
-                atc_commit(s_full);
+                atc_commit(&s_full[atc_buf(t)]);
+                return true;
+            };
+            // The tensor pipe's order is QK(0), QK(1), PV(0), QK(2), PV(1), ...: while the softmax
+            // warps work on S(t), Q K(t+1)^T already runs, and P(t) V runs beside the softmax of
+            // S(t+1).  With one key/value stage the order is QK(t), PV(t), QK(t+1).
+            if (ok) ok = issue_qk(0);
+            for (int t = 0; t < n_tiles && ok; ++t) {
+                const int s = t % KV_STAGES;
+                if (EARLY_QK && t + 1 < n_tiles) {
+                    ok = issue_qk(t + 1);
+                    if (!ok) break;
+                }
                 // O += P V once the softmax warps have written P: K steps of 16 keys
-                ok = atc_wait(p_full, t & 1, 4);
+                ok = atc_wait(&p_full[atc_buf(t)], atc_phase(t), 4);
                 if (!ok) break;
                 atc_fence_after();
+                const uint32_t v_addr = atc_u32(kv_s + (size_t)s * 2 * KV_BYTES) + KV_BYTES;
 #pragma unroll
                 for (int kk = 0; kk < TKV / 16; ++kk) {
                     // V: rows = keys (128 bytes = 64 dims each), 8-key groups 1024 bytes apart,
                     // 64-dim blocks SUB_BYTES apart; 16 keys further = 2048 bytes
                     const uint64_t dv = atc_desc(v_addr + kk * 2048, SUB_BYTES, 1024);
-                    atc_mma_ts(tmem + O_COL, tmem + P_COL + kk * 8, dv, idesc_pv, (t | kk) != 0);
+                    atc_mma_ts(tmem + O_COL, tmem + SP_COLS * atc_buf(t) + kk * 8, dv, idesc_pv,
+                               (t | kk) != 0);
                 }
                 atc_commit(&kv_empty[s]);
                 atc_commit(pv_done);
+                if (!EARLY_QK && t + 1 < n_tiles) ok = issue_qk(t + 1);
             }
+            // pv_done runs through a phase per tile and a parity cannot name one of many phases
+            // to a warp that arrives late: the end has a barrier of its own
+            if (ok) atc_commit(o_done);
         }
     } else {
         const int quad = warp & 3;
@@ -339,7 +374,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         float m_ref = -INFINITY, l_sum = 0.f;
         bool ok = true;
         for (int t = 0; t < n_tiles; ++t) {
-            ok = atc_wait(s_full, t & 1, 5);
+            const uint32_t sp_col = SP_COLS * atc_buf(t);    // this tile's S, then its P
+            ok = atc_wait(&s_full[atc_buf(t)], atc_phase(t), 5);
             if (!ok) break;
             atc_fence_after();
             const int kt = t * TKV;
@@ -348,7 +384,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             // reach past the row's own position (or rows that do not exist) need the mask.
             float sv[4][32];
 #pragma unroll
-            for (int c = 0; c < 4; ++c) atc_ld32_nowait(lane_base + S_COL + c * 32, sv[c]);
+            for (int c = 0; c < 4; ++c) atc_ld32_nowait(lane_base + sp_col + c * 32, sv[c]);
             atc_ld_wait();
             const bool masked = !valid || kt + TKV - 1 > qpos;
             if (masked) {
@@ -371,21 +407,21 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 m_ref = mx;
                 l_sum *= corr;
             }
-            // P and O are free once the previous tile's P V has finished
-            if (t > 0) {
+            // O may be rescaled once the previous tile's P V has finished (P(t) takes the place
+            // of S(t), which this thread has read, so it waits for nothing).  S(t) exists, so the
+            // P V two tiles back is over and the parity names the right phase.
+            if (t > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
                 ok = atc_wait(pv_done, (t - 1) & 1, 6);
                 if (!ok) break;
                 atc_fence_after();
-                if (__any_sync(0xffffffffu, corr != 1.f)) {
 #pragma unroll 1
-                    for (int c = 0; c < HD / 32; ++c) {
-                        float ov[32];
-                        atc_ld32(lane_base + O_COL + c * 32, ov);
-                        uint32_t w[32];
+                for (int c = 0; c < HD / 32; ++c) {
+                    float ov[32];
+                    atc_ld32(lane_base + O_COL + c * 32, ov);
+                    uint32_t w[32];
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) w[i] = __float_as_uint(ov[i] * corr);
-                        atc_st32(lane_base + O_COL + c * 32, w);
-                    }
+                    for (int i = 0; i < 32; ++i) w[i] = __float_as_uint(ov[i] * corr);
+                    atc_st32(lane_base + O_COL + c * 32, w);
                 }
             }
             // pass 2: probabilities p = 2^(s * scale - m_ref) (one fused multiply-add and one
@@ -403,15 +439,15 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                     l4[i & 3] += p0 + p1;
                     w[i] = atc_pack(p0, p1);
                 }
-                atc_st32(lane_base + P_COL + c * 32, w);
+                atc_st32(lane_base + sp_col + c * 32, w);
             }
             l_sum += (l4[0] + l4[1]) + (l4[2] + l4[3]);
             atc_st_wait();
             atc_fence_before();
             __syncwarp();
-            if (lane == 0) atc_arrive(p_full);
+            if (lane == 0) atc_arrive(&p_full[atc_buf(t)]);
         }
-        if (ok && atc_wait(pv_done, (n_tiles - 1) & 1, 7)) {
+        if (ok && atc_wait(o_done, 0, 7)) {
             atc_fence_after();
             const float inv = l_sum > 0.f ? 1.0f / l_sum : 0.f;
             bf16* dst = a.out + (int64_t)(t0 + tok) * a.out_stride + (int64_t)(g * GS + j) * HD;

@@ -310,7 +310,8 @@ def test_attention_on_tensor_cores(ops, H, G, hd, page, window, n_splits):
 
 
 @pytest.mark.parametrize("H, G, hd, page", [(8, 2, 64, 16), (32, 8, 128, 16), (8, 1, 128, 32),
-                                           (4, 4, 64, 8), (2, 1, 128, 128)])
+                                           (4, 4, 64, 8), (2, 1, 128, 128), (4, 2, 256, 16),
+                                           (2, 2, 192, 32)])
 def test_attention_tcgen05(ops, H, G, hd, page):
     """Prompt portions on the tcgen05 kernel: long rows (several key tiles, several query
     tiles), rows that start deep in a context, short rows; unused cache places hold large
@@ -326,10 +327,13 @@ def test_attention_tcgen05(ops, H, G, hd, page):
         q = case["wide"][:, :H * hd]
         out = torch.full((q.shape[0], H * hd), float("nan"), dtype=torch.bfloat16, device="cuda")
         every = list(range(len(rows)))
-        ops.attention_tc(q, pages, case["table"], page, case["row_start"], case["row_pos0"], out,
-                         None, len(rows), max(n for _, n in rows), H, G, hd, 1.0 / math.sqrt(hd))
-        assert ops.attention_tc_error(hd) == 0
-        check_attention(case, out.cpu().float(), every, "bfloat16", H, hd, None)
+        for _ in range(10):   # the warps of the kernel overlap differently from run to run
+            out.fill_(float("nan"))
+            ops.attention_tc(q, pages, case["table"], page, case["row_start"], case["row_pos0"],
+                             out, None, len(rows), max(n for _, n in rows), H, G, hd,
+                             1.0 / math.sqrt(hd))
+            assert ops.attention_tc_error(hd) == 0
+            check_attention(case, out.cpu().float(), every, "bfloat16", H, hd, None)
     finally:
         ATTN_ROWS = saved
 
