@@ -56,6 +56,17 @@ constexpr float RESCALE_THRESHOLD = 8.0f;                     // log2 units
 
 __device__ int g_attn_tc_error = 0;
 
+__device__ __forceinline__ float atc_max3(float a, float b, float c) {
+    float m;
+    asm("max.f32 %0, %1, %2, %3;\n" : "=f"(m) : "f"(a), "f"(b), "f"(c));
+    return m;
+}
+__device__ __forceinline__ float atc_ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+
 // S/P buffer of key tile t and the parity of its use of that buffer's barriers.
 __device__ __forceinline__ int atc_buf(int t) { return EARLY_QK ? (t & 1) : 0; }
 __device__ __forceinline__ uint32_t atc_phase(int t) { return (uint32_t)((EARLY_QK ? (t >> 1) : t) & 1); }
@@ -398,7 +409,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 #pragma unroll
             for (int c = 0; c < 4; ++c)
 #pragma unroll
-                for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], sv[c][i]);
+                for (int i = 0; i < 32; i += 2)    // the three-input maximum takes two scores at once
+                    mx4[(i >> 1) & 3] = atc_max3(mx4[(i >> 1) & 3], sv[c][i], sv[c][i + 1]);
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * a.scale_log2;
             // the reference maximum moves only when it must (first keys, or growth beyond 2^8)
             float corr = 1.f;
@@ -427,21 +439,28 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             // pass 2: probabilities p = 2^(s * scale - m_ref) (one fused multiply-add and one
             // exponential each; a masked score is -inf and gives 0), their sum, P as bfloat16
             const float neg_ref = m_ref == -INFINITY ? 0.f : -m_ref;   // all masked: p = 0 anyway
-            float l4[4] = {0.f, 0.f, 0.f, 0.f};
+            // (two scores per packed multiply-add and per packed add; the exponential is the
+            // bare ex2.approx: its operand is never positive by more than 2^8 and a flushed
+            // denormal is a zero probability)
+            const float2 scale2 = make_float2(a.scale_log2, a.scale_log2);
+            const float2 ref2 = make_float2(neg_ref, neg_ref);
+            float2 l2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
                 uint32_t w[32];
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
                     const int k0 = c * 64 + 2 * i;           // keys k0, k0 + 1 of the tile
-                    const float p0 = exp2f(fmaf(sv[k0 / 32][k0 % 32], a.scale_log2, neg_ref));
-                    const float p1 = exp2f(fmaf(sv[(k0 + 1) / 32][(k0 + 1) % 32], a.scale_log2, neg_ref));
-                    l4[i & 3] += p0 + p1;
-                    w[i] = atc_pack(p0, p1);
+                    const float2 x = __ffma2_rn(make_float2(sv[k0 / 32][k0 % 32],
+                                                            sv[(k0 + 1) / 32][(k0 + 1) % 32]),
+                                                scale2, ref2);
+                    const float2 pr = make_float2(atc_ex2(x.x), atc_ex2(x.y));
+                    l2[i & 1] = __fadd2_rn(l2[i & 1], pr);
+                    w[i] = atc_pack(pr.x, pr.y);
                 }
                 atc_st32(lane_base + sp_col + c * 32, w);
             }
-            l_sum += (l4[0] + l4[1]) + (l4[2] + l4[3]);
+            l_sum += (l2[0].x + l2[0].y) + (l2[1].x + l2[1].y);
             atc_st_wait();
             atc_fence_before();
             __syncwarp();
