@@ -264,7 +264,7 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=1024)
     ap.add_argument("--prefill-tokens", type=int, default=2048)
-    ap.add_argument("--page-size", type=int, default=16)
+    ap.add_argument("--page-size", type=int, default=64)
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")
     args = ap.parse_args()
     if args.impl == "reference":
