@@ -208,7 +208,9 @@ def time_decode_e2e(llm, cfg, batch: int, context: int, steps: int, warmup: int)
     from scratch_llm_b200 import Request, SamplingParams
 
     prompts = random_prompts(batch, context, cfg.vocab_size, seed=1000 + batch)
-    params = SamplingParams(temperature=0.0, max_tokens=warmup + steps + 8)
+    # room for the steps in which later prompts are still read while earlier requests decode
+    params = SamplingParams(temperature=0.0,
+                            max_tokens=warmup + steps + 8 + batch + batch * context // 1024)
     for i, p in enumerate(prompts):
         llm.submit(Request(f"e{i}", p, params))
     produced = set()
