@@ -284,3 +284,156 @@ def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
         for (rid, pos), row in got.items():
             torch.testing.assert_close(row, want[rid][pos], rtol=1e-4, atol=1e-5,
                                        msg=lambda m: f"{way.__name__} {rid} {pos}: {m}")
+
+
+# ------------------------------- a toy feed-forward with routing, a toy position encoding
+
+def make_toy_routed():
+    """Two more parts defined here, outside the framework's files: a feed-forward that routes
+    every token to the one of three small experts whose router logit (32-bit) is largest and
+    weighs its output with the softmax probability of that logit; and a position encoding that
+    is not rotary: it adds alpha * sin(position * 2^-j) to component j of every query and key
+    head.  A model with one layer of each beside a standard layer."""
+    from scratch_llm_b200.config import register_architecture, ARCHITECTURES
+    from scratch_llm_b200.config.spec import LayerSpec, ModelSpec, PartSpec, sequential_order
+    from scratch_llm_b200.parts import (FEED_FORWARDS, POSITION_ENCODINGS, FeedForward,
+                                        PositionEncoding, register_feed_forward,
+                                        register_position_encoding)
+    from scratch_llm_b200.weights import ParamSpec
+
+    if "top1_experts" not in FEED_FORWARDS:
+        @register_feed_forward("top1_experts")
+        class Top1Experts(FeedForward):
+            def __init__(self, hidden_size, inner, n_experts):
+                self.d, self.f, self.e = hidden_size, inner, n_experts
+
+            def param_specs(self):
+                return {"router.weight": ParamSpec((self.e, self.d)),
+                        "w_in": ParamSpec((self.e * self.f, self.d)),
+                        "w_out": ParamSpec((self.e * self.d, self.f))}
+
+            def load(self, tensors, ctx):
+                put = lambda t: t.to(ctx.device, torch.float32)  # noqa: E731
+                self.router = put(tensors["router.weight"])
+                self.w_in = put(tensors["w_in"]).view(self.e, self.f, self.d)
+                self.w_out = put(tensors["w_out"]).view(self.e, self.d, self.f)
+
+            def forward(self, x):
+                xf = x.float()
+                probs = torch.softmax(xf @ self.router.T, -1)      # router logits in 32-bit
+                p, idx = probs.max(-1)
+                h = torch.relu(torch.bmm(self.w_in[idx], xf[:, :, None]))
+                return (torch.bmm(self.w_out[idx], h)[:, :, 0] * p[:, None]).to(x.dtype)
+
+    if "added_sinusoid" not in POSITION_ENCODINGS:
+        @register_position_encoding("added_sinusoid")
+        class AddedSinusoid(PositionEncoding):
+            def __init__(self, head_dim, alpha):
+                self.hd, self.alpha = head_dim, float(alpha)
+
+            def load(self, tensors, ctx):
+                self.freq = (2.0 ** -torch.arange(self.hd, dtype=torch.float32)).to(ctx.device)
+
+            def apply(self, q, k, positions):
+                add = self.alpha * torch.sin(positions.float()[:, None] * self.freq)   # [n, hd]
+                q += add[:, None, :].to(q.dtype)
+                k += add[:, None, :].to(k.dtype)
+
+    if "ToyRoutedForCausalLM" not in ARCHITECTURES:
+        @dataclass(frozen=True)
+        class ToyRoutedConfig:
+            width: int
+            n_vocab: int
+            architecture = "ToyRoutedForCausalLM"
+
+            @classmethod
+            def from_dict(cls, raw):
+                return cls(raw["width"], raw["n_vocab"])
+
+            def to_dict(self):
+                return {"architectures": [self.architecture], "width": self.width,
+                        "n_vocab": self.n_vocab}
+
+            def model_spec(self):
+                d = self.width
+                norm = PartSpec("rmsnorm", {"size": d, "eps": 1e-5})
+                att = PartSpec("gqa_attention", {"hidden_size": d, "n_heads": 3, "n_kv_heads": 3,
+                                                 "head_dim": 16, "scale": 0.25, "window": None})
+                names = {"mixer": "mixer", "feed_forward": "ff", "mixer_norm": "n1",
+                         "feed_forward_norm": "n2"}
+                layers = (
+                    LayerSpec("l0", "pre_norm", att,
+                              PartSpec("top1_experts", {"hidden_size": d, "inner": 24, "n_experts": 3}),
+                              norm, norm, PartSpec("added_sinusoid", {"head_dim": 16, "alpha": 0.5}),
+                              names),
+                    LayerSpec("l1", "pre_norm", att,
+                              PartSpec("swiglu", {"hidden_size": d, "intermediate_size": 40}),
+                              norm, norm,
+                              PartSpec("rotary", {"head_dim": 16, "theta": 100.0, "max_position": 128}),
+                              names))
+                return ModelSpec(d, self.n_vocab, 128, layers, sequential_order(2), norm,
+                                 "emb.weight", "out_norm", "head.weight", tie_embeddings=True)
+
+        register_architecture("ToyRoutedForCausalLM", ToyRoutedConfig)
+    return ARCHITECTURES["ToyRoutedForCausalLM"].config_cls
+
+
+def toy_routed_plain(cfg, w, ids):
+    d, hd, H = cfg.width, 16, 3
+    x = w["emb.weight"][torch.tensor(ids)]
+    s = len(ids)
+    pos = torch.arange(s)
+    heads = lambda t: t.view(s, H, hd).transpose(0, 1)  # noqa: E731
+    # layer 0: attention with the added sinusoid, then the routed experts
+    h = P.rmsnorm(x, w["l0.n1.weight"], 1e-5)
+    add = 0.5 * torch.sin(pos.float()[:, None] * 2.0 ** -torch.arange(hd, dtype=torch.float32))
+    q = heads(h @ w["l0.mixer.q_proj.weight"].T) + add
+    k = heads(h @ w["l0.mixer.k_proj.weight"].T) + add
+    v = heads(h @ w["l0.mixer.v_proj.weight"].T)
+    a = P.attention(q, k, v, pos, pos, 0.25).transpose(0, 1).reshape(s, H * hd)
+    x = x + a @ w["l0.mixer.o_proj.weight"].T
+    h = P.rmsnorm(x, w["l0.n2.weight"], 1e-5)
+    probs = torch.softmax(h @ w["l0.ff.router.weight"].T, -1)
+    w_in, w_out = w["l0.ff.w_in"].view(3, 24, d), w["l0.ff.w_out"].view(3, d, 24)
+    out = torch.zeros_like(x)
+    for t in range(s):
+        e = int(probs[t].argmax())
+        out[t] = (w_out[e] @ torch.relu(w_in[e] @ h[t])) * probs[t, e]
+    x = x + out
+    # layer 1: the standard layer
+    cos, sin = P.rope_tables(hd, 128, 100.0)
+    acfg = dict(num_attention_heads=H, num_key_value_heads=H, head_dim=hd, hidden_size=d)
+    a, _ = P.attention_layer(P.rmsnorm(x, w["l1.n1.weight"], 1e-5), pos, w, "l1.mixer", acfg, cos, sin)
+    x = x + a
+    h = P.rmsnorm(x, w["l1.n2.weight"], 1e-5)
+    x = x + P.swiglu(h, w["l1.ff.gate_proj.weight"], w["l1.ff.up_proj.weight"],
+                     w["l1.ff.down_proj.weight"])
+    return P.rmsnorm(x, w["out_norm.weight"], 1e-5) @ w["emb.weight"].T
+
+
+def test_toy_routed_feed_forward_and_another_position_encoding(tmp_path):
+    """A feed-forward with routing and a position encoding that is not rotary are registered
+    from here, built by the framework from a configuration and stepped (whole prompts, portions
+    of changing size, mixed batches with reused pages, and captured decode steps) without a
+    change to the framework's files."""
+    import trace_util as T
+    from scratch_llm_b200.engine import ModelRunner, load_model
+    from scratch_llm_b200.weights import write_random_model
+    Toy = make_toy_routed()
+    cfg = Toy(width=36, n_vocab=70)
+    d = write_random_model(cfg, tmp_path / "toy_routed", seed=6, std=0.15, dtype="float32")
+    _, w = P.read_model_dir(d)
+    model = load_model(d, "float32", verbose=False)
+    reqs = T.make_requests(70, [37, 5, 64, 20, 9], seed=3)
+    want = {rid: toy_routed_plain(cfg, w, toks) for rid, toks in reqs.items()}
+    # the router's choices are not all the same: the test would else say little
+    h = torch.randn(50, 36)
+    assert len(set((h @ w["l0.ff.router.weight"].T).argmax(-1).tolist())) > 1
+    for way in (T.whole, T.tail_one_by_one, T.changing_portions, T.mixed):
+        steps = way(reqs)
+        runner = ModelRunner(model, 8, -(-T.peak_tokens(steps) // 8), 4)
+        with torch.no_grad():
+            got = T.run_in_process(runner, steps)
+        for (rid, pos), row in got.items():
+            torch.testing.assert_close(row, want[rid][pos], rtol=1e-4, atol=2e-5,
+                                       msg=lambda m: f"{way.__name__} {rid} {pos}: {m}")
