@@ -19,7 +19,7 @@ SMALL_BATCH = 8
 #: from this many tokens on, gate/up + SwiGLU run on the fused tcgen05 kernel (below it the
 #: 128-token tiles leave too many of the 148 SMs idle and the library product plus a separate
 #: activation kernel is faster)
-FUSED_GEMM_MIN_TOKENS = 768
+FUSED_GEMM_MIN_TOKENS = 512
 
 
 class Linear:
