@@ -328,6 +328,12 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool = 
     return out
 
 
+def gemm_tc_set_pairs(on: bool) -> None:
+    """Choose the tcgen05 GEMM kernel: pairs of SMs with 256 x 256 tiles (the default) or single
+    SMs with 128 x 256 tiles."""
+    _core("sllm_gemm_tcgen05").sllm_gemm_tc_set_pairs(c_int(int(on)))
+
+
 def gemm_tc_error() -> int:
     """The first error a bounded wait inside gemm_tc recorded since the last call (0 = none).
     Synchronises the device."""

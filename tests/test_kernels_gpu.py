@@ -179,8 +179,20 @@ def test_gemv_persistent_bulk_copies(ops, m, n, k):
 
 
 @pytest.mark.parametrize("m, n, k", [(128, 256, 64), (128, 256, 256), (256, 512, 192), (300, 600, 200),
-                                     (5, 40, 72), (2048, 1024, 512), (130, 6144, 4096)])
-def test_gemm_tcgen05(ops, m, n, k):
+                                     (5, 40, 72), (2048, 1024, 512), (130, 6144, 4096),
+                                     (513, 2560, 1024)])
+@pytest.mark.parametrize("pairs", [True, False])
+def test_gemm_tcgen05(ops, m, n, k, pairs):
+    """Both kernels: tiles of 256 x 256 on pairs of SMs (cta_group::2), and tiles of 128 x 256 on
+    single SMs."""
+    ops.gemm_tc_set_pairs(pairs)
+    try:
+        _gemm_tcgen05_case(ops, m, n, k)
+    finally:
+        ops.gemm_tc_set_pairs(True)
+
+
+def _gemm_tcgen05_case(ops, m, n, k):
     g = torch.Generator().manual_seed(m + n + k)
     if k <= 256:   # small integers: every product and sum is exact, also in bfloat16
         x = torch.randint(-1, 2, (m, k), generator=g).to(torch.bfloat16)
