@@ -107,6 +107,10 @@ struct AttnArgs {
     bf16* out; int64_t out_stride;
     float* part_o; float* part_lse; int n_splits;
     int H; int G; float scale_log2; int window;
+    // attn_decode_cs_kernel only.  cos_t != nullptr: q, k and v are taken from the step's fused
+    // projection as they are (q points at its first column): the kernel rotates q and the row's
+    // new key itself and, if write_kv, stores the new key and value.
+    const float* cos_t; const float* sin_t; int interleaved; int write_kv;
 };
 
 template <bool SPLIT>
@@ -409,6 +413,7 @@ constexpr int CS_LDP = BKV + 8;        // row stride of the probability tile (el
 constexpr int CS_OC = HD / NWARP;      // output columns per warp
 constexpr int CS_OT = CS_OC / 8 > 0 ? CS_OC / 8 : 1;   // 8-wide output tiles per warp
 
+
 __global__ void __launch_bounds__(THREADS, 3) attn_decode_cs_kernel(const AttnArgs a) {
     using M = Mode<true>;
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -458,6 +463,43 @@ __global__ void __launch_bounds__(THREADS, 3) attn_decode_cs_kernel(const AttnAr
     cp_async_commit();
 
     const int64_t v_off = (int64_t)a.G * a.page_size * HD;
+    // With the rotation fused (rows of one new token at position pos0): everything it needs
+    // from global memory is requested now, so that it has arrived when the tiles have.
+    // Thread t rotates pair t % (HD / 2) of the query heads t / (HD / 2), ... and of the new key,
+    // and carries element t, t + THREADS, ... of the new value.
+    const bool fused_rope = a.cos_t != nullptr;
+    const int new_tile = fused_rope && a.write_kv ? (pos0 - k_lo) / BKV : -1;
+    const bool owns_new = new_tile >= tile_begin && new_tile < tile_end;
+    constexpr int HALF = HD / 2;
+    constexpr int V_PER = (HD + THREADS - 1) / THREADS, K_PER = (HALF + THREADS - 1) / THREADS;
+    float rope_c[K_PER], rope_s[K_PER];
+    __nv_bfloat162 k_new[K_PER];
+    bf16 v_new[V_PER];
+    if (fused_rope) {
+#pragma unroll
+        for (int u = 0; u < K_PER; ++u) {
+            const int j = tid + u * THREADS;
+            if (j < HALF) {
+                rope_c[u] = a.cos_t[(int64_t)pos0 * HALF + j];
+                rope_s[u] = a.sin_t[(int64_t)pos0 * HALF + j];
+            }
+        }
+        if (owns_new) {
+            const bf16* k_src = a.q + (int64_t)t0 * a.q_stride + (int64_t)(a.H + g) * HD;
+            const bf16* v_src = k_src + (int64_t)a.G * HD;
+#pragma unroll
+            for (int u = 0; u < K_PER; ++u) {
+                const int j = tid + u * THREADS;
+                if (j < HALF) {
+                    const int i0 = a.interleaved ? 2 * j : j, i1 = a.interleaved ? 2 * j + 1 : j + HALF;
+                    k_new[u] = __halves2bfloat162(k_src[i0], k_src[i1]);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < V_PER; ++u)
+                if (tid + u * THREADS < HD) v_new[u] = v_src[tid + u * THREADS];
+        }
+    }
     auto locate_tile = [&](int tile, int slot) {
         if (tid < BKV) {
             const int kpos = k_lo + tile * BKV + tid;
@@ -492,6 +534,24 @@ __global__ void __launch_bounds__(THREADS, 3) attn_decode_cs_kernel(const AttnAr
     locate_tile(tile_begin + 1, 1);
     cp_async_wait<1>();
     __syncthreads();
+    if (fused_rope) {
+        // q as the projection left it: rotate the row's GS heads here (32-bit, one rounding,
+        // the arithmetic of rope_cache.cu)
+#pragma unroll
+        for (int u = 0; u < K_PER; ++u) {
+            const int j = tid + u * THREADS;
+            if (j < HALF) {
+                const int i0 = a.interleaved ? 2 * j : j, i1 = a.interleaved ? 2 * j + 1 : j + HALF;
+                for (int i = 0; i < GS; ++i) {
+                    const float x0 = __bfloat162float(Qs[i * LDS + i0]);
+                    const float x1 = __bfloat162float(Qs[i * LDS + i1]);
+                    Qs[i * LDS + i0] = __float2bfloat16_rn(x0 * rope_c[u] - x1 * rope_s[u]);
+                    Qs[i * LDS + i1] = __float2bfloat16_rn(x0 * rope_s[u] + x1 * rope_c[u]);
+                }
+            }
+        }
+        __syncthreads();
+    }
 
     uint32_t qf[KSTEPS][4];
 #pragma unroll
@@ -522,6 +582,38 @@ __global__ void __launch_bounds__(THREADS, 3) attn_decode_cs_kernel(const AttnAr
         cp_async_wait<1>();
         __syncthreads();
         locate_tile(tile + 2, stage);
+        if (tile == new_tile) {
+            // the row's new key (rotated here) and value: into the cache for the steps to come,
+            // and over what the copy fetched from that place of the cache for this one
+            const int in_tile = pos0 - k_lo - tile * BKV;
+            bf16* k_row = Ks + stage * BKV * LDS + in_tile * LDS;
+            bf16* v_row = Vs + stage * BKV * LDS + in_tile * LDS;
+            const int page = a.block_table[(int64_t)r * a.table_stride + pos0 / a.page_size];
+            bf16* k_dst = const_cast<bf16*>(a.pages) +
+                          (((long long)page * 2 * a.G + g) * a.page_size + pos0 % a.page_size) * HD;
+            bf16* v_dst = k_dst + v_off;
+#pragma unroll
+            for (int u = 0; u < K_PER; ++u) {
+                const int j = tid + u * THREADS;
+                if (j < HALF) {
+                    const int i0 = a.interleaved ? 2 * j : j, i1 = a.interleaved ? 2 * j + 1 : j + HALF;
+                    const float x0 = __low2float(k_new[u]), x1 = __high2float(k_new[u]);
+                    const bf16 r0 = __float2bfloat16_rn(x0 * rope_c[u] - x1 * rope_s[u]);
+                    const bf16 r1 = __float2bfloat16_rn(x0 * rope_s[u] + x1 * rope_c[u]);
+                    k_row[i0] = r0; k_row[i1] = r1;
+                    k_dst[i0] = r0; k_dst[i1] = r1;
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < V_PER; ++u) {
+                const int i = tid + u * THREADS;
+                if (i < HD) {
+                    v_row[i] = v_new[u];
+                    v_dst[i] = v_new[u];
+                }
+            }
+            __syncthreads();
+        }
         const bf16* ks_s = Ks + stage * BKV * LDS + key_lo_w * LDS;
         const bf16* vs_s = Vs + stage * BKV * LDS;
         const int kt = k_lo + tile * BKV + key_lo_w;
@@ -724,6 +816,7 @@ SLLM_EXPORT int sllm_attn_mma(const void* q, int64_t q_stride, const void* pages
     a.page_size = page_size; a.row_start = row_start; a.row_pos0 = row_pos0; a.row_list = row_list;
     a.out = (bf16*)out; a.out_stride = out_stride;
     a.part_o = nullptr; a.part_lse = nullptr; a.n_splits = 1;
+    a.cos_t = nullptr; a.sin_t = nullptr; a.interleaved = 1; a.write_kv = 0;
     a.H = H; a.G = G; a.scale_log2 = scale * 1.4426950408889634f; a.window = window;
     const int GS = H / G;
     cudaError_t e;
@@ -765,6 +858,64 @@ SLLM_EXPORT int sllm_attn_mma(const void* q, int64_t q_stride, const void* pages
     }
     return 0;
 }
+
+#if SLLM_HEAD_DIM % 64 == 0
+// 1: this head size has the decode kernel that can rotate q and the new key and store the new
+// key and value itself.
+SLLM_EXPORT int sllm_attn_mma_decode_fused_supported() { return 1; }
+
+// The decode kernel for rows of ONE new token (groups of up to 16 query heads) that takes q, k
+// and v as the projection left them.  cos_t / sin_t: [positions, HD / 2] float tables; `qkv` is
+// the step's fused projection [tokens, (H + 2 G) * HD] (q heads, k heads, v heads); the kernel
+// rotates q and the new key (adjacent pairs if `interleaved`, else the halves) and, if
+// `write_kv`, stores the rotated key and the value at the row's position in the cache.
+// `scratch` as in sllm_attn_mma for n_splits > 1 (a merge kernel follows).
+SLLM_EXPORT int sllm_attn_mma_decode(const void* qkv, int64_t qkv_stride, void* pages,
+                                     const int* block_table, int table_stride, int page_size,
+                                     const int* row_start, const int* row_pos0,
+                                     const int* row_list, int n_list, void* out,
+                                     int64_t out_stride, int H, int G, float scale, int window,
+                                     int n_splits, float* scratch, int64_t n_tokens_total,
+                                     const float* cos_t, const float* sin_t, int interleaved,
+                                     int write_kv, cudaStream_t stream) {
+    if (n_list <= 0) return 0;
+    if (H <= 0 || G <= 0 || H % G != 0 || page_size <= 0 || window < 0 || n_list > 65535 ||
+        G > 65535 || (qkv_stride % 8) != 0 || (out_stride % 2) != 0 || n_splits < 1 || H / G > 16)
+        return (int)cudaErrorInvalidValue;
+    if (((uintptr_t)qkv & 15) || ((uintptr_t)pages & 15) || ((uintptr_t)out & 3) || !cos_t || !sin_t)
+        return (int)cudaErrorInvalidValue;
+    AttnArgs a;
+    a.q = (const bf16*)qkv; a.q_stride = qkv_stride;
+    a.pages = (const bf16*)pages; a.block_table = block_table; a.table_stride = table_stride;
+    a.page_size = page_size; a.row_start = row_start; a.row_pos0 = row_pos0; a.row_list = row_list;
+    a.out = (bf16*)out; a.out_stride = out_stride;
+    a.part_o = nullptr; a.part_lse = nullptr; a.n_splits = n_splits;
+    a.H = H; a.G = G; a.scale_log2 = scale * 1.4426950408889634f; a.window = window;
+    a.cos_t = cos_t; a.sin_t = sin_t; a.interleaved = interleaved; a.write_kv = write_kv;
+    if (n_splits > 1) {
+        if (!scratch) return (int)cudaErrorInvalidValue;
+        a.part_o = scratch;
+        a.part_lse = scratch + n_tokens_total * H * n_splits * HD;
+    }
+    const size_t smem = smem_bytes<true>();
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_cs_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    dim3 grid(n_splits, n_list, G);   // one tile of 16 packed queries per (row, kv head)
+    e = sllm_launch_pdl(attn_decode_cs_kernel, grid, dim3(THREADS), smem, stream, a);
+    if (e != cudaSuccess) return (int)e;
+    if (n_splits > 1) {
+        dim3 mgrid(n_list, H);
+        e = sllm_launch_pdl(attn_merge_kernel, mgrid, dim3(HD >= 128 ? 128 : 32), 0, stream,
+                            (const float*)a.part_o, (const float*)a.part_lse, n_splits, row_start,
+                            row_list, (bf16*)out, out_stride, H);
+        if (e != cudaSuccess) return (int)e;
+    }
+    return 0;
+}
+#else
+SLLM_EXPORT int sllm_attn_mma_decode_fused_supported() { return 0; }
+#endif
 
 // ------------------------------------------------------------------------------------------
 // The split kernel for callers that must not allocate: see attention_mma_noalloc.h.

@@ -454,6 +454,70 @@ def attention_mma(q: torch.Tensor, pages: torch.Tensor, block_table: torch.Tenso
     return out
 
 
+def attention_decode_fused_supported(head_dim: int) -> bool:
+    """Whether this head size has the decode attention kernel that rotates q and the new key and
+    stores the new key and value itself (head sizes that are multiples of 64)."""
+    if head_dim % 16 or not 16 <= head_dim <= MMA_MAX_HEAD_DIM:
+        return False
+    return bool(_load(*attention_mma_library(head_dim)).sllm_attn_mma_decode_fused_supported())
+
+
+def attention_mma_decode(qkv: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor,
+                         page_size: int, row_start: torch.Tensor, row_pos0: torch.Tensor,
+                         out: torch.Tensor, row_list: torch.Tensor | None, n_list: int,
+                         n_heads: int, n_kv_heads: int, head_dim: int, scale: float,
+                         window: int | None, cos: torch.Tensor, sin: torch.Tensor,
+                         interleaved: bool, write: bool, n_splits: int = 1,
+                         scratch: torch.Tensor | None = None) -> torch.Tensor:
+    """Decode attention (rows of one new token) over the paged cache on the tensor cores, for
+    head sizes that are multiples of 64, straight from the step's fused projection ``qkv``
+    [tokens, (H + 2 G) * hd] as the product left it: the kernel rotates q and the new key itself
+    (``cos``/``sin`` tables, adjacent pairs if ``interleaved``) and, if ``write``, stores the new
+    key and value into ``pages``: no separate rotate-and-store kernel runs.  ``scratch`` as in
+    :func:`attention_mma` for several splits."""
+    _need(qkv, torch.bfloat16, "qkv", contiguous=False)
+    _need(pages, torch.bfloat16, "pages")
+    _need(out, torch.bfloat16, "out", contiguous=False)
+    _need(block_table, torch.int32, "block_table", contiguous=False)
+    _need(row_start, torch.int32, "row_start")
+    _need(row_pos0, torch.int32, "row_pos0")
+    _need(cos, torch.float32, "cos")
+    _need(sin, torch.float32, "sin")
+    if row_list is not None:
+        _need(row_list, torch.int32, "row_list")
+    if qkv.stride(1) != 1 or out.stride(1) != 1 \
+            or qkv.shape[1] != (n_heads + 2 * n_kv_heads) * head_dim \
+            or out.shape != (qkv.shape[0], n_heads * head_dim):
+        raise KernelError("attention qkv/out layout")
+    if pages.shape[1:] != (2, n_kv_heads, page_size, head_dim):
+        raise KernelError(f"pages must be [n_pages, 2, {n_kv_heads}, {page_size}, {head_dim}], "
+                          f"got {list(pages.shape)}")
+    if not attention_decode_fused_supported(head_dim) or n_heads % n_kv_heads \
+            or n_heads // n_kv_heads > 16:
+        raise KernelError(f"attention_mma_decode takes head sizes that are multiples of 64 and "
+                          f"groups of up to 16 query heads; got {head_dim}, {n_heads}/{n_kv_heads}")
+    if cos.shape[1] != head_dim // 2 or sin.shape != cos.shape:
+        raise KernelError("rotary table width")
+    n_tokens = qkv.shape[0]
+    if n_splits > 1:
+        need = attention_mma_scratch_floats(n_tokens, n_heads, head_dim, n_splits)
+        if scratch is None:
+            raise KernelError("several splits need scratch memory for their partial results")
+        _need(scratch, torch.float32, "scratch")
+        if scratch.numel() < need:
+            raise KernelError(f"attention scratch holds {scratch.numel()} floats, {need} needed")
+    if block_table.stride(1) != 1:
+        raise KernelError("block_table rows must be contiguous")
+    _check(_load(*attention_mma_library(head_dim)).sllm_attn_mma_decode(
+        _ptr(qkv), c_int64(qkv.stride(0)), _ptr(pages), _ptr(block_table),
+        c_int(block_table.stride(0)), c_int(page_size), _ptr(row_start), _ptr(row_pos0),
+        _ptr(row_list), c_int(n_list), _ptr(out), c_int64(out.stride(0)), c_int(n_heads),
+        c_int(n_kv_heads), c_float(scale), c_int(window or 0), c_int(n_splits), _ptr(scratch),
+        c_int64(n_tokens), _ptr(cos), _ptr(sin), c_int(int(interleaved)), c_int(int(write)),
+        _stream()), "attention_mma_decode")
+    return out
+
+
 def attention_tc(q: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor, page_size: int,
                  row_start: torch.Tensor, row_pos0: torch.Tensor, out: torch.Tensor,
                  row_list: torch.Tensor | None, n_list: int, max_new: int, n_heads: int,

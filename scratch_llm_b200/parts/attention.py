@@ -85,10 +85,17 @@ class GQAttention(Mixer):
                            batch.positions)
             cos = sin = None
             interleaved = True
+        out = torch.empty((qkv.shape[0], H * hd), dtype=qkv.dtype, device=qkv.device)
+        if (cos is not None and qkv.dtype == torch.bfloat16 and batch.n_multi == 0
+                and batch.n_single > 0 and H // G <= 16
+                and ops.attention_decode_fused_supported(hd)):
+            # a step of single tokens: the decode kernel rotates q and the new keys itself and
+            # stores the new keys and values (one launch fewer, q and k make no round trip)
+            self._decode_fused(qkv, out, batch, cache, (cos, sin, interleaved, write))
+            return self.o(out)
         ops.rope_kv_write(qkv, batch.positions, batch.token_row, cos, sin, cache.pages,
                           cache.block_table, cache.page_size, H, G, hd, interleaved, write)
         q = qkv[:, :H * hd]
-        out = torch.empty((qkv.shape[0], H * hd), dtype=qkv.dtype, device=qkv.device)
         if qkv.dtype == torch.bfloat16 and hd <= ops.MMA_MAX_HEAD_DIM:
             self._attend_tensor_cores(q, out, batch, cache)
         else:
@@ -96,6 +103,25 @@ class GQAttention(Mixer):
                                batch.row_start, batch.row_pos0, out, batch.n_rows,
                                batch.max_new, H, G, hd, self.scale, self.window)
         return self.o(out)
+
+    def _n_splits(self, batch) -> int:
+        H, G = self.n_heads, self.n_kv_heads
+        return decode_splits(batch.n_single * G * (-(-(H // G) // 16)),
+                             batch.context_bucket if self.window is None
+                             else min(batch.context_bucket, self.window + 64))
+
+    def _decode_fused(self, qkv, out, batch, cache: CacheView, rope) -> None:
+        H, G, hd = self.n_heads, self.n_kv_heads, self.head_dim
+        n_splits = self._n_splits(batch)
+        scratch = None
+        if n_splits > 1:
+            scratch = torch.empty(ops.attention_mma_scratch_floats(qkv.shape[0], H, hd, n_splits),
+                                  dtype=torch.float32, device=qkv.device)
+        cos, sin, interleaved, write = rope
+        ops.attention_mma_decode(qkv, cache.pages, cache.block_table, cache.page_size,
+                                 batch.row_start, batch.row_pos0, out, batch.single_rows,
+                                 batch.n_single, H, G, hd, self.scale, self.window, cos, sin,
+                                 interleaved, write, n_splits, scratch)
 
     def _attend_tensor_cores(self, q, out, batch, cache: CacheView) -> None:
         """Rows with several new tokens go to the wide kernel, rows with one to the split
@@ -114,9 +140,7 @@ class GQAttention(Mixer):
                                   batch.max_new_multi, H, G, hd, self.scale, self.window,
                                   split=False)
         if batch.n_single:
-            n_splits = decode_splits(batch.n_single * G * (-(-(H // G) // 16)),
-                                     batch.context_bucket if self.window is None
-                                     else min(batch.context_bucket, self.window + 64))
+            n_splits = self._n_splits(batch)
             scratch = None
             if n_splits > 1:
                 scratch = torch.empty(ops.attention_mma_scratch_floats(q.shape[0], H, hd, n_splits),

@@ -321,6 +321,60 @@ def test_attention_on_tensor_cores(ops, H, G, hd, page, window, n_splits):
         check_attention(case, out.cpu().float(), every, "bfloat16", H, hd, window)
 
 
+@pytest.mark.parametrize("n_splits", [1, 3, 8])
+@pytest.mark.parametrize("interleaved", [True, False])
+@pytest.mark.parametrize("H, G, hd, page, window", [(8, 2, 64, 16, None), (32, 8, 128, 64, None),
+                                                    (6, 3, 128, 8, 70), (16, 1, 64, 16, None)])
+def test_decode_attention_fused_with_rotation(ops, H, G, hd, page, window, n_splits, interleaved):
+    """The decode kernel that takes q, k and v as the projection left them (rotates q and the new
+    key, stores key and value) gives, bit for bit, what the separate kernels give (rotation and
+    store, then split attention), and leaves the same cache."""
+    import math
+    contexts = [0, 1, 15, 16, 63, 64, 200, 517]          # keys cached before the step
+    n = len(contexts)
+    max_pos = 600
+    cos, sin = P.rope_tables(hd, max_pos, 10000.0)
+    per = [-(-(c + 1) // page) for c in contexts]
+    n_pages = sum(per) + 2
+    g = torch.Generator().manual_seed(3)
+    pages = (torch.randn(n_pages, 2, G, page, hd, generator=g) * 0.5).to(torch.bfloat16)
+    order = torch.randperm(n_pages, generator=g).tolist()
+    table = torch.full((n, max(per)), -1, dtype=torch.int32)
+    for r in range(n):
+        for p in range(per[r]):
+            table[r, p] = order.pop()
+    qkv = (torch.randn(n, (H + 2 * G) * hd, generator=g)).to(torch.bfloat16)
+    row_start = torch.arange(n + 1, dtype=torch.int32).cuda()
+    row_pos0 = torch.tensor(contexts, dtype=torch.int32).cuda()
+    rows = torch.arange(n, dtype=torch.int32).cuda()
+    scale = 1.0 / math.sqrt(hd)
+    scratch = torch.empty(ops.attention_mma_scratch_floats(n, H, hd, n_splits) + 1,
+                          dtype=torch.float32, device="cuda")
+    # the separate kernels
+    qkv_a, pages_a = qkv.clone().cuda(), pages.clone().cuda()
+    ops.rope_kv_write(qkv_a, row_pos0, rows, cos.cuda(), sin.cuda(), pages_a, table.cuda(), page,
+                      H, G, hd, interleaved, True)
+    out_a = torch.full((n, H * hd), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.attention_mma(qkv_a[:, :H * hd], pages_a, table.cuda(), page, row_start, row_pos0, out_a,
+                      rows, n, 1, H, G, hd, scale, window, split=True, n_splits=n_splits,
+                      scratch=scratch)
+    # the one kernel
+    pages_b = pages.clone().cuda()
+    out_b = torch.full((n, H * hd), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.attention_mma_decode(qkv.cuda(), pages_b, table.cuda(), page, row_start, row_pos0, out_b,
+                             rows, n, H, G, hd, scale, window, cos.cuda(), sin.cuda(), interleaved,
+                             True, n_splits, scratch)
+    assert torch.equal(out_b.cpu(), out_a.cpu())
+    assert torch.equal(pages_b.cpu(), pages_a.cpu())
+    # a layer that reads another layer's cache: nothing is stored
+    pages_c = pages_a.clone()
+    out_c = torch.full((n, H * hd), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.attention_mma_decode(qkv.cuda(), pages_c, table.cuda(), page, row_start, row_pos0, out_c,
+                             rows, n, H, G, hd, scale, window, cos.cuda(), sin.cuda(), interleaved,
+                             False, n_splits, scratch)
+    assert torch.equal(out_c.cpu(), out_a.cpu()) and torch.equal(pages_c.cpu(), pages_a.cpu())
+
+
 @pytest.mark.parametrize("H, G, hd, page", [(8, 2, 64, 16), (32, 8, 128, 16), (8, 1, 128, 32),
                                            (4, 4, 64, 8), (2, 1, 128, 128), (4, 2, 256, 16),
                                            (2, 2, 192, 32)])
