@@ -33,8 +33,9 @@ def decode_splits(base_ctas: int, context: int, slots: int = 3 * 148) -> int:
     captured graph.  ``slots``: CTAs of the split kernel resident on the GPU at once."""
     tiles = max(1, -(-context // 64))
     best, best_cost = 1, None
-    for n in range(1, min(32, tiles) + 1):
-        cost = -(-base_ctas * n // slots) * (-(-tiles // n) + 2) + (1 if n > 1 else 0)
+    for n in range(1, min(64, tiles) + 1):
+        # waves x (key tiles per CTA + a CTA's fixed cost) + what the merge reads per split
+        cost = -(-base_ctas * n // slots) * (-(-tiles // n) + 2) + (0.1 * n if n > 1 else 0)
         if best_cost is None or cost < best_cost:
             best, best_cost = n, cost
     return best
