@@ -139,7 +139,8 @@ def test_gemv_streams_weights_once(ops, m, n, k):
 
 @pytest.mark.parametrize("m, n, k", [(1, 16, 1024), (3, 100, 1536), (8, 4096 + 8, 4096),
                                      (5, 512, 14336), (8, 6144, 4096), (2, 44, 5120),
-                                     (7, 9000, 2048), (4, 40000, 1024)])
+                                     (7, 9000, 2048), (4, 40000, 1024), (4, 1004, 13824),
+                                     (8, 5120 * 3, 5120)])
 def test_gemv_persistent_bulk_copies(ops, m, n, k):
     """The persistent small-batch product (weights through shared memory by bulk copies, four
     ranges of K combined by ticket): values, launches in a row on the shared workspace, bitwise
