@@ -305,7 +305,7 @@ def main() -> int:
     achieved = step_bytes / (ms * 1e-3) / 1e9
     flops = prefill_flops(cfg, args.prefill_tokens)
     out = {
-        "metric": "decode tok/s at batch 8 (Llama-3-8B sizes, random weights)",
+        "metric": f"decode tok/s at batch {args.batch} (Llama-3-8B sizes, random weights)",
         "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
