@@ -751,31 +751,49 @@ __global__ void __launch_bounds__(THREADS, 3) attn_decode_cs_kernel(const AttnAr
 #endif  // SLLM_HEAD_DIM % 64 == 0
 
 // Combines the partial results of the splits: o = sum_s 2^(lse_s - m) o_s / sum_s 2^(lse_s - m).
-// grid (listed rows, H); a block walks the row's tokens.
-__global__ void attn_merge_kernel(const float* __restrict__ part_o,
-                                  const float* __restrict__ part_lse, int n_splits,
-                                  const int* __restrict__ row_start,
-                                  const int* __restrict__ row_list, bf16* __restrict__ out,
-                                  int64_t out_stride, int H) {
+// grid (listed rows, H / 4), 4 warps: a warp takes one head and walks the row's tokens; a lane
+// takes 4 consecutive elements of the head at a time.  The sums run over the splits in their
+// order (so the result does not depend on the launch's shape); the loop is unrolled so that
+// the loads of several splits are in flight at once.
+constexpr int MERGE_WARPS = 4;
+__global__ void __launch_bounds__(MERGE_WARPS * 32) attn_merge_kernel(
+        const float* __restrict__ part_o, const float* __restrict__ part_lse, int n_splits,
+        const int* __restrict__ row_start, const int* __restrict__ row_list,
+        bf16* __restrict__ out, int64_t out_stride, int H) {
     pdl_wait();
     pdl_trigger();
     const int r = row_list ? row_list[blockIdx.x] : blockIdx.x;
-    const int head = blockIdx.y;
+    const int head = blockIdx.y * MERGE_WARPS + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (head >= H) return;
     for (int t = row_start[r]; t < row_start[r + 1]; ++t) {
         const int64_t qh = (int64_t)t * H + head;
+        const float* lse = part_lse + qh * n_splits;
         float mm = -INFINITY;
-        for (int s = 0; s < n_splits; ++s) mm = fmaxf(mm, part_lse[qh * n_splits + s]);
-        for (int d = threadIdx.x; d < HD; d += blockDim.x) {
-            float num = 0.f, den = 0.f;
+        for (int s = lane; s < n_splits; s += 32) mm = fmaxf(mm, lse[s]);
+        mm = warp_max(mm);
+        for (int d = lane * 4; d < HD; d += 128) {
+            float4 num = make_float4(0.f, 0.f, 0.f, 0.f);
+            float den = 0.f;
             if (mm != -INFINITY) {
+                const float* o = part_o + qh * n_splits * HD + d;
+#pragma unroll 8
                 for (int s = 0; s < n_splits; ++s) {
-                    const float f = exp2f(part_lse[qh * n_splits + s] - mm);
-                    num += f * part_o[(qh * n_splits + s) * HD + d];
+                    const float f = exp2f(lse[s] - mm);
+                    const float4 v = *reinterpret_cast<const float4*>(o + (int64_t)s * HD);
+                    num.x += f * v.x;
+                    num.y += f * v.y;
+                    num.z += f * v.z;
+                    num.w += f * v.w;
                     den += f;
                 }
             }
-            out[(int64_t)t * out_stride + (int64_t)head * HD + d] =
-                __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+            const bool some = den > 0.f;
+            __nv_bfloat162 lo = __floats2bfloat162_rn(some ? num.x / den : 0.f, some ? num.y / den : 0.f);
+            __nv_bfloat162 hi = __floats2bfloat162_rn(some ? num.z / den : 0.f, some ? num.w / den : 0.f);
+            bf16* dst = out + (int64_t)t * out_stride + (int64_t)head * HD + d;
+            // out_stride is even and HD a multiple of 16: 4-byte stores are aligned
+            *reinterpret_cast<__nv_bfloat162*>(dst) = lo;
+            *reinterpret_cast<__nv_bfloat162*>(dst + 2) = hi;
         }
     }
 }
@@ -850,8 +868,8 @@ SLLM_EXPORT int sllm_attn_mma(const void* q, int64_t q_stride, const void* pages
 #endif
     if (e != cudaSuccess) return (int)e;
     if (n_splits > 1) {
-        dim3 mgrid(n_list, H);
-        e = sllm_launch_pdl(attn_merge_kernel, mgrid, dim3(HD >= 128 ? 128 : 32), 0, stream,
+        dim3 mgrid(n_list, (H + MERGE_WARPS - 1) / MERGE_WARPS);
+        e = sllm_launch_pdl(attn_merge_kernel, mgrid, dim3(MERGE_WARPS * 32), 0, stream,
                             (const float*)a.part_o, (const float*)a.part_lse, n_splits, row_start,
                             row_list, (bf16*)out, out_stride, H);
         if (e != cudaSuccess) return (int)e;
@@ -905,8 +923,8 @@ SLLM_EXPORT int sllm_attn_mma_decode(const void* qkv, int64_t qkv_stride, void* 
     e = sllm_launch_pdl(attn_decode_cs_kernel, grid, dim3(THREADS), smem, stream, a);
     if (e != cudaSuccess) return (int)e;
     if (n_splits > 1) {
-        dim3 mgrid(n_list, H);
-        e = sllm_launch_pdl(attn_merge_kernel, mgrid, dim3(HD >= 128 ? 128 : 32), 0, stream,
+        dim3 mgrid(n_list, (H + MERGE_WARPS - 1) / MERGE_WARPS);
+        e = sllm_launch_pdl(attn_merge_kernel, mgrid, dim3(MERGE_WARPS * 32), 0, stream,
                             (const float*)a.part_o, (const float*)a.part_lse, n_splits, row_start,
                             row_list, (bf16*)out, out_stride, H);
         if (e != cudaSuccess) return (int)e;
@@ -991,8 +1009,8 @@ SLLM_EXPORT int sllm_attn_mma_split_noalloc(const void* q, int64_t q_stride, con
     attn_mma_kernel<true><<<grid, THREADS, smem, stream>>>(a);
     SLLM_LAUNCH_CHECK();
     if (n_splits > 1) {
-        dim3 mgrid(n_list, H);
-        attn_merge_kernel<<<mgrid, HD >= 128 ? 128 : 32, 0, stream>>>(
+        dim3 mgrid(n_list, (H + MERGE_WARPS - 1) / MERGE_WARPS);
+        attn_merge_kernel<<<mgrid, MERGE_WARPS * 32, 0, stream>>>(
             a.part_o, a.part_lse, n_splits, row_start, row_list, (bf16*)out, out_stride, H);
         SLLM_LAUNCH_CHECK();
     }

@@ -108,7 +108,15 @@ def _check(code: int, what: str) -> None:
                           f"({'invalid value: a size this kernel does not take' if code == 1 else 'see cudaError_t'})")
 
 
+# the current stream's handle without building a torch.cuda.Stream object (3 us a call, which
+# is a third of a launch's host cost in steps that run outside a captured graph)
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_current_device = getattr(torch._C, "_cuda_getDevice", None)
+
+
 def _stream() -> c_void_p:
+    if _raw_stream is not None and _current_device is not None:
+        return c_void_p(_raw_stream(_current_device()))
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
