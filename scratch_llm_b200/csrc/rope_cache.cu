@@ -9,6 +9,7 @@
 // place.  k is rotated and stored, v is copied, into
 //   pages[page, 0 (K) | 1 (V), g, offset, :]     pages: [n_pages, 2, G, page_size, hd]
 // where page = block_table[row, position / page_size], offset = position % page_size.
+// A token whose row is -1 is padding: it is neither rotated nor stored.
 #include "common.cuh"
 
 namespace sllm {
@@ -26,6 +27,7 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
     pdl_wait();
     pdl_trigger();
     const int64_t n = blockIdx.x;
+    if (token_row[n] < 0) return;   // a padding token: it belongs to no row
     const int half = hd >> 1;
     const int local = threadIdx.x / half, j = threadIdx.x - local * half;
     const int head = blockIdx.y * heads_per_block + local;
@@ -104,6 +106,7 @@ __global__ void rope_kv_write_vec_kernel(__nv_bfloat16* __restrict__ qkv,
         const int64_t th = i / per_head;
         const int head = (int)(th % n_heads);
         const int64_t n = th / n_heads;
+        if (token_row[n] < 0) continue;   // a padding token: it belongs to no row
         const int pos = positions[n];
         bf16* h = qkv + n * (int64_t)(H + 2 * G) * hd + (int64_t)head * hd;
         // first and second group of 8 elements this thread owns, and its pairs' table offset

@@ -28,6 +28,45 @@ import numpy as np
 import torch
 
 
+@dataclass(frozen=True)
+class PadPlan:
+    """The sizes a small step is padded to, so that steps of many shapes share few captured
+    graphs.  Padding tokens follow the last row's tokens: id 0, position 0, ``token_row`` -1
+    (they belong to no row, nothing of them is stored and attention skips them).  Padding rows
+    have no tokens; the lists of single and multi rows are filled up with such a row."""
+
+    n_tokens: int
+    n_single: int
+    n_multi: int
+    n_out: int
+
+
+#: steps of up to this many tokens are padded and replayed as graphs; larger ones keep the
+#: device busy for longer than the host needs to launch them
+PAD_MAX_TOKENS = 512
+
+
+def _round_up(n: int, step: int) -> int:
+    return -(-n // step) * step
+
+
+def _next_power_of_two(n: int) -> int:
+    p = 1
+    while p < n:
+        p *= 2
+    return p
+
+
+def pad_plan(n_tokens: int, n_single: int, n_multi: int, n_out: int) -> PadPlan:
+    """Tokens go up to a multiple of 16 (of 64 above 128), single rows to a multiple of 8,
+    multi rows to a power of two, wanted places to a power of two up to 8 and to a multiple of
+    16 above; nothing wanted stays nothing wanted."""
+    tokens = _round_up(n_tokens, 16) if n_tokens <= 128 else _round_up(n_tokens, 64)
+    out = 0 if n_out == 0 else _next_power_of_two(n_out) if n_out <= 8 else _round_up(n_out, 16)
+    return PadPlan(tokens, _round_up(n_single, 8), _next_power_of_two(n_multi) if n_multi else 0,
+                   out)
+
+
 @dataclass
 class RowInput:
     """The next tokens of one request and the places among them whose logits are wanted."""
@@ -69,6 +108,11 @@ class StepBatch:
     # host copies, for parts that plan their launches from them
     host_row_new: list[int] = field(default_factory=list)
     host_row_pos0: list[int] = field(default_factory=list)
+    # a padded step (see PadPlan): tokens and wanted places that are real; the sizes above
+    # count the padding, and max_new / max_new_multi are then upper bounds
+    padded: bool = False
+    n_real_tokens: int = 0
+    n_real_out: int = 0
 
 
 class BatchStager:
@@ -145,10 +189,12 @@ def context_bucket(context: int) -> int:
 
 
 def build_batch(cache, stager: BatchStager, rows: Sequence[RowInput], vocab_size: int,
-                max_position: int, table_width: int | None = None) -> StepBatch:
+                max_position: int, table_width: int | None = None,
+                pad: bool = False) -> StepBatch:
     """Check the rows against the cache manager's view of their requests, pack the descriptor
     and copy it to the device.  ``table_width`` fixes the width of the block tables (for a
-    step that replays a captured CUDA graph, every array must keep its size and address)."""
+    step that replays a captured CUDA graph, every array must keep its size and address).
+    ``pad``: bring the step to the sizes of :func:`pad_plan`."""
     n_rows = len(rows)
     lens = [len(r.tokens) for r in rows]
     if n_rows and min(lens) < 1:
@@ -225,6 +271,10 @@ def build_batch(cache, stager: BatchStager, rows: Sequence[RowInput], vocab_size
     li = np.asarray(logit_index, dtype=np.int32)
     single = [i for i, n in enumerate(lens) if n == 1]
     multi = [i for i, n in enumerate(lens) if n > 1]
+    if pad:
+        return _padded_batch(stager, pad_plan(n_tokens, len(single), len(multi), li.size),
+                             token_ids, positions, token_row, row_start, row_pos0, row_slot, li,
+                             single, multi, tables, lens)
     dev = stager.upload([token_ids, positions, token_row, row_start, row_pos0, row_slot, li,
                          np.asarray(single, dtype=np.int32), np.asarray(multi, dtype=np.int32),
                          *tables])
@@ -238,4 +288,43 @@ def build_batch(cache, stager: BatchStager, rows: Sequence[RowInput], vocab_size
         multi_rows=dev[8], block_tables=dev[9:], n_single=len(single), n_multi=len(multi),
         max_new_multi=max((lens[i] for i in multi), default=0),
         max_context_single=ctx_single, context_bucket=context_bucket(ctx_single),
-        host_row_new=lens, host_row_pos0=row_pos0.tolist())
+        host_row_new=lens, host_row_pos0=row_pos0.tolist(), n_real_tokens=n_tokens,
+        n_real_out=len(logit_index))
+
+
+def _padded_batch(stager: BatchStager, plan: PadPlan, token_ids, positions, token_row, row_start,
+                  row_pos0, row_slot, li, single, multi, tables, lens) -> StepBatch:
+    """The descriptor of a step at the sizes of ``plan``: see :class:`PadPlan`."""
+    n_tokens, n_rows = int(token_ids.size), len(lens)
+    rows_padded = plan.n_single + plan.n_multi + 1      # at least one row without tokens
+    empty_row = rows_padded - 1
+
+    def grown(a: np.ndarray, n: int, fill: int) -> np.ndarray:
+        out = np.full(n, fill, dtype=np.int32)
+        out[:a.size] = a
+        return out
+
+    single_np = np.asarray(single, dtype=np.int32)
+    ctx_single = int(row_pos0[single_np].max()) + 1 if single else 0
+    padded_tables = []
+    for tab in tables:
+        wide = np.full((rows_padded, tab.shape[1]), -1, dtype=np.int32)
+        wide[:n_rows] = tab
+        padded_tables.append(wide)
+    dev = stager.upload([
+        grown(token_ids, plan.n_tokens, 0), grown(positions, plan.n_tokens, 0),
+        grown(token_row, plan.n_tokens, -1), grown(row_start, rows_padded + 1, n_tokens),
+        grown(row_pos0, rows_padded, 0), grown(row_slot, rows_padded, 0),
+        grown(li, plan.n_out, 0), grown(single_np, plan.n_single, empty_row),
+        grown(np.asarray(multi, dtype=np.int32), plan.n_multi, empty_row), *padded_tables])
+    return StepBatch(
+        n_tokens=plan.n_tokens, n_rows=rows_padded, n_out=plan.n_out, max_new=plan.n_tokens,
+        max_context=int((row_pos0.astype(np.int64) + np.asarray(lens, dtype=np.int64)).max()),
+        token_ids=dev[0], positions=dev[1], token_row=dev[2], row_start=dev[3],
+        row_pos0=dev[4], row_slot=dev[5], logit_index=dev[6], single_rows=dev[7],
+        multi_rows=dev[8], block_tables=dev[9:], n_single=plan.n_single, n_multi=plan.n_multi,
+        max_new_multi=plan.n_tokens if plan.n_multi else 0,
+        max_context_single=ctx_single, context_bucket=context_bucket(ctx_single),
+        host_row_new=list(lens) + [0] * (rows_padded - n_rows),
+        host_row_pos0=row_pos0.tolist() + [0] * (rows_padded - n_rows),
+        padded=True, n_real_tokens=n_tokens, n_real_out=int(li.size))

@@ -19,7 +19,7 @@ from ..config import load_config
 from ..kernels import ops
 from ..parts import BuildContext
 from ..weights import load_tensors
-from .batch import BatchStager, RowInput, StepBatch, build_batch
+from .batch import PAD_MAX_TOKENS, BatchStager, RowInput, StepBatch, build_batch
 from .model import DecoderModel, build_model
 
 DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16,
@@ -38,11 +38,23 @@ def require_cuda() -> torch.device:
 
 
 class _CapturedStep:
-    """A decode step of a fixed number of rows, captured as a CUDA graph."""
+    """A step of fixed launch shapes, captured as a CUDA graph."""
 
-    def __init__(self, graph: torch.cuda.CUDAGraph, logits: torch.Tensor, pointers: tuple) -> None:
+    def __init__(self, graph: torch.cuda.CUDAGraph, logits: torch.Tensor | None,
+                 pointers: tuple) -> None:
         self.graph, self.logits, self.pointers = graph, logits, pointers
         self.n_kernels = 0
+
+
+#: a step that wants more logits than this is not padded and captured: a captured step keeps
+#: its output [wanted, vocabulary] in 32-bit allocated
+PAD_MAX_WANTED = 64
+#: captured graphs a runner keeps; the one used longest ago goes first
+MAX_CAPTURED_STEPS = 192
+#: a decode shape is captured at its second use: every later step has it again.  A padded
+#: shape is captured once it has come this often: a capture costs as much as the launches of
+#: some ten plain steps and saves a tenth of a step each time, and many shapes come only a few times
+CAPTURE_PADDED_AFTER = 24
 
 
 class ModelRunner:
@@ -51,7 +63,10 @@ class ModelRunner:
     reference's CudaGraphDecoder (src/scratch_llm/serving/cudagraph.py:31-96) and its
     per-batch-size buckets (src/scratch_llm/serving/graph_buckets.py:94-200): the descriptor
     arrays, the block tables (at their full width) and the pools keep their addresses, the
-    kernels read contexts and pages on the device."""
+    kernels read contexts and pages on the device.  Other steps of up to PAD_MAX_TOKENS tokens
+    (portions of prompts, alone or beside decoded tokens) are padded to a few sizes
+    (engine/batch.py::pad_plan) and captured per padded shape, if every mixer and feed-forward
+    is ``pad_safe``: launched plainly, such a step costs the host more than the device."""
 
     def __init__(self, model: DecoderModel, page_size: int, n_pages: int, max_requests: int,
                  cuda_graphs: bool = True) -> None:
@@ -68,18 +83,27 @@ class ModelRunner:
         self.cuda_graphs = cuda_graphs and all(
             getattr(part, "capturable", True) for block in model.blocks
             for part in (block.mixer, block.feed_forward))
+        self.pad_small_steps = self.cuda_graphs and all(
+            getattr(part, "pad_safe", False) for block in model.blocks
+            for part in (block.mixer, block.feed_forward))
         self._table_width = self.cache.max_pages_per_request(self.max_position)
-        self._captured: dict[tuple[int, int], _CapturedStep] = {}
+        self._captured: dict[tuple, _CapturedStep] = {}
+        self._graph_pool = None     # memory shared by the captured steps (they never overlap)
         self.replayed_kernels = 0   # kernels of this package launched through graph replays
-        self._seen_sizes: set[tuple[int, int]] = set()
+        self.replayed_steps = 0
+        self._uses: dict[tuple, int] = {}   # how often an uncaptured shape has come
+        self.capture_padded_after = CAPTURE_PADDED_AFTER
+        self._capture_stream: torch.cuda.Stream | None = None
         # tokens that a sampler chose and the host has not read yet: a row may name one of them
         # as its input (RowInput.pending), so that the next step can be launched before the
         # host has seen the tokens of this one
         self.pending_tokens = torch.zeros(max(1, max_requests), dtype=torch.int32,
                                           device=self.device)
         # room for the widest decode step, so that captured addresses stay valid
-        self._stager.reserve(8 * (max_requests + 4) + 4 * max(1, len(self.cache.groups)) +
-                             max_requests * (self._table_width + 4) * max(1, len(self.cache.groups)))
+        groups = max(1, len(self.cache.groups))
+        rows = max_requests + 16   # a padded step has up to 7 + 1 + the multi rows' padding more
+        self._stager.reserve(3 * (PAD_MAX_TOKENS + 64) + 8 * (rows + 4) + 4 * groups +
+                             rows * (self._table_width + 4) * groups)
 
     # ----------------------------------------------------------------------- requests
 
@@ -94,13 +118,14 @@ class ModelRunner:
 
     # --------------------------------------------------------------------------- step
 
-    def build_batch(self, rows: Sequence[RowInput], table_width: int | None = None) -> StepBatch:
+    def build_batch(self, rows: Sequence[RowInput], table_width: int | None = None,
+                    pad: bool = False) -> StepBatch:
         for row in rows:
             if row.pending is not None and row.pending >= self.pending_tokens.numel():
                 raise ValueError(f"request {row.request_id!r}: pending token {row.pending} is "
                                  f"beyond the buffer's {self.pending_tokens.numel()} entries")
         batch = build_batch(self.cache, self._stager, rows, self.vocab_size, self.max_position,
-                            table_width=table_width)
+                            table_width=table_width, pad=pad)
         batch.pending_tokens = self.pending_tokens
         return batch
 
@@ -117,46 +142,87 @@ class ModelRunner:
                 raise OutOfPages(f"no free pages for {len(row.tokens)} more tokens of request "
                                  f"{row.request_id!r} (free per group: {self.cache.free_pages()})")
         if self.cuda_graphs and all(len(r.tokens) == 1 and len(r.want) == 1 for r in rows):
-            logits = self._decode_step(rows)
+            batch = self.build_batch(rows, table_width=self._table_width)
+            # launch shapes depend on these two alone
+            logits = self._graph_step(batch, (len(rows), batch.context_bucket), 2)
+        elif (self.pad_small_steps and sum(len(r.tokens) for r in rows) <= PAD_MAX_TOKENS
+              and sum(len(r.want) for r in rows) <= PAD_MAX_WANTED):
+            batch = self.build_batch(rows, table_width=self._table_width, pad=True)
+            logits = self._graph_step(batch, ("padded", batch.n_tokens, batch.n_single,
+                                              batch.n_multi, batch.n_out, batch.context_bucket),
+                                      self.capture_padded_after)
+            if logits is not None and batch.n_real_out != batch.n_out:
+                logits = logits[:batch.n_real_out]
         else:
             logits = self.model.forward(self.build_batch(rows), self.cache)
         for row in rows:
             self.cache.commit(row.request_id, len(row.tokens))
         return logits
 
-    def _decode_step(self, rows: Sequence[RowInput]) -> torch.Tensor:
-        """Replay (or, at a size's second use, capture) the decode step for len(rows) rows."""
-        n = len(rows)
-        batch = self.build_batch(rows, table_width=self._table_width)
+    def _graph_step(self, batch: StepBatch, key: tuple, capture_at: int) -> torch.Tensor | None:
+        """Replay the step captured for ``key`` (the launch shapes of the batch); capture it
+        at the key's use number ``capture_at``, run it plainly before."""
         pointers = (batch.token_ids.data_ptr(), batch.logit_index.data_ptr(),
                     tuple(t.data_ptr() for t in batch.block_tables))
-        key = (n, batch.context_bucket)   # launch shapes depend on these two alone
         cap = self._captured.get(key)
         if cap is not None and cap.pointers == pointers:
+            self._captured[key] = self._captured.pop(key)   # most recently used last
             cap.graph.replay()
             self.replayed_kernels += cap.n_kernels
-            return cap.logits.clone()   # the graph's own output is overwritten by the next replay
-        if key not in self._seen_sizes:   # first use of this shape: run it plainly (warms up)
-            self._seen_sizes.add(key)
+            self.replayed_steps += 1
+            # the graph's own output is overwritten by the next replay
+            return None if cap.logits is None else cap.logits.clone()
+        uses = self._uses.get(key, 0) + 1
+        if uses < capture_at:   # (the first use also warms up what the capture must not do)
+            self._uses[key] = uses
             return self.model.forward(batch, self.cache)
+        self._uses.pop(key, None)
+        cap = self._capture(batch, pointers)
+        if cap is None:
+            return self.model.forward(batch, self.cache)
+        self._captured.pop(key, None)
+        self._captured[key] = cap
+        while len(self._captured) > MAX_CAPTURED_STEPS:
+            self._captured.pop(next(iter(self._captured)))
+        cap.graph.replay()
+        self.replayed_kernels += cap.n_kernels
+        self.replayed_steps += 1
+        return None if cap.logits is None else cap.logits.clone()
+
+    def _capture(self, batch: StepBatch, pointers: tuple) -> _CapturedStep | None:
+        """Record the step into a graph on a side stream.  All graphs share one memory pool
+        (they are replayed one after the other on one stream; their outputs stay allocated).
+        Unlike ``torch.cuda.graph`` this neither collects garbage nor empties the allocator's
+        cache, which cost more than the capture itself."""
+        if self._graph_pool is None:
+            self._graph_pool = torch.cuda.graph_pool_handle()
+            self._capture_stream = torch.cuda.Stream(self.device)
         graph = torch.cuda.CUDAGraph()
         before = ops.launch_count
-        try:
-            with torch.cuda.graph(graph):
+        stream = self._capture_stream
+        stream.wait_stream(torch.cuda.current_stream())
+        failed = False
+        with torch.cuda.stream(stream):
+            graph.capture_begin(pool=self._graph_pool)
+            try:
                 logits = self.model.forward(batch, self.cache)
-        except RuntimeError:
+            except RuntimeError:
+                failed = True
+            try:
+                graph.capture_end()
+            except RuntimeError:
+                failed = True
+        torch.cuda.current_stream().wait_stream(stream)
+        if failed:
             # a part that reads device values on the host while it runs cannot be captured:
             # from here on this runner launches every step plainly
-            self.cuda_graphs = False
+            self.cuda_graphs = self.pad_small_steps = False
             self._captured.clear()
             torch.cuda.synchronize()
-            return self.model.forward(batch, self.cache)
+            return None
         cap = _CapturedStep(graph, logits, pointers)
         cap.n_kernels = ops.launch_count - before
-        self._captured[key] = cap
-        graph.replay()
-        self.replayed_kernels += cap.n_kernels
-        return logits.clone()
+        return cap
 
 
 def load_model(model_dir: str | Path, dtype: str | torch.dtype = "bfloat16",

@@ -43,6 +43,8 @@ def decode_splits(base_ctas: int, context: int, slots: int = 3 * 148) -> int:
 
 @register_mixer("gqa_attention")
 class GQAttention(Mixer):
+    pad_safe = True   # padding tokens are not stored, rows without tokens leave the kernels at once
+
     def __init__(self, hidden_size: int, n_heads: int, n_kv_heads: int, head_dim: int,
                  scale: float, window: int | None = None,
                  names: Mapping[str, str] | None = None) -> None:
@@ -86,7 +88,9 @@ class GQAttention(Mixer):
                            batch.positions)
             cos = sin = None
             interleaved = True
-        out = torch.empty((qkv.shape[0], H * hd), dtype=qkv.dtype, device=qkv.device)
+        # (padding tokens get no attention output: zeros, so that what follows stays finite)
+        out = (torch.zeros if batch.padded else torch.empty)(
+            (qkv.shape[0], H * hd), dtype=qkv.dtype, device=qkv.device)
         if (cos is not None and qkv.dtype == torch.bfloat16 and batch.n_multi == 0
                 and batch.n_single > 0 and H // G <= 16
                 and ops.attention_decode_fused_supported(hd)):

@@ -77,6 +77,12 @@ class Part:
     #: False if ``forward`` reads device values on the host (``.item()``, ``.tolist()``) or
     #: otherwise cannot be recorded into a CUDA graph; decode steps are then launched plainly
     capturable = True
+    #: True if the part takes a padded step: tokens after the last row's that belong to no row
+    #: (``token_row`` -1, id 0, position 0; their activations are never read), rows without
+    #: tokens, and counts in the batch that include them.  Small steps of any shape are then
+    #: padded to a few sizes and replayed as CUDA graphs.  Parts that work on every token by
+    #: itself are safe; the default is the careful one.
+    pad_safe = False
 
     def param_specs(self) -> dict[str, ParamSpec]:
         return {}

@@ -17,6 +17,8 @@ from .registry import register_feed_forward
 
 @register_feed_forward("swiglu")
 class SwiGLU(FeedForward):
+    pad_safe = True   # every token by itself
+
     def __init__(self, hidden_size: int, intermediate_size: int,
                  names: Mapping[str, str] | None = None) -> None:
         self.hidden_size, self.intermediate_size = hidden_size, intermediate_size

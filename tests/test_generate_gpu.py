@@ -179,3 +179,54 @@ def test_no_cpu_path():
     from scratch_llm_b200.kernels import ops
     with pytest.raises(ops.KernelError, match="no CPU path"):
         ops.embed(torch.zeros(2, dtype=torch.int32), torch.zeros(4, 8), torch.zeros(2, 8))
+
+
+@pytest.mark.parametrize("dtype, tol", [("float32", dict(rtol=2e-5, atol=5e-6)),
+                                        ("bfloat16", dict(rtol=3e-2, atol=3e-2))])
+def test_small_steps_padded_and_replayed_as_graphs(dtype, tol, model_dirs):
+    """Steps of a few tokens (portions of prompts alone and beside decoded tokens) are padded
+    to a few shapes and replayed as captured graphs.  Against a runner that launches every
+    step plainly and unpadded: the same logits, graphs were replayed, and the cache holds the
+    same keys and values (padding tokens store nothing)."""
+    from scratch_llm_b200.engine import ModelRunner, RowInput, load_model
+    model = load_model(model_dirs["B"], dtype, verbose=False)
+    page = PAGE_SIZE["B"]
+    runners = [ModelRunner(model, page, 64, 6, cuda_graphs=g) for g in (True, False)]
+    assert runners[0].pad_small_steps and not runners[1].pad_small_steps
+    runners[0].capture_padded_after = 2   # (shapes are captured later by default)
+    vocab = CONFIGS["B"]["vocab_size"]
+    g = torch.Generator().manual_seed(3)
+    toks = lambda n: torch.randint(0, vocab, (n,), generator=g).tolist()  # noqa: E731
+    for r in runners:
+        for rid in "abcd":
+            assert r.admit(rid)
+    # shapes repeat (19 and 21 tokens both pad to 32, ...), rows change places, some steps want
+    # nothing, one row wants several places
+    plan = [
+        [("a", 19, [18])], [("b", 21, [20])], [("c", 30, [0, 29])], [("d", 17, [])],
+        [("a", 1, [0]), ("b", 1, [0]), ("c", 5, [4])], [("c", 1, [0]), ("d", 7, [6]), ("a", 1, [0])],
+        [("b", 3, [2]), ("a", 1, [0]), ("d", 1, [0])], [("d", 2, [0, 1]), ("c", 2, [1])],
+        [("a", 40, []), ("b", 1, [0])], [("b", 33, []), ("c", 1, [0])], [("c", 37, [36]), ("d", 1, [0])],
+        [("a", 2, [1]), ("b", 2, [1]), ("c", 2, [1]), ("d", 2, [1])],
+        [("a", 3, [2]), ("b", 2, [1]), ("c", 4, [3]), ("d", 2, [1])],
+    ]
+    with torch.no_grad():
+        for step in plan:
+            rows = [RowInput(rid, toks(n), want) for rid, n, want in step]
+            got = [r.step(rows) for r in runners]
+            if got[1] is None:
+                assert got[0] is None
+                continue
+            assert got[0].shape == got[1].shape
+            torch.testing.assert_close(got[0].cpu(), got[1].cpu(), **tol)
+    assert runners[0].replayed_steps >= 4 and runners[1].replayed_steps == 0
+    for a, b in zip((grp.pages for grp in runners[0].cache.groups),
+                    (grp.pages for grp in runners[1].cache.groups)):
+        if dtype == "float32":
+            assert torch.equal(a.cpu(), b.cpu())
+        else:
+            torch.testing.assert_close(a.float().cpu(), b.float().cpu(), **tol)
+    for r in runners:
+        for rid in "abcd":
+            r.release(rid)
+        r.cache.check()

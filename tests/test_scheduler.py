@@ -288,3 +288,20 @@ def test_plan_ahead_decisions():
     rows = sched2.plan()
     sched2.commit_rows(rows)
     assert sched2.plan_ahead(rows) is None
+
+
+def test_padding_plan_of_small_steps():
+    """Steps of many shapes fall on few padded shapes; nothing wanted stays nothing wanted."""
+    from scratch_llm_b200.engine.batch import PAD_MAX_TOKENS, pad_plan
+    seen = set()
+    for n_tokens in range(1, PAD_MAX_TOKENS + 1):
+        for n_single, n_multi, n_out in ((0, 1, 1), (3, 1, 4), (9, 2, 0), (0, 3, n_tokens)):
+            if n_single + 2 * n_multi > n_tokens:
+                continue
+            plan = pad_plan(n_tokens, n_single, n_multi, n_out)
+            assert n_tokens <= plan.n_tokens < n_tokens + (16 if n_tokens <= 128 else 64)
+            assert n_single <= plan.n_single < n_single + 8 and plan.n_single % 8 == 0
+            assert n_multi <= plan.n_multi < 2 * max(n_multi, 1)
+            assert (plan.n_out == 0) == (n_out == 0) and n_out <= plan.n_out < max(2 * n_out, n_out + 16)
+            seen.add((plan.n_tokens, plan.n_single, plan.n_multi))
+    assert len({t for t, _, _ in seen}) == 8 + 6   # 16..128 in steps of 16, 192..512 in steps of 64
