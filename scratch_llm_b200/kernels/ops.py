@@ -248,7 +248,8 @@ def gemv_mma(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool =
     return out
 
 
-#: workspaces of the persistent small-batch product, per device: partial sums and tickets.  A
+#: workspaces of the persistent small-batch product, per device: the words through which the
+#: ranges of K exchange partial sums (zero between launches).  A
 #: workspace that has been handed to a launch is never freed (a captured CUDA graph may hold its
 #: address), so a larger one is made beside it when a wider matrix comes.
 _gemv_workspaces: dict[int, list[torch.Tensor]] = {}

@@ -142,16 +142,16 @@ def test_gemv_streams_weights_once(ops, m, n, k):
                                      (7, 9000, 2048), (4, 40000, 1024), (4, 1004, 13824),
                                      (8, 5120 * 3, 5120)])
 def test_gemv_persistent_bulk_copies(ops, m, n, k):
-    """The persistent small-batch product (weights through shared memory by bulk copies, four
-    ranges of K combined by ticket): values, launches in a row on the shared workspace, bitwise
-    independence of the number of tokens, and the fused SwiGLU."""
+    """The persistent small-batch product (weights through shared memory by bulk copies, ranges
+    of K combined through words in global memory): values, launches in a row on the shared
+    workspace, bitwise independence of the number of tokens, and the fused SwiGLU."""
     assert ops.gemv_tma_supports(m, n, k)
     assert not ops.gemv_tma_supports(9, n, k) and not ops.gemv_tma_supports(m, n, k + 8)
     x = rand(m, k, dtype=torch.bfloat16, seed=1)
     w = rand(n, k, dtype=torch.bfloat16, seed=2, scale=0.05)
     want = x.float() @ w.float().T
     for dt in (torch.float32, torch.bfloat16):
-        for _ in range(3):   # the tickets are back at zero after every launch
+        for _ in range(3):   # the words of the exchange are back at zero after every launch
             out = torch.full((m, n), float("nan"), dtype=dt, device="cuda")
             ops.gemv_tma(x.cuda(), w.cuda(), out)
             tol = dict(rtol=2e-3, atol=2e-3) if dt == torch.float32 else TOL["bfloat16"]
