@@ -101,7 +101,8 @@ class ModelRunner:
                                           device=self.device)
         # room for the widest decode step, so that captured addresses stay valid
         groups = max(1, len(self.cache.groups))
-        rows = max_requests + 16   # a padded step has up to 7 + 1 + the multi rows' padding more
+        # a padded step has up to 7 single rows, one empty row and as many multi rows more
+        rows = 2 * max_requests + 16
         self._stager.reserve(3 * (PAD_MAX_TOKENS + 64) + 8 * (rows + 4) + 4 * groups +
                              rows * (self._table_width + 4) * groups)
 
