@@ -101,7 +101,7 @@ def test_cutting_does_not_change_logits_beyond_rounding(model_dirs, expected):
 
 
 def test_long_prompt_takes_the_fused_tensor_core_path(tmp_path):
-    """A prompt of more than 768 tokens in one step runs gate/up + SwiGLU on the tcgen05 kernel
+    """A prompt of 1,000 tokens in one step runs gate/up + SwiGLU on the tcgen05 kernel
     (shorter ones use other kernels); its logits still match the plain implementation."""
     from scratch_llm_b200.config import config_from_dict
     from scratch_llm_b200.kernels import ops
