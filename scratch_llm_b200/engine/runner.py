@@ -148,10 +148,18 @@ class ModelRunner:
             logits = self._graph_step(batch, (len(rows), batch.context_bucket), 2)
         elif (self.pad_small_steps and sum(len(r.tokens) for r in rows) <= PAD_MAX_TOKENS
               and sum(len(r.want) for r in rows) <= PAD_MAX_WANTED):
-            batch = self.build_batch(rows, table_width=self._table_width, pad=True)
+            # block tables as wide as the longest row needs, rounded up to a power of two
+            # (at their full width a model with very long positions would upload megabytes)
+            pages = max(-(-(self.cache.requests[r.request_id].n_tokens + len(r.tokens))
+                          // self.cache.page_size) for r in rows)
+            width = 8
+            while width < pages:
+                width *= 2
+            width = min(width, self._table_width)
+            batch = self.build_batch(rows, table_width=width, pad=True)
             logits = self._graph_step(batch, ("padded", batch.n_tokens, batch.n_single,
-                                              batch.n_multi, batch.n_out, batch.context_bucket),
-                                      self.capture_padded_after)
+                                              batch.n_multi, batch.n_out, batch.context_bucket,
+                                              width), self.capture_padded_after)
             if logits is not None and batch.n_real_out != batch.n_out:
                 logits = logits[:batch.n_real_out]
         else:
