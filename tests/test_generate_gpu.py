@@ -230,3 +230,53 @@ def test_small_steps_padded_and_replayed_as_graphs(dtype, tol, model_dirs):
         for rid in "abcd":
             r.release(rid)
         r.cache.check()
+
+
+@pytest.mark.parametrize("dtype, slack", [("float32", 2e-5), ("bfloat16", 6e-2)])
+def test_requests_arriving_while_others_decode(dtype, slack, model_dirs):
+    """Requests arrive every other step, so that most steps mix a prompt (or a portion of one)
+    with decoded tokens; the pool is small enough that requests are set back.  With padded
+    steps captured at once and decode steps launched ahead, every token is what a runner
+    without graphs and padding gives (32-bit: the same tokens; bfloat16: each token the plain
+    model's choice up to rounding)."""
+    import random
+    from scratch_llm_b200 import LLM, Request, SamplingParams
+    rng = random.Random(4)
+    vocab = CONFIGS["B"]["vocab_size"]
+    reqs = [Request(i, [rng.randrange(vocab) for _ in range(rng.randrange(2, 60))],
+                    SamplingParams(temperature=0.0, max_tokens=rng.randrange(4, 28)))
+            for i in range(36)]
+
+    def run(graphs):
+        llm = LLM(model_dirs["B"], dtype=dtype, max_tokens=176, page_size=PAGE_SIZE["B"],
+                  max_requests=6, max_batch_tokens=48, chunk_size=32, lookahead=graphs)
+        if graphs:
+            assert llm.runner.pad_small_steps
+            llm.runner.capture_padded_after = 2
+        else:
+            llm.runner.cuda_graphs = llm.runner.pad_small_steps = False
+        out = {r.request_id: [] for r in reqs}
+        nxt = step = 0
+        while nxt < len(reqs) or llm.has_work:
+            if nxt < len(reqs) and step % 2 == 0:
+                llm.submit(reqs[nxt])
+                nxt += 1
+            if llm.has_work:
+                for rid, tok in llm.step().items():
+                    out[rid].append(tok)
+            step += 1
+        llm.runner.cache.check()
+        assert not llm.runner.cache.requests
+        return out, llm
+
+    got, llm = run(True)
+    assert llm.runner.replayed_steps > 20 and len(llm.runner._captured) > 3
+    assert llm._sched.stats.preemptions > 0
+    assert [len(got[r.request_id]) for r in reqs] == [r.params.max_tokens for r in reqs]
+    if dtype == "float32":
+        want, _ = run(False)
+        assert got == want
+    else:
+        cfg, w = plain_weights(model_dirs["B"], dtype)
+        for r in reqs[::3]:
+            assert_greedy_consistent(cfg, w, list(r.prompt_ids), got[r.request_id], slack)
