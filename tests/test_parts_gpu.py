@@ -437,3 +437,140 @@ def test_toy_routed_feed_forward_and_another_position_encoding(tmp_path):
         for (rid, pos), row in got.items():
             torch.testing.assert_close(row, want[rid][pos], rtol=1e-4, atol=2e-5,
                                        msg=lambda m: f"{way.__name__} {rid} {pos}: {m}")
+
+
+# --------------------------------------- a toy norm and a toy arrangement of a layer's parts
+
+def make_toy_parallel():
+    """Two more parts defined here: a norm that centres before it scales (mean and variance in
+    32-bit, no bias), and a block that gives ONE normed copy of the stream to mixer and
+    feed-forward side by side, x + Mixer(Norm(x)) + FeedForward(Norm(x)).  A model with such
+    a layer before a standard one, and the toy norm before the output matrix."""
+    from scratch_llm_b200.config import register_architecture, ARCHITECTURES
+    from scratch_llm_b200.config.spec import LayerSpec, ModelSpec, PartSpec, sequential_order
+    from scratch_llm_b200.parts import BLOCKS, NORMS, Norm, register_block, register_norm
+    from scratch_llm_b200.weights import ParamSpec
+
+    if "centred_norm" not in NORMS:
+        @register_norm("centred_norm")
+        class CentredNorm(Norm):
+            def __init__(self, size, eps):
+                self.size, self.eps = size, float(eps)
+
+            def param_specs(self):
+                return {"weight": ParamSpec((self.size,), "gain")}
+
+            def load(self, tensors, ctx):
+                self.weight = tensors["weight"].to(ctx.device, torch.float32)
+                self.dtype = ctx.dtype
+
+            def forward(self, resid, delta, out_rows=None):
+                if out_rows is None:
+                    if delta is not None:
+                        resid += delta.float()      # the norm owns the add into the stream
+                    x = resid
+                else:                               # the gathered final norm: stream untouched
+                    x = resid[out_rows.long()]
+                    if delta is not None:
+                        x = x + delta[out_rows.long()].float()
+                mu = x.mean(-1, keepdim=True)
+                var = ((x - mu) ** 2).mean(-1, keepdim=True)
+                return ((x - mu) * torch.rsqrt(var + self.eps) * self.weight).to(self.dtype)
+
+    if "parallel" not in BLOCKS:
+        @register_block("parallel")
+        class ParallelBlock:
+            def __init__(self, mixer, feed_forward, mixer_norm, feed_forward_norm, position):
+                self.mixer, self.feed_forward = mixer, feed_forward
+                self.norm, self.position = mixer_norm, position     # the second norm is not used
+
+            def forward(self, resid, pending, batch, cache, write):
+                h = self.norm.forward(resid, pending)
+                return self.mixer.forward(h, batch, cache, write, self.position) + \
+                    self.feed_forward.forward(h)
+
+    if "ToyParallelForCausalLM" not in ARCHITECTURES:
+        @dataclass(frozen=True)
+        class ToyParallelConfig:
+            width: int
+            n_vocab: int
+            architecture = "ToyParallelForCausalLM"
+
+            @classmethod
+            def from_dict(cls, raw):
+                return cls(raw["width"], raw["n_vocab"])
+
+            def to_dict(self):
+                return {"architectures": [self.architecture], "width": self.width,
+                        "n_vocab": self.n_vocab}
+
+            def model_spec(self):
+                d = self.width
+                rms = PartSpec("rmsnorm", {"size": d, "eps": 1e-5})
+                centred = PartSpec("centred_norm", {"size": d, "eps": 1e-4})
+                att = PartSpec("gqa_attention", {"hidden_size": d, "n_heads": 4, "n_kv_heads": 2,
+                                                 "head_dim": 16, "scale": 0.25, "window": None})
+                ff = PartSpec("swiglu", {"hidden_size": d, "intermediate_size": 56})
+                rope = PartSpec("rotary", {"head_dim": 16, "theta": 1000.0, "max_position": 128})
+                names = {"mixer": "mixer", "feed_forward": "ff", "mixer_norm": "n1",
+                         "feed_forward_norm": "n2"}
+                layers = (LayerSpec("l0", "parallel", att, ff, centred, centred, rope, names),
+                          LayerSpec("l1", "pre_norm", att, ff, rms, rms, rope, names))
+                return ModelSpec(d, self.n_vocab, 128, layers, sequential_order(2), centred,
+                                 "emb.weight", "out_norm", "head.weight", tie_embeddings=False)
+
+        register_architecture("ToyParallelForCausalLM", ToyParallelConfig)
+    return ARCHITECTURES["ToyParallelForCausalLM"].config_cls
+
+
+def toy_parallel_plain(cfg, w, ids):
+    d, hd, H, G = cfg.width, 16, 4, 2
+    x = w["emb.weight"][torch.tensor(ids)]
+    pos = torch.arange(len(ids))
+    cos, sin = P.rope_tables(hd, 128, 1000.0)
+    acfg = dict(num_attention_heads=H, num_key_value_heads=G, head_dim=hd, hidden_size=d)
+
+    def centred(x, weight, eps=1e-4):
+        mu = x.mean(-1, keepdim=True)
+        return (x - mu) * torch.rsqrt(((x - mu) ** 2).mean(-1, keepdim=True) + eps) * weight
+
+    h = centred(x, w["l0.n1.weight"])
+    a, _ = P.attention_layer(h, pos, w, "l0.mixer", acfg, cos, sin)
+    x = x + a + P.swiglu(h, w["l0.ff.gate_proj.weight"], w["l0.ff.up_proj.weight"],
+                         w["l0.ff.down_proj.weight"])
+    a, _ = P.attention_layer(P.rmsnorm(x, w["l1.n1.weight"], 1e-5), pos, w, "l1.mixer", acfg, cos, sin)
+    x = x + a
+    x = x + P.swiglu(P.rmsnorm(x, w["l1.n2.weight"], 1e-5), w["l1.ff.gate_proj.weight"],
+                     w["l1.ff.up_proj.weight"], w["l1.ff.down_proj.weight"])
+    return centred(x, w["out_norm.weight"]) @ w["head.weight"].T
+
+
+@pytest.mark.parametrize("dtype, tol", [("float32", dict(rtol=1e-4, atol=2e-5)),
+                                        ("bfloat16", dict(rtol=3e-2, atol=3e-2))])
+def test_toy_norm_and_another_arrangement_of_a_layer(dtype, tol, tmp_path):
+    """A norm and a block arrangement are registered from here, built by the framework from a
+    configuration and stepped in every way of cutting (with captured decode steps and, the
+    parts being the framework's own attention and feed-forward, padded small steps) without a
+    change to the framework's files."""
+    import trace_util as T
+    from scratch_llm_b200.engine import ModelRunner, load_model
+    from scratch_llm_b200.weights import write_random_model
+    Toy = make_toy_parallel()
+    cfg = Toy(width=40, n_vocab=90)
+    d = write_random_model(cfg, tmp_path / "toy_parallel", seed=9, std=0.15, dtype="float32")
+    _, w = P.read_model_dir(d)
+    if dtype == "bfloat16":
+        w = {k: (v if k.endswith(("n1.weight", "n2.weight", "out_norm.weight"))
+                 else v.to(torch.bfloat16).float()) for k, v in w.items()}
+    model = load_model(d, dtype, verbose=False)
+    reqs = T.make_requests(90, [33, 6, 64, 21, 10], seed=5)
+    want = {rid: toy_parallel_plain(cfg, w, toks) for rid, toks in reqs.items()}
+    for way in (T.whole, T.tail_one_by_one, T.changing_portions, T.mixed):
+        steps = way(reqs)
+        runner = ModelRunner(model, 8, -(-T.peak_tokens(steps) // 8), 4)
+        runner.capture_padded_after = 2
+        with torch.no_grad():
+            got = T.run_in_process(runner, steps)
+        for (rid, pos), row in got.items():
+            torch.testing.assert_close(row, want[rid][pos], **tol,
+                                       msg=lambda m: f"{way.__name__} {rid} {pos}: {m}")
