@@ -203,8 +203,10 @@ class ModelRunner:
         (they are replayed one after the other on one stream; their outputs stay allocated).
         Unlike ``torch.cuda.graph`` this neither collects garbage nor empties the allocator's
         cache, which cost more than the capture itself."""
-        if self._graph_pool is None:
+        if self._graph_pool is None or not self._captured:
+            # (a pool lives as long as a graph uses it: with none left, a new one is needed)
             self._graph_pool = torch.cuda.graph_pool_handle()
+        if self._capture_stream is None:
             self._capture_stream = torch.cuda.Stream(self.device)
         graph = torch.cuda.CUDAGraph()
         before = ops.launch_count
