@@ -220,6 +220,15 @@ def test_small_steps_padded_and_replayed_as_graphs(dtype, tol, model_dirs):
             assert got[0].shape == got[1].shape
             torch.testing.assert_close(got[0].cpu(), got[1].cpu(), **tol)
     assert runners[0].replayed_steps >= 4 and runners[1].replayed_steps == 0
+    # with every captured step dropped (as after a failed capture) capturing starts afresh
+    runners[0]._captured.clear()
+    before = runners[0].replayed_steps
+    with torch.no_grad():
+        for _ in range(3):
+            rows = [RowInput(rid, toks(2), [1]) for rid in "abcd"]
+            got = [r.step(rows) for r in runners]
+            torch.testing.assert_close(got[0].cpu(), got[1].cpu(), **tol)
+    assert runners[0].replayed_steps > before
     for a, b in zip((grp.pages for grp in runners[0].cache.groups),
                     (grp.pages for grp in runners[1].cache.groups)):
         if dtype == "float32":
