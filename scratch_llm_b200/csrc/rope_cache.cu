@@ -85,6 +85,11 @@ __device__ __forceinline__ void rotate8(const uint4& a, const uint4& b, const fl
     }
 }
 
+constexpr int ROPE_HEAD_GROUPS = 4;   // threads that share a token's heads between them
+
+// A thread takes one 8-element unit (adjacent pairing) or one pair of units (split pairing) of
+// a token and walks a quarter of the token's heads with it: the angles are fetched once and
+// serve every head.
 __global__ void rope_kv_write_vec_kernel(__nv_bfloat16* __restrict__ qkv,
                                          const int* __restrict__ positions,
                                          const int* __restrict__ token_row,
@@ -93,68 +98,78 @@ __global__ void rope_kv_write_vec_kernel(__nv_bfloat16* __restrict__ qkv,
                                          __nv_bfloat16* __restrict__ pages,
                                          const int* __restrict__ block_table, int table_stride,
                                          int page_size, int H, int G, int hd, int rotate,
-                                         int interleaved, int write, int64_t n_units) {
+                                         int interleaved, int write, int64_t n_items) {
     pdl_wait();
     pdl_trigger();
     typedef __nv_bfloat16 bf16;
     const int half = hd >> 1;
     const int per_head = interleaved ? hd / 8 : hd / 16;   // units of a head
     const int n_heads = write ? H + 2 * G : H;
-    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n_units;
+    const int heads_per_group = (n_heads + ROPE_HEAD_GROUPS - 1) / ROPE_HEAD_GROUPS;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n_items;
          i += (int64_t)gridDim.x * blockDim.x) {
         const int u = (int)(i % per_head);
-        const int64_t th = i / per_head;
-        const int head = (int)(th % n_heads);
-        const int64_t n = th / n_heads;
-        if (token_row[n] < 0) continue;   // a padding token: it belongs to no row
+        const int64_t t = i / per_head;
+        const int group = (int)(t % ROPE_HEAD_GROUPS);
+        const int64_t n = t / ROPE_HEAD_GROUPS;
+        const int row = token_row[n];
+        if (row < 0) continue;   // a padding token: it belongs to no row
         const int pos = positions[n];
-        bf16* h = qkv + n * (int64_t)(H + 2 * G) * hd + (int64_t)head * hd;
-        // first and second group of 8 elements this thread owns, and its pairs' table offset
+        // first and second group of 8 elements this thread owns in every head
         const int e0 = 8 * u, e1 = half + 8 * u;   // (e1 only with the split pairing)
-        uint4 a = *reinterpret_cast<const uint4*>(h + e0), b;
-        if (!interleaved) b = *reinterpret_cast<const uint4*>(h + e1);
-        const bool is_v = head >= H + G;
-        if (rotate && !is_v) {
-            if (interleaved) {
-                // 4 adjacent pairs inside one group of 8
-                const float4 c4 = *reinterpret_cast<const float4*>(cos_t + (int64_t)pos * half + 4 * u);
-                const float4 s4 = *reinterpret_cast<const float4*>(sin_t + (int64_t)pos * half + 4 * u);
-                const float c[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
-                bf16* x = reinterpret_cast<bf16*>(&a);
-#pragma unroll
-                for (int p = 0; p < 4; ++p) {
-                    const float x0 = __bfloat162float(x[2 * p]), x1 = __bfloat162float(x[2 * p + 1]);
-                    x[2 * p] = __float2bfloat16_rn(x0 * c[p] - x1 * sn[p]);
-                    x[2 * p + 1] = __float2bfloat16_rn(x0 * sn[p] + x1 * c[p]);
-                }
-            } else {
-                float c[8], sn[8];
-                const float* cp = cos_t + (int64_t)pos * half + 8 * u;
-                const float* sp = sin_t + (int64_t)pos * half + 8 * u;
-                *reinterpret_cast<float4*>(c) = *reinterpret_cast<const float4*>(cp);
+        float c[8], sn[8];
+        if (rotate) {
+            const float* cp = cos_t + (int64_t)pos * half + (interleaved ? 4 * u : 8 * u);
+            const float* sp = sin_t + (int64_t)pos * half + (interleaved ? 4 * u : 8 * u);
+            *reinterpret_cast<float4*>(c) = *reinterpret_cast<const float4*>(cp);
+            *reinterpret_cast<float4*>(sn) = *reinterpret_cast<const float4*>(sp);
+            if (!interleaved) {
                 *reinterpret_cast<float4*>(c + 4) = *reinterpret_cast<const float4*>(cp + 4);
-                *reinterpret_cast<float4*>(sn) = *reinterpret_cast<const float4*>(sp);
                 *reinterpret_cast<float4*>(sn + 4) = *reinterpret_cast<const float4*>(sp + 4);
-                uint4 ra, rb;
-                rotate8(a, b, c, sn, ra, rb);
-                a = ra;
-                b = rb;
             }
         }
-        if (head < H) {
-            if (rotate) {
-                *reinterpret_cast<uint4*>(h + e0) = a;
-                if (!interleaved) *reinterpret_cast<uint4*>(h + e1) = b;
-            }
-            continue;
+        int64_t page_base = 0;
+        if (write) {
+            const int page = block_table[(int64_t)row * table_stride + pos / page_size];
+            page_base = (int64_t)page * 2 * G * page_size * hd + (int64_t)(pos % page_size) * hd;
         }
-        const int page = block_table[(int64_t)token_row[n] * table_stride + pos / page_size];
-        const int off = pos % page_size;
-        const int g = head - H - (is_v ? G : 0);
-        bf16* dst = pages + (((int64_t)page * 2 + (is_v ? 1 : 0)) * G + g) * page_size * hd +
-                    (int64_t)off * hd;
-        *reinterpret_cast<uint4*>(dst + e0) = a;
-        if (!interleaved) *reinterpret_cast<uint4*>(dst + e1) = b;
+        bf16* tok = qkv + n * (int64_t)(H + 2 * G) * hd;
+        const int head_end = min(n_heads, (group + 1) * heads_per_group);
+#pragma unroll 4
+        for (int head = group * heads_per_group; head < head_end; ++head) {
+            bf16* h = tok + (int64_t)head * hd;
+            uint4 a = *reinterpret_cast<const uint4*>(h + e0), b;
+            if (!interleaved) b = *reinterpret_cast<const uint4*>(h + e1);
+            const bool is_v = head >= H + G;
+            if (rotate && !is_v) {
+                if (interleaved) {
+                    // 4 adjacent pairs inside one group of 8
+                    bf16* x = reinterpret_cast<bf16*>(&a);
+#pragma unroll
+                    for (int p = 0; p < 4; ++p) {
+                        const float x0 = __bfloat162float(x[2 * p]), x1 = __bfloat162float(x[2 * p + 1]);
+                        x[2 * p] = __float2bfloat16_rn(x0 * c[p] - x1 * sn[p]);
+                        x[2 * p + 1] = __float2bfloat16_rn(x0 * sn[p] + x1 * c[p]);
+                    }
+                } else {
+                    uint4 ra, rb;
+                    rotate8(a, b, c, sn, ra, rb);
+                    a = ra;
+                    b = rb;
+                }
+            }
+            if (head < H) {
+                if (rotate) {
+                    *reinterpret_cast<uint4*>(h + e0) = a;
+                    if (!interleaved) *reinterpret_cast<uint4*>(h + e1) = b;
+                }
+                continue;
+            }
+            const int g = head - H - (is_v ? G : 0);
+            bf16* dst = pages + page_base + ((int64_t)(is_v ? G : 0) + g) * page_size * hd;
+            *reinterpret_cast<uint4*>(dst + e0) = a;
+            if (!interleaved) *reinterpret_cast<uint4*>(dst + e1) = b;
+        }
     }
 }
 
@@ -183,7 +198,7 @@ SLLM_EXPORT int sllm_rope_kv_write(void* qkv, const int* positions, const int* t
                                     interleaved, write, heads_per_block);
     if (dtype == 1 && hd % 16 == 0 && !((uintptr_t)qkv & 15) && !((uintptr_t)pages & 15) &&
         (!rotate || (!((uintptr_t)cos_t & 15) && !((uintptr_t)sin_t & 15)))) {
-        const int64_t n_units = (int64_t)n_tokens * n_heads * (interleaved ? hd / 8 : hd / 16);
+        const int64_t n_units = (int64_t)n_tokens * ROPE_HEAD_GROUPS * (interleaved ? hd / 8 : hd / 16);
         int64_t blocks = (n_units + 255) / 256;
         if (blocks > 148 * 16) blocks = 148 * 16;
         return (int)sllm_launch_pdl(rope_kv_write_vec_kernel, dim3((unsigned)blocks), dim3(256), 0,
