@@ -574,3 +574,111 @@ def test_toy_norm_and_another_arrangement_of_a_layer(dtype, tol, tmp_path):
         for (rid, pos), row in got.items():
             torch.testing.assert_close(row, want[rid][pos], **tol,
                                        msg=lambda m: f"{way.__name__} {rid} {pos}: {m}")
+
+
+# ------------------------------ layers with different needs of the cache: a window and all keys
+
+def make_toy_windowed():
+    """An architecture of the framework's own parts whose first and third layer attend to the
+    last 12 keys only while the second attends to all of them: two groups of cache entries with
+    pages of their own, and pages of the windowed group go back while a request is live."""
+    from scratch_llm_b200.config import register_architecture, ARCHITECTURES
+    from scratch_llm_b200.config.spec import LayerSpec, ModelSpec, PartSpec, sequential_order
+
+    if "ToyWindowedForCausalLM" not in ARCHITECTURES:
+        @dataclass(frozen=True)
+        class ToyWindowedConfig:
+            width: int
+            n_vocab: int
+            window: int
+            architecture = "ToyWindowedForCausalLM"
+
+            @classmethod
+            def from_dict(cls, raw):
+                return cls(raw["width"], raw["n_vocab"], raw["window"])
+
+            def to_dict(self):
+                return {"architectures": [self.architecture], "width": self.width,
+                        "n_vocab": self.n_vocab, "window": self.window}
+
+            def model_spec(self):
+                d = self.width
+                norm = PartSpec("rmsnorm", {"size": d, "eps": 1e-5})
+                att = lambda window: PartSpec("gqa_attention", {  # noqa: E731
+                    "hidden_size": d, "n_heads": 4, "n_kv_heads": 2, "head_dim": 16, "scale": 0.25,
+                    "window": window})
+                ff = PartSpec("swiglu", {"hidden_size": d, "intermediate_size": 72})
+                rope = PartSpec("rotary", {"head_dim": 16, "theta": 1000.0, "max_position": 256})
+                names = {"mixer": "mixer", "feed_forward": "ff", "mixer_norm": "n1",
+                         "feed_forward_norm": "n2"}
+                layers = tuple(LayerSpec(f"l{i}", "pre_norm", att(w), ff, norm, norm, rope, names)
+                               for i, w in enumerate((self.window, None, self.window)))
+                return ModelSpec(d, self.n_vocab, 256, layers, sequential_order(3), norm,
+                                 "emb.weight", "out_norm", "head.weight", tie_embeddings=True)
+
+        register_architecture("ToyWindowedForCausalLM", ToyWindowedConfig)
+    return ARCHITECTURES["ToyWindowedForCausalLM"].config_cls
+
+
+def toy_windowed_plain(cfg, w, ids):
+    d, hd = cfg.width, 16
+    x = w["emb.weight"][torch.tensor(ids)]
+    pos = torch.arange(len(ids))
+    cos, sin = P.rope_tables(hd, 256, 1000.0)
+    for i, window in enumerate((cfg.window, None, cfg.window)):
+        acfg = dict(num_attention_heads=4, num_key_value_heads=2, head_dim=hd, hidden_size=d,
+                    sliding_window=window)
+        a, _ = P.attention_layer(P.rmsnorm(x, w[f"l{i}.n1.weight"], 1e-5), pos, w, f"l{i}.mixer",
+                                 acfg, cos, sin)
+        x = x + a
+        x = x + P.swiglu(P.rmsnorm(x, w[f"l{i}.n2.weight"], 1e-5), w[f"l{i}.ff.gate_proj.weight"],
+                         w[f"l{i}.ff.up_proj.weight"], w[f"l{i}.ff.down_proj.weight"])
+    return P.rmsnorm(x, w["out_norm.weight"], 1e-5) @ w["emb.weight"].T
+
+
+@pytest.mark.parametrize("dtype, tol", [("float32", dict(rtol=1e-4, atol=2e-5)),
+                                        ("bfloat16", dict(rtol=3e-2, atol=3e-2))])
+def test_windowed_and_full_layers_share_a_model(dtype, tol, tmp_path):
+    """Two groups of cache entries in one model (a window of 12 keys; all keys): every way of
+    cutting gives the plain logits, the windowed group needs far fewer pages than the other,
+    and its pages go back while requests are live."""
+    import trace_util as T
+    from scratch_llm_b200.engine import ModelRunner, load_model
+    from scratch_llm_b200.weights import write_random_model
+    Toy = make_toy_windowed()
+    cfg = Toy(width=48, n_vocab=80, window=12)
+    d = write_random_model(cfg, tmp_path / "toy_windowed", seed=12, std=0.08, dtype="float32")
+    _, w = P.read_model_dir(d)
+    if dtype == "bfloat16":
+        w = {k: (v if k.endswith(("n1.weight", "n2.weight", "out_norm.weight"))
+                 else v.to(torch.bfloat16).float()) for k, v in w.items()}
+    model = load_model(d, dtype, verbose=False)
+    kv, _ = model.cache_specs()
+    assert [s.window for s in kv] == [12, None, 12]
+    reqs = T.make_requests(80, [40, 7, 100, 13, 64, 90], seed=8)
+    want = {rid: toy_windowed_plain(cfg, w, toks) for rid, toks in reqs.items()}
+    # the window's edge matters: with a window one key wider the logits move by far more
+    # than the 32-bit tolerance (the 32-bit run is the one that would show such a fault)
+    wider = toy_windowed_plain(Toy(width=48, n_vocab=80, window=13), w, reqs[list(reqs)[2]])
+    assert float((wider - want[list(reqs)[2]]).abs().max()) > 20 * 2e-5
+    for way in (T.whole, T.tail_one_by_one, T.changing_portions, T.mixed):
+        steps = way(reqs)
+        runner = ModelRunner(model, 8, -(-T.peak_tokens(steps) // 8), 4)
+        runner.capture_padded_after = 2
+        assert len(runner.cache.groups) == 2
+        low = [g.pool.n_pages for g in runner.cache.groups]
+
+        def watch():
+            for i, g in enumerate(runner.cache.groups):
+                low[i] = min(low[i], g.pool.n_free)
+
+        with torch.no_grad():
+            got = T.run_in_process(runner, steps, after_step=watch)
+        used = [g.pool.n_pages - a for g, a in zip(runner.cache.groups, low)]
+        windowed = [i for i, g in enumerate(runner.cache.groups) if g.spec.window][0]
+        assert used[windowed] < used[1 - windowed]       # pages behind the window went back
+        for (rid, pos), row in got.items():
+            torch.testing.assert_close(row, want[rid][pos], **tol,
+                                       msg=lambda m: f"{way.__name__} {rid} {pos}: {m}")
+        assert not runner.cache.requests and all(
+            g.pool.n_free == g.pool.n_pages for g in runner.cache.groups)

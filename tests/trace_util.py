@@ -95,8 +95,9 @@ def peak_tokens(steps, round_to=64):
     return peak
 
 
-def run_in_process(runner, steps):
-    """{(request, position): logits row} of a trace through ModelRunner.step."""
+def run_in_process(runner, steps, after_step=None):
+    """{(request, position): logits row} of a trace through ModelRunner.step.  ``after_step``
+    is called after every step, before the step's finished requests are released."""
     from scratch_llm_b200.engine import RowInput
 
     out, fed = {}, {}
@@ -114,6 +115,8 @@ def run_in_process(runner, steps):
                 out[(e["id"], fed[e["id"]] + w)] = logits[k].float().cpu()
                 k += 1
             fed[e["id"]] += len(e["tokens"])
+        if after_step is not None:
+            after_step()
         for rid in s["end"]:
             runner.release(rid)
         runner.cache.check()
