@@ -12,9 +12,9 @@ kernels/   bindings of the CUDA sources in csrc/
 
 __version__ = "0.1.0"
 
-from .engine import (LLM, Request, ServeResult, generate, generate_with_logprobs,  # noqa: E402
-                     serve_continuous)
+from .engine import (LLM, Request, ServeResult, batched_greedy_decode, generate,  # noqa: E402
+                     generate_with_logprobs, serve_continuous)
 from .sampling import SamplingParams  # noqa: E402
 
-__all__ = ["LLM", "Request", "SamplingParams", "ServeResult", "generate",
-           "generate_with_logprobs", "serve_continuous"]
+__all__ = ["LLM", "Request", "SamplingParams", "ServeResult", "batched_greedy_decode",
+           "generate", "generate_with_logprobs", "serve_continuous"]

@@ -227,3 +227,15 @@ def generate_with_logprobs(llm: LLM, prompt_ids: Sequence[int], params: Sampling
 
 def serve_continuous(llm: LLM, requests: Sequence[Request]) -> ServeResult:
     return llm.serve(requests)
+
+
+def batched_greedy_decode(llm: LLM, prompts: Sequence[Sequence[int]], max_tokens: int
+                          ) -> list[list[int]]:
+    """The reference's static batched decode (src/scratch_llm/serving/batched.py:26-58) with the
+    engine in the model's place: the generated ids of every prompt, greedy, exactly
+    ``max_tokens`` each (no stop ids).  The reference needs prompts of one length, because its
+    rows share their positions; here every row has its own, so any lengths are taken."""
+    if len(prompts) == 0:
+        raise ValueError("prompts must be non-empty")
+    return llm.generate([list(p) for p in prompts],
+                        SamplingParams(temperature=0.0, max_tokens=max_tokens))

@@ -48,6 +48,10 @@ def test_greedy_generation_matches_plain(name, dtype, slack, model_dirs):
         assert_greedy_consistent(cfg, w, p, g, slack)
     if dtype == "float32":
         assert got[0] == P.greedy(cfg, w, prompts[0], n_new)
+    # the reference's name for a greedy batch gives the same
+    from scratch_llm_b200 import batched_greedy_decode
+    if dtype == "float32":
+        assert batched_greedy_decode(llm, prompts, n_new) == got
     # one prompt alone gives what it gave in the batch
     alone = llm.generate(prompts[1], SamplingParams(temperature=0.0, max_tokens=n_new))
     if dtype == "float32":
