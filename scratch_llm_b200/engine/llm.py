@@ -36,6 +36,10 @@ class Completed:
     finish_reason: str
     admitted_at_step: int
     n_preempted: int
+    #: when the request arrived and when the host had each of its tokens, on ``serve``'s clock
+    #: (the reference's RequestRecord: start_s, token_times_s)
+    start_s: float = 0.0
+    token_times_s: tuple[float, ...] = ()
 
 
 @dataclass(frozen=True)
@@ -159,17 +163,40 @@ class LLM:
 
     # ------------------------------------------------------------------------------ serve
 
-    def serve(self, requests: Sequence[Request], want_logprobs: bool = False) -> ServeResult:
-        """Run ``requests`` to completion under continuous batching."""
+    def serve(self, requests: Sequence[Request], want_logprobs: bool = False, *,
+              arrivals_s: Sequence[float] | None = None, clock=time.perf_counter,
+              sleep=time.sleep) -> ServeResult:
+        """Run ``requests`` to completion under continuous batching.  ``arrivals_s`` (one
+        offset in seconds per request, from the start of the call) turns the closed list into a
+        stream: a request is queued once ``clock`` has passed its offset, and ``sleep`` is the
+        idle wait while nothing is live (both can be replaced, for a test's own clock), as in the
+        reference's ``serve`` (src/scratch_llm/serving/continuous.py:98-121, 268-274)."""
         if self.has_work:
             raise RuntimeError("serve() needs an idle engine: requests from submit() are live")
+        n = len(requests)
+        if arrivals_s is not None:
+            if len(arrivals_s) != n:
+                raise ValueError("arrivals_s must carry one offset per request")
+            if any(a < 0 for a in arrivals_s):
+                raise ValueError("arrivals_s offsets must be >= 0 (they are offsets from the start)")
+        arrival = [float(a) for a in arrivals_s] if arrivals_s is not None else [0.0] * n
+        waiting = sorted(range(n), key=lambda i: (arrival[i], i))
+        waiting.reverse()   # the next arrival last, to pop it
+        times: dict[Hashable, list[float]] = {r.request_id: [] for r in requests}
         self._sched = None
         start = time.perf_counter()
+        t0 = clock()
         try:
-            for r in requests:
-                self.submit(r)
-            while self.has_work:
-                self.step(want_logprobs)
+            while waiting or self.has_work:
+                while waiting and clock() - t0 >= arrival[waiting[-1]]:
+                    self.submit(requests[waiting.pop()])
+                if not self.has_work:
+                    sleep(max(0.0, t0 + arrival[waiting[-1]] - clock()))
+                    continue
+                produced = self.step(want_logprobs)
+                now = clock()
+                for rid in produced:
+                    times[rid].append(now)
             sched = self._sched
             self._in_flight = None   # rows planned ahead for requests that have all ended
             ops.check_kernel_errors()
@@ -179,11 +206,14 @@ class LLM:
         self._sched = None
         wall = time.perf_counter() - start
         done = []
-        for r in requests:
+        for i, r in enumerate(requests):
             seq: Sequence_ = sched.finished[r.request_id]
             done.append(Completed(r, tuple(seq.generated),
                                   tuple(seq.logprobs) if want_logprobs else None,
-                                  seq.finish_reason or "", seq.admitted_at_step, seq.n_preempted))
+                                  seq.finish_reason or "", seq.admitted_at_step, seq.n_preempted,
+                                  t0 + arrival[i], tuple(times[r.request_id])))
+        if sched is None:
+            sched = self._scheduler()
         return ServeResult(tuple(done), sched.stats, wall)
 
     # --------------------------------------------------------------------------- generate
@@ -225,8 +255,10 @@ def generate_with_logprobs(llm: LLM, prompt_ids: Sequence[int], params: Sampling
     return llm.generate_with_logprobs(list(prompt_ids), params)
 
 
-def serve_continuous(llm: LLM, requests: Sequence[Request]) -> ServeResult:
-    return llm.serve(requests)
+def serve_continuous(llm: LLM, requests: Sequence[Request], *,
+                     arrivals_s: Sequence[float] | None = None, clock=time.perf_counter,
+                     sleep=time.sleep) -> ServeResult:
+    return llm.serve(requests, arrivals_s=arrivals_s, clock=clock, sleep=sleep)
 
 
 def batched_greedy_decode(llm: LLM, prompts: Sequence[Sequence[int]], max_tokens: int

@@ -293,3 +293,45 @@ def test_requests_arriving_while_others_decode(dtype, slack, model_dirs):
         cfg, w = plain_weights(model_dirs["B"], dtype)
         for r in reqs[::3]:
             assert_greedy_consistent(cfg, w, list(r.prompt_ids), got[r.request_id], slack)
+
+
+def test_serve_with_arrivals_on_a_test_clock(model_dirs):
+    """``arrivals_s`` turns the request list into a stream (the reference's serve_continuous
+    option): on a clock of the test's own, requests are queued when their time has come, the
+    engine sleeps while nothing is live, every token has its time, and the tokens are those
+    of the closed list."""
+    from scratch_llm_b200 import LLM, Request, SamplingParams, serve_continuous
+    prompts = prompts_for(256, [12, 30, 7, 21, 16])
+    reqs = [Request(i, p, SamplingParams(temperature=0.0, max_tokens=6 + i))
+            for i, p in enumerate(prompts)]
+    llm = LLM(model_dirs["A"], dtype="float32", max_tokens=1024, page_size=16)
+    want = llm.serve(reqs)
+    now = [100.0]
+    slept = []
+
+    def clock():
+        now[0] += 0.001           # every look at the clock costs a millisecond
+        return now[0]
+
+    def sleep(seconds):
+        slept.append(seconds)
+        now[0] += seconds
+
+    arrivals = [0.0, 0.5, 0.5, 3.0, 0.2]
+    got = serve_continuous(llm, reqs, arrivals_s=arrivals, clock=clock, sleep=sleep)
+    assert [c.token_ids for c in got.completed] == [c.token_ids for c in want.completed]
+    assert slept and all(s >= 0 for s in slept)     # request 3 comes after the others are done
+    by_id = {c.request.request_id: c for c in got.completed}
+    for i, c in by_id.items():
+        assert len(c.token_times_s) == len(c.token_ids)
+        assert list(c.token_times_s) == sorted(c.token_times_s)
+        assert c.token_times_s[0] > c.start_s                  # no token before its arrival
+        assert abs(c.start_s - (got.completed[0].start_s + arrivals[i])) < 1e-9
+    # admission follows arrival: 0, then 4, then 1 and 2, then 3
+    steps = [by_id[i].admitted_at_step for i in (0, 4, 1, 2, 3)]
+    assert steps == sorted(steps) and steps[0] < steps[1] < steps[2] and steps[3] < steps[4]
+    with pytest.raises(ValueError, match="one offset per request"):
+        llm.serve(reqs, arrivals_s=[0.0])
+    with pytest.raises(ValueError, match=">= 0"):
+        llm.serve(reqs, arrivals_s=[0.0, 1.0, -1.0, 0.0, 0.0])
+    assert not llm.has_work
