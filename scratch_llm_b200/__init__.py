@@ -13,8 +13,8 @@ kernels/   bindings of the CUDA sources in csrc/
 __version__ = "0.1.0"
 
 from .engine import (LLM, Request, ServeResult, batched_greedy_decode, generate,  # noqa: E402
-                     generate_with_logprobs, serve_continuous)
+                     generate_with_logprobs, serve_continuous, serve_static_wave)
 from .sampling import SamplingParams  # noqa: E402
 
 __all__ = ["LLM", "Request", "SamplingParams", "ServeResult", "batched_greedy_decode",
-           "generate", "generate_with_logprobs", "serve_continuous"]
+           "generate", "generate_with_logprobs", "serve_continuous", "serve_static_wave"]

@@ -3,11 +3,11 @@
 from .batch import RowInput, StepBatch
 from .model import DecoderModel, build_model
 from .llm import (LLM, Completed, ServeResult, batched_greedy_decode, generate,
-                  generate_with_logprobs, serve_continuous)
+                  generate_with_logprobs, serve_continuous, serve_static_wave)
 from .runner import DTYPES, ModelRunner, OutOfPages, load_model
 from .scheduler import Request, Scheduler
 
 __all__ = ["LLM", "Completed", "Request", "Scheduler", "ServeResult", "batched_greedy_decode",
            "generate",
-           "generate_with_logprobs", "serve_continuous", "DTYPES", "DecoderModel", "ModelRunner", "OutOfPages", "RowInput", "StepBatch",
+           "generate_with_logprobs", "serve_continuous", "serve_static_wave", "DTYPES", "DecoderModel", "ModelRunner", "OutOfPages", "RowInput", "StepBatch",
            "build_model", "load_model"]

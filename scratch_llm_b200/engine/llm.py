@@ -94,9 +94,9 @@ class LLM:
         self.lookahead = lookahead
         self._in_flight: _InFlight | None = None
 
-    def _scheduler(self) -> Scheduler:
+    def _scheduler(self, policy: str = "continuous") -> Scheduler:
         return Scheduler(self.runner.cache, self.runner.max_position, self.max_batch_tokens,
-                         self.chunk_size, self.admission, self.runner.vocab_size)
+                         self.chunk_size, self.admission, self.runner.vocab_size, policy)
 
     # ------------------------------------------------------------------------------ serve
 
@@ -165,12 +165,13 @@ class LLM:
 
     def serve(self, requests: Sequence[Request], want_logprobs: bool = False, *,
               arrivals_s: Sequence[float] | None = None, clock=time.perf_counter,
-              sleep=time.sleep) -> ServeResult:
+              sleep=time.sleep, policy: str = "continuous") -> ServeResult:
         """Run ``requests`` to completion under continuous batching.  ``arrivals_s`` (one
         offset in seconds per request, from the start of the call) turns the closed list into a
         stream: a request is queued once ``clock`` has passed its offset, and ``sleep`` is the
         idle wait while nothing is live (both can be replaced, for a test's own clock), as in the
-        reference's ``serve`` (src/scratch_llm/serving/continuous.py:98-121, 268-274)."""
+        reference's ``serve`` (src/scratch_llm/serving/continuous.py:98-121, 268-274).
+        ``policy="wave"``: requests join only when no request is live (the reference's baseline)."""
         if self.has_work:
             raise RuntimeError("serve() needs an idle engine: requests from submit() are live")
         n = len(requests)
@@ -183,7 +184,7 @@ class LLM:
         waiting = sorted(range(n), key=lambda i: (arrival[i], i))
         waiting.reverse()   # the next arrival last, to pop it
         times: dict[Hashable, list[float]] = {r.request_id: [] for r in requests}
-        self._sched = None
+        self._sched = self._scheduler(policy)
         start = time.perf_counter()
         t0 = clock()
         try:
@@ -212,8 +213,6 @@ class LLM:
                                   tuple(seq.logprobs) if want_logprobs else None,
                                   seq.finish_reason or "", seq.admitted_at_step, seq.n_preempted,
                                   t0 + arrival[i], tuple(times[r.request_id])))
-        if sched is None:
-            sched = self._scheduler()
         return ServeResult(tuple(done), sched.stats, wall)
 
     # --------------------------------------------------------------------------- generate
@@ -259,6 +258,13 @@ def serve_continuous(llm: LLM, requests: Sequence[Request], *,
                      arrivals_s: Sequence[float] | None = None, clock=time.perf_counter,
                      sleep=time.sleep) -> ServeResult:
     return llm.serve(requests, arrivals_s=arrivals_s, clock=clock, sleep=sleep)
+
+
+def serve_static_wave(llm: LLM, requests: Sequence[Request], *, clock=time.perf_counter
+                      ) -> ServeResult:
+    """The reference's comparator (src/scratch_llm/serving/continuous.py:449-476): requests are
+    admitted only when no request is live, a wave runs until its longest request has ended."""
+    return llm.serve(requests, clock=clock, policy="wave")
 
 
 def batched_greedy_decode(llm: LLM, prompts: Sequence[Sequence[int]], max_tokens: int

@@ -21,6 +21,13 @@ later recomputed from its prompt plus the tokens it had generated, then goes on.
 portion that cannot get its pages is cut to what fits, or waits for a later step.  A request
 that alone could never fit the pool is refused when it is submitted.
 
+``policy="wave"`` is the reference's other policy (src/scratch_llm/serving/continuous.py:287,
+449-476: requests are admitted only into an all-free batch, and a wave runs until its longest
+request has finished), kept as the baseline that continuous batching is compared with: a wave
+opens when no request is live, takes requests while slots, budget and pages allow (over several
+steps if the token budget cuts its prompts), and closes when the slots are full or the queue is
+empty.
+
 The scheduler is host-side logic over a :class:`CacheManager`; it runs without a GPU.
 """
 
@@ -84,9 +91,13 @@ class SchedulerStats:
 class Scheduler:
     def __init__(self, cache: CacheManager, max_position: int, max_batch_tokens: int = 2048,
                  chunk_size: int | None = None, admission: str = "optimistic",
-                 vocab_size: int | None = None) -> None:
+                 vocab_size: int | None = None, policy: str = "continuous") -> None:
         if admission not in ("optimistic", "reserve_full"):
             raise ValueError("admission is 'optimistic' or 'reserve_full'")
+        if policy not in ("continuous", "wave"):
+            raise ValueError("policy is 'continuous' or 'wave'")
+        self.policy = policy
+        self._wave_open = True
         if max_batch_tokens < 1 or (chunk_size is not None and chunk_size < 1):
             raise ValueError("max_batch_tokens and chunk_size must be positive")
         self.cache, self.max_position = cache, max_position
@@ -203,6 +214,11 @@ class Scheduler:
             planned.add(id(seq))
             budget -= m
         # 3. admissions, first come first served, no skipping ahead
+        if self.policy == "wave":
+            if not self.running:
+                self._wave_open = True
+            elif not self._wave_open:
+                budget = 0          # a wave is running: nobody joins it
         while self.queue and budget >= 1 and self.cache.n_free_slots > 0:
             seq = self.queue[0]
             if self.admission == "reserve_full":
@@ -225,6 +241,9 @@ class Scheduler:
             self.running.append(seq)
             rows.append(PlannedRow(seq, 0, m, m == len(seq.tokens)))
             budget -= m
+        if self.policy == "wave" and self._wave_open and self.running and \
+                (not self.queue or self.cache.n_free_slots == 0):
+            self._wave_open = False     # full, or nobody left to take: the wave is closed
         # nothing can move although requests are live: the pool is full of half-read prompts
         if not rows and self.running:
             victim = max(self.running, key=lambda s: s.order)

@@ -330,6 +330,12 @@ def test_serve_with_arrivals_on_a_test_clock(model_dirs):
     # admission follows arrival: 0, then 4, then 1 and 2, then 3
     steps = [by_id[i].admitted_at_step for i in (0, 4, 1, 2, 3)]
     assert steps == sorted(steps) and steps[0] < steps[1] < steps[2] and steps[3] < steps[4]
+    # the reference's comparator: waves of requests, the same tokens in more steps
+    from scratch_llm_b200 import serve_static_wave
+    small = LLM(model_dirs["A"], dtype="float32", max_tokens=1024, page_size=16, max_requests=2)
+    waves = serve_static_wave(small, reqs)
+    assert [c.token_ids for c in waves.completed] == [c.token_ids for c in want.completed]
+    assert waves.stats.steps > small.serve(reqs).stats.steps
     with pytest.raises(ValueError, match="one offset per request"):
         llm.serve(reqs, arrivals_s=[0.0])
     with pytest.raises(ValueError, match=">= 0"):

@@ -305,3 +305,38 @@ def test_padding_plan_of_small_steps():
             assert (plan.n_out == 0) == (n_out == 0) and n_out <= plan.n_out < max(2 * n_out, n_out + 16)
             seen.add((plan.n_tokens, plan.n_single, plan.n_multi))
     assert len({t for t, _, _ in seen}) == 8 + 6   # 16..128 in steps of 16, 192..512 in steps of 64
+
+
+def test_wave_policy_admits_only_into_an_empty_engine():
+    """The reference's comparator: nobody joins a running wave, a wave runs until its longest
+    request has ended; a wave whose prompts the token budget cuts is admitted over several
+    steps.  The tokens are those of continuous batching."""
+    with pytest.raises(ValueError, match="policy"):
+        make(n_pages=10, policy="waves")
+    results = {}
+    for policy in ("continuous", "wave"):
+        sched, cache = make(n_pages=200, max_requests=3, max_batch_tokens=16, policy=policy)
+        for i in range(7):
+            sched.submit(Request(i, [i + 1] * (5 + i), greedy(2 + 3 * (i % 3))))
+        log = []
+        run(sched, cache, log)
+        results[policy] = {i: sched.finished[i].generated for i in range(7)}
+        first = {}
+        last = {}
+        for s, rows in enumerate(log):
+            for rid, *_ in rows:
+                first.setdefault(rid, s)
+                last[rid] = s
+        if policy == "wave":
+            waves = [(0, 1, 2), (3, 4, 5), (6,)]
+            for a, b in zip(waves, waves[1:]):
+                assert max(last[i] for i in a) < min(first[i] for i in b)
+            # prompts of 5, 6 and 7 tokens under a budget of 16: the third joins a step later
+            assert first[0] == first[1] == 0 and first[2] in (0, 1)
+            assert sched.stats.steps > results_steps
+        else:
+            results_steps = sched.stats.steps
+            assert first[3] <= max(last[i] for i in (0, 1, 2))   # a freed slot is taken at once
+    assert results["wave"] == results["continuous"]
+    assert all(results["wave"][i] == oracle([i + 1] * (5 + i), greedy(2 + 3 * (i % 3)))
+               for i in range(7))
