@@ -86,6 +86,19 @@ class SchedulerStats:
     rows_per_step: list[int] = field(default_factory=list)
     tokens_per_step: list[int] = field(default_factory=list)
     page_occupancy: list[float] = field(default_factory=list)
+    # what the held pages waste (the reference's paged_frag_mean and paged_alloc_peak_tokens,
+    # src/scratch_llm/serving/continuous.py:67-87), sampled every WASTE_EVERY steps before
+    # finished requests give their pages back
+    waste_samples: list[float] = field(default_factory=list)
+    allocated_peak_tokens: int = 0
+
+    @property
+    def waste_mean(self) -> float | None:
+        return sum(self.waste_samples) / len(self.waste_samples) if self.waste_samples else None
+
+
+#: the cache's waste is sampled every so many steps (it walks every live request's tables)
+WASTE_EVERY = 8
 
 
 class Scheduler:
@@ -306,6 +319,10 @@ class Scheduler:
         st.rows_per_step.append(len(rows))
         st.tokens_per_step.append(sum(r.n for r in rows))
         st.peak_live = max(st.peak_live, len(self.running))
+        if st.steps % WASTE_EVERY == 1:
+            waste = self.cache.waste_stats()
+            st.waste_samples.append(waste["waste"])
+            st.allocated_peak_tokens = max(st.allocated_peak_tokens, int(waste["allocated_tokens"]))
         for r in rows:
             rid = r.seq.request.request_id
             if r.seq.finish_reason:

@@ -7,7 +7,7 @@ import zlib
 import pytest
 
 from scratch_llm_b200.cache import CacheManager
-from scratch_llm_b200.engine.scheduler import Request, Scheduler
+from scratch_llm_b200.engine.scheduler import Request, Scheduler, SchedulerStats
 from scratch_llm_b200.parts import KVSpec
 from scratch_llm_b200.sampling import SamplingParams
 
@@ -79,6 +79,20 @@ def test_mixed_steps_budget_and_portions():
     assert sched.stats.preemptions == 0
     assert sched.stats.prefill_tokens == 5 + 23 + 12
     assert sched.stats.decode_tokens == (6 - 1) + (3 - 1) + (2 - 1)
+
+
+def test_stats_of_the_held_pages():
+    """What the held pages waste: sampled while requests are live, between 0 and the share a
+    request's last page can leave empty."""
+    sched, cache = make(n_pages=200, page_size=4, max_requests=4, max_batch_tokens=64)
+    for i in range(6):
+        sched.submit(Request(i, [1] * (3 + 2 * i), greedy(20)))
+    run(sched, cache)
+    st = sched.stats
+    assert st.waste_samples and all(0.0 <= w < 0.75 for w in st.waste_samples)
+    assert st.waste_mean is not None and 0.0 < st.waste_mean < 0.5
+    assert 4 <= st.allocated_peak_tokens <= 4 * (13 + 20 + 4)
+    assert SchedulerStats().waste_mean is None
 
 
 def test_first_come_first_served_and_slots():
