@@ -29,6 +29,20 @@ SIZES = dict(hidden_size=4096, num_hidden_layers=32, num_attention_heads=32,
              num_key_value_heads=8, head_dim=128, intermediate_size=14336, vocab_size=128256,
              rope_theta=500000.0, rms_norm_eps=1e-5, tie_word_embeddings=False,
              max_position_embeddings=8192, torch_dtype="bfloat16")
+# the other two configurations at full size that the baseline names; chosen with --sizes
+SIZES_BY_NAME = {
+    "llama-3-8b": SIZES,
+    "llama-3.2-1b": dict(hidden_size=2048, num_hidden_layers=16, num_attention_heads=32,
+                         num_key_value_heads=8, head_dim=64, intermediate_size=8192,
+                         vocab_size=128256, rope_theta=500000.0, rms_norm_eps=1e-5,
+                         tie_word_embeddings=True, max_position_embeddings=8192,
+                         torch_dtype="bfloat16"),
+    "llama-2-13b": dict(hidden_size=5120, num_hidden_layers=40, num_attention_heads=40,
+                        num_key_value_heads=40, head_dim=128, intermediate_size=13824,
+                        vocab_size=32000, rope_theta=10000.0, rms_norm_eps=1e-5,
+                        tie_word_embeddings=False, max_position_embeddings=4096,
+                        torch_dtype="bfloat16"),
+}
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
 
 
@@ -111,7 +125,8 @@ def reference_arm() -> int:
     return 0
 
 
-def build_engine(n_layers: int, capacity_tokens: int, max_requests: int, page_size: int):
+def build_engine(n_layers: int, capacity_tokens: int, max_requests: int, page_size: int,
+                 sizes: dict | None = None):
     import torch
 
     from scratch_llm_b200.config import config_from_dict
@@ -120,7 +135,7 @@ def build_engine(n_layers: int, capacity_tokens: int, max_requests: int, page_si
     from scratch_llm_b200.parts import BuildContext
     from scratch_llm_b200.weights.random_init import random_tensors
 
-    cfg = config_from_dict({**SIZES, "num_hidden_layers": n_layers,
+    cfg = config_from_dict({**(sizes or SIZES), "num_hidden_layers": n_layers,
                             "architectures": ["LlamaForCausalLM"]})
     model = build_model(cfg)
     ops.prepare(model.head_dims(), verbose=False)
@@ -142,10 +157,34 @@ def build_engine(n_layers: int, capacity_tokens: int, max_requests: int, page_si
 
 
 def weight_bytes(cfg) -> int:
+    """Bytes of weights a decode step reads (a tied output matrix is still read; the embedding
+    table is not: a step gathers a few rows of it)."""
     d, f, v = cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size
     hq, hk = cfg.num_attention_heads * cfg.head_size, cfg.kv_heads * cfg.head_size
     per_layer = (hq + 2 * hk) * d + d * hq + 3 * f * d
     return 2 * (cfg.num_hidden_layers * per_layer + v * d) + 4 * (2 * cfg.num_hidden_layers + 1) * d
+
+
+def time_serve(llm, cfg, n_requests: int, seed: int = 3):
+    """The baseline's continuous-batching workload: `n_requests` requests with prompt lengths
+    16-2048 and output lengths 16-512 (seeded, uniform), all queued at once, through LLM.serve
+    (host token ids in and out).  Returns (generated tok/s, prompt tokens, generated tokens,
+    seconds, steps)."""
+    import random
+
+    from scratch_llm_b200 import Request, SamplingParams
+
+    rng = random.Random(seed)
+    reqs = []
+    for i in range(n_requests):
+        n_in, n_out = rng.randint(16, 2048), rng.randint(16, 512)
+        reqs.append(Request(f"s{i}", [rng.randrange(cfg.vocab_size) for _ in range(n_in)],
+                            SamplingParams(temperature=0.0, max_tokens=n_out)))
+    llm.serve(reqs[:4])          # warm-up: compiles nothing, but pages in the kernels
+    res = llm.serve(reqs)
+    n_out = sum(len(c.token_ids) for c in res.completed)
+    n_in = sum(len(r.prompt_ids) for r in reqs)
+    return n_out / res.wall_s, n_in, n_out, res.wall_s, res.stats.steps
 
 
 def prefill_flops(cfg, t: int) -> float:
@@ -268,7 +307,14 @@ def main() -> int:
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--page-size", type=int, default=64)
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")
+    ap.add_argument("--sizes", default="llama-3-8b", choices=sorted(SIZES_BY_NAME),
+                    help="layer sizes (the default is the configuration the metric is quoted on)")
+    ap.add_argument("--serve", type=int, default=0, metavar="N",
+                    help="also run the continuous-batching workload with N requests")
     args = ap.parse_args()
+    sizes = SIZES_BY_NAME[args.sizes]
+    if args.layers == SIZES["num_hidden_layers"] and args.sizes != "llama-3-8b":
+        args.layers = sizes["num_hidden_layers"]
     if args.impl == "reference":
         return reference_arm()
     if args.gpus != 1:
@@ -282,7 +328,9 @@ def main() -> int:
     pk = peaks()
     big = max(64, args.batch)
     capacity = big * (args.context + args.warmup + args.steps + 64) + 4096
-    cfg, model, llm = build_engine(args.layers, capacity, big + 1, args.page_size)
+    if args.serve:
+        capacity = max(capacity, min(args.serve, 64) * 2600)
+    cfg, model, llm = build_engine(args.layers, capacity, big + 1, args.page_size, sizes)
 
     with torch.no_grad():
         prefill_ms = time_prefill(llm, cfg, args.prefill_tokens)
@@ -297,6 +345,12 @@ def main() -> int:
                 pms, _ = time_decode_device(llm, cfg, b, args.context, max(8, args.steps // 2),
                                             args.warmup, f"p{b}_")
                 points[f"decode_b{b}"] = round(b / pms * 1e3, 1)
+        serve = None
+        if args.serve:
+            tok_s, n_in, n_out, seconds, steps = time_serve(llm, cfg, args.serve)
+            serve = {"requests": args.serve, "generated_tok_s": round(tok_s, 1),
+                     "prompt_tokens": n_in, "generated_tokens": n_out,
+                     "seconds": round(seconds, 3), "steps": steps}
 
     value = args.batch / ms * 1e3
     ctx_mid = args.context + args.warmup + args.steps / 2
@@ -305,13 +359,13 @@ def main() -> int:
     achieved = step_bytes / (ms * 1e-3) / 1e9
     flops = prefill_flops(cfg, args.prefill_tokens)
     out = {
-        "metric": f"decode tok/s at batch {args.batch} (Llama-3-8B sizes, random weights)",
+        "metric": f"decode tok/s at batch {args.batch} ({args.sizes} sizes, random weights)",
         "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "impl": "ours",
-        "config": {"model": "llama-3-8b-sizes", "layers": cfg.num_hidden_layers,
-                   "layers_of_config": SIZES["num_hidden_layers"], "hidden": cfg.hidden_size,
+        "config": {"model": f"{args.sizes}-sizes", "layers": cfg.num_hidden_layers,
+                   "layers_of_config": sizes["num_hidden_layers"], "hidden": cfg.hidden_size,
                    "heads": cfg.num_attention_heads, "kv_heads": cfg.kv_heads,
                    "head_dim": cfg.head_size, "intermediate": cfg.intermediate_size,
                    "vocab": cfg.vocab_size, "global_batch": args.batch, "seq_len": args.context,
@@ -331,6 +385,8 @@ def main() -> int:
         "points": points,
         "clocks": clk.summary,
     }
+    if serve is not None:
+        out["serve"] = serve
     print(json.dumps(out))
     return 0
 
