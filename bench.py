@@ -43,6 +43,8 @@ SIZES_BY_NAME = {
                         tie_word_embeddings=False, max_position_embeddings=4096,
                         torch_dtype="bfloat16"),
 }
+SIZE_LABELS = {"llama-3-8b": "Llama-3-8B", "llama-3.2-1b": "Llama-3.2-1B",
+               "llama-2-13b": "Llama-2-13B"}
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
 
 
@@ -359,7 +361,8 @@ def main() -> int:
     achieved = step_bytes / (ms * 1e-3) / 1e9
     flops = prefill_flops(cfg, args.prefill_tokens)
     out = {
-        "metric": f"decode tok/s at batch {args.batch} ({args.sizes} sizes, random weights)",
+        "metric": f"decode tok/s at batch {args.batch} ({SIZE_LABELS[args.sizes]} sizes, "
+                  "random weights)",
         "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",

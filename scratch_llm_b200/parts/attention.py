@@ -123,8 +123,11 @@ class GQAttention(Mixer):
             scratch = torch.empty(ops.attention_mma_scratch_floats(qkv.shape[0], H, hd, n_splits),
                                   dtype=torch.float32, device=qkv.device)
         cos, sin, interleaved, write = rope
+        # every row is single and the list names them in order: the kernel needs no list
+        # (one load less on the way to a CTA's first keys)
+        rows = None if batch.n_single == batch.n_rows else batch.single_rows
         ops.attention_mma_decode(qkv, cache.pages, cache.block_table, cache.page_size,
-                                 batch.row_start, batch.row_pos0, out, batch.single_rows,
+                                 batch.row_start, batch.row_pos0, out, rows,
                                  batch.n_single, H, G, hd, self.scale, self.window, cos, sin,
                                  interleaved, write, n_splits, scratch)
 
