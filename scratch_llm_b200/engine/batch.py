@@ -60,7 +60,11 @@ def _next_power_of_two(n: int) -> int:
 def pad_plan(n_tokens: int, n_single: int, n_multi: int, n_out: int) -> PadPlan:
     """Tokens go up to a multiple of 16 (of 64 above 128), single rows to a multiple of 8,
     multi rows to a power of two, wanted places to a power of two up to 8 and to a multiple of
-    16 above; nothing wanted stays nothing wanted."""
+    16 above; nothing wanted stays nothing wanted.  A decode step (every row one token, its
+    logits wanted) only goes up to the next multiple of 8 in all three."""
+    if n_multi == 0 and n_tokens == n_single == n_out:
+        n = _round_up(n_tokens, 8)
+        return PadPlan(n, n, 0, n)
     tokens = _round_up(n_tokens, 16) if n_tokens <= 128 else _round_up(n_tokens, 64)
     out = 0 if n_out == 0 else _next_power_of_two(n_out) if n_out <= 8 else _round_up(n_out, 16)
     return PadPlan(tokens, _round_up(n_single, 8), _next_power_of_two(n_multi) if n_multi else 0,

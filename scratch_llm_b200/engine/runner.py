@@ -46,6 +46,9 @@ class _CapturedStep:
         self.n_kernels = 0
 
 
+#: decode steps of more rows than this are padded to the next multiple of 8 rows (below, a
+#: step's few rows choose how many CTAs share a row's keys, and padding would spoil the choice)
+DECODE_EXACT_ROWS = 8
 #: a step that wants more logits than this is not padded and captured: a captured step keeps
 #: its output [wanted, vocabulary] in 32-bit allocated
 PAD_MAX_WANTED = 64
@@ -143,9 +146,15 @@ class ModelRunner:
                 raise OutOfPages(f"no free pages for {len(row.tokens)} more tokens of request "
                                  f"{row.request_id!r} (free per group: {self.cache.free_pages()})")
         if self.cuda_graphs and all(len(r.tokens) == 1 and len(r.want) == 1 for r in rows):
-            batch = self.build_batch(rows, table_width=self._table_width)
+            # up to DECODE_EXACT_ROWS rows a decode step is captured as it is; above, for the
+            # next multiple of 8 rows, so that requests that end one by one do not ask for a
+            # capture each
+            pad = self.pad_small_steps and len(rows) > DECODE_EXACT_ROWS
+            batch = self.build_batch(rows, table_width=self._table_width, pad=pad)
             # launch shapes depend on these two alone
-            logits = self._graph_step(batch, (len(rows), batch.context_bucket), 2)
+            logits = self._graph_step(batch, (batch.n_tokens, batch.context_bucket), 2)
+            if pad and batch.n_real_out != batch.n_out:
+                logits = logits[:batch.n_real_out]
         elif (self.pad_small_steps and sum(len(r.tokens) for r in rows) <= PAD_MAX_TOKENS
               and sum(len(r.want) for r in rows) <= PAD_MAX_WANTED):
             # block tables as wide as the longest row needs, rounded up to a power of two
