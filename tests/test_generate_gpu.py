@@ -341,3 +341,32 @@ def test_serve_with_arrivals_on_a_test_clock(model_dirs):
     with pytest.raises(ValueError, match=">= 0"):
         llm.serve(reqs, arrivals_s=[0.0, 1.0, -1.0, 0.0, 0.0])
     assert not llm.has_work
+
+
+@pytest.mark.parametrize("dtype, slack", [("float32", 2e-5), ("bfloat16", 6e-2)])
+def test_decode_steps_of_many_rows_are_padded_to_eights(dtype, slack, model_dirs):
+    """More than 8 requests decode together and end one by one: their steps are padded to the
+    next multiple of 8 rows, so that 13, 12, 11, ... rows replay one captured graph.  The
+    tokens are those of a runner without graphs (32-bit: the same; bfloat16: each the plain
+    model's choice up to rounding)."""
+    from scratch_llm_b200 import LLM, Request, SamplingParams
+    vocab = CONFIGS["C"]["vocab_size"]
+    prompts = prompts_for(vocab, [9, 20, 3, 14, 7, 11, 5, 16, 8, 12, 6, 10, 4])
+    reqs = [Request(i, p, SamplingParams(temperature=0.0, max_tokens=6 + 2 * i))
+            for i, p in enumerate(prompts)]
+    llm = LLM(model_dirs["C"], dtype=dtype, max_tokens=2048, page_size=PAGE_SIZE["C"],
+              max_requests=16)
+    got = llm.serve(reqs)
+    decode_keys = [k for k in llm.runner._captured if isinstance(k[0], int)]
+    assert {k[0] for k in decode_keys} <= {1, 2, 3, 4, 5, 6, 7, 8, 16}
+    assert any(k[0] == 16 for k in decode_keys) and llm.runner.replayed_steps > 10
+    if dtype == "float32":
+        plain = LLM(model_dirs["C"], dtype=dtype, max_tokens=2048, page_size=PAGE_SIZE["C"],
+                    max_requests=16, lookahead=False)
+        plain.runner.cuda_graphs = plain.runner.pad_small_steps = False
+        want = plain.serve(reqs)
+        assert [c.token_ids for c in got.completed] == [c.token_ids for c in want.completed]
+    else:
+        cfg, w = plain_weights(model_dirs["C"], dtype)
+        for r, c in list(zip(reqs, got.completed))[::3]:
+            assert_greedy_consistent(cfg, w, list(r.prompt_ids), list(c.token_ids), slack)
