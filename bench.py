@@ -16,7 +16,6 @@ from __future__ import annotations
 import argparse
 import json
 import statistics
-import subprocess
 import sys
 import time
 from pathlib import Path
@@ -24,147 +23,58 @@ from pathlib import Path
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
+from baseline.common import (SIZE_LABELS, SIZES_BY_NAME, ClockSampler, kv_bytes_per_token,
+                             model_config, peaks, prefill_flops, spread, weight_bytes)
+
 # the headline configuration: Llama-3-8B layer sizes
-SIZES = dict(hidden_size=4096, num_hidden_layers=32, num_attention_heads=32,
-             num_key_value_heads=8, head_dim=128, intermediate_size=14336, vocab_size=128256,
-             rope_theta=500000.0, rms_norm_eps=1e-5, tie_word_embeddings=False,
-             max_position_embeddings=8192, torch_dtype="bfloat16")
-# the other two configurations at full size that the baseline names; chosen with --sizes
-SIZES_BY_NAME = {
-    "llama-3-8b": SIZES,
-    "llama-3.2-1b": dict(hidden_size=2048, num_hidden_layers=16, num_attention_heads=32,
-                         num_key_value_heads=8, head_dim=64, intermediate_size=8192,
-                         vocab_size=128256, rope_theta=500000.0, rms_norm_eps=1e-5,
-                         tie_word_embeddings=True, max_position_embeddings=8192,
-                         torch_dtype="bfloat16"),
-    "llama-2-13b": dict(hidden_size=5120, num_hidden_layers=40, num_attention_heads=40,
-                        num_key_value_heads=40, head_dim=128, intermediate_size=13824,
-                        vocab_size=32000, rope_theta=10000.0, rms_norm_eps=1e-5,
-                        tie_word_embeddings=False, max_position_embeddings=4096,
-                        torch_dtype="bfloat16"),
-}
-SIZE_LABELS = {"llama-3-8b": "Llama-3-8B", "llama-3.2-1b": "Llama-3.2-1B",
-               "llama-2-13b": "Llama-2-13B"}
-FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
-
-
-def peaks() -> dict:
-    path = ROOT / "MEASURED_PEAKS.json"
-    if path.is_file():
-        try:
-            raw = json.loads(path.read_text())
-            return {"hbm_gbs": float(raw["hbm_gbs"]), "bf16_tflops": float(raw["bf16_tflops"]),
-                    "bf16_tflops_sustained": float(raw.get("bf16_tflops_sustained",
-                                                           raw["bf16_tflops"])),
-                    "source": "measured"}
-        except (KeyError, ValueError, json.JSONDecodeError):
-            pass
-    return dict(FALLBACK_PEAKS)
-
-
-class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while a timed region runs."""
-
-    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
-              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-              "clocks_event_reasons.sw_power_cap")
-
-    def __init__(self, index: int) -> None:
-        self.index, self.proc = index, None
-
-    def __enter__(self):
-        try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
-                 "--format=csv,noheader,nounits", "-lms", "100"],
-                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-        except OSError:
-            self.proc = None
-        return self
-
-    def __exit__(self, *exc):
-        self.summary = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
-        if self.proc is None:
-            return
-        time.sleep(0.15)
-        self.proc.terminate()
-        try:
-            out, _ = self.proc.communicate(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-            out = ""
-        clocks, reasons, mx = [], set(), None
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in out.splitlines():
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) != 6:
-                continue
-            try:
-                clocks.append(float(parts[0]))
-                mx = float(parts[1])
-            except ValueError:
-                continue
-            for name, val in zip(names, parts[2:]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        if clocks:
-            self.summary = {"sm_mhz": statistics.median(clocks), "sm_max_mhz": mx,
-                            "reasons": sorted(reasons), "samples": len(clocks)}
-
-
-def reference_arm() -> int:
-    # The one offline install this arm may use,
-    #   python -m pip install --no-index --no-build-isolation --find-links /opt/wheelhouse
-    #       --target baseline/_ref <reference>
-    # fails: the reference's build backend (hatchling) is not in the wheelhouse.
-    ref = ROOT / "baseline" / "_ref" / "scratch_llm"
-    why = ("offline install failed: the reference's build backend 'hatchling' is not in the "
-           "wheelhouse (ModuleNotFoundError), so baseline/_ref is empty")
-    if ref.is_dir():
-        why = ("baseline/_ref holds the reference, but it has no engine for Llama-3-8B sizes "
-               "on one call: not wired")
-    print(json.dumps({"impl": "reference", "unavailable": why}))
-    return 0
+SIZES = SIZES_BY_NAME["llama-3-8b"]
+#: up to this many layers the random model is written as a model folder and opened through
+#: ``load_model`` like any user's; above, each tensor is drawn on the device when the model
+#: asks for it (a folder of 16 GB takes minutes to draw on the CPU and to write)
+FOLDER_MAX_LAYERS = 4
 
 
 def build_engine(n_layers: int, capacity_tokens: int, max_requests: int, page_size: int,
                  sizes: dict | None = None):
+    """The engine with random weights N(0, 0.02): (config, model, LLM, how the weights came)."""
+    import tempfile
+
     import torch
 
     from scratch_llm_b200.config import config_from_dict
-    from scratch_llm_b200.engine import LLM, build_model
+    from scratch_llm_b200.engine import LLM, build_model, load_model
     from scratch_llm_b200.kernels import ops
     from scratch_llm_b200.parts import BuildContext
+    from scratch_llm_b200.weights import write_random_model
     from scratch_llm_b200.weights.random_init import random_tensors
 
     cfg = config_from_dict({**(sizes or SIZES), "num_hidden_layers": n_layers,
                             "architectures": ["LlamaForCausalLM"]})
-    model = build_model(cfg)
-    ops.prepare(model.head_dims(), verbose=False)
-    specs = model.param_specs()
-    device = torch.device("cuda", 0)
+    if n_layers <= FOLDER_MAX_LAYERS:
+        # the way a user's model comes in: a folder with config.json and model.safetensors
+        with tempfile.TemporaryDirectory() as tmp:
+            write_random_model(cfg, tmp, seed=0)
+            model = load_model(tmp, "bfloat16", verbose=False)
+        how = "model folder (config.json + model.safetensors) through load_model"
+    else:
+        model = build_model(cfg)
+        ops.prepare(model.head_dims(), verbose=False)
+        specs = model.param_specs()
+        device = torch.device("cuda", 0)
 
-    class Lazy(dict):
-        """Draws each tensor on the device when the model asks for it, so that the random
-        weights never exist twice."""
+        class Lazy(dict):
+            """Draws each tensor on the device when the model asks for it, so that the random
+            weights never exist twice."""
 
-        def __missing__(self, name):
-            return random_tensors({name: specs[name]}, 0, torch.bfloat16, device=device)[name]
+            def __missing__(self, name):
+                return random_tensors({name: specs[name]}, 0, torch.bfloat16, device=device)[name]
 
-    model.load(Lazy(), BuildContext(dtype=torch.bfloat16, device=device))
-    model.config = cfg
+        model.load(Lazy(), BuildContext(dtype=torch.bfloat16, device=device))
+        model.config = cfg
+        how = "drawn on the device tensor by tensor (no folder of this size is written)"
     llm = LLM(model, max_tokens=capacity_tokens, page_size=page_size, max_requests=max_requests,
               max_batch_tokens=4096, chunk_size=2048)
-    return cfg, model, llm
-
-
-def weight_bytes(cfg) -> int:
-    """Bytes of weights a decode step reads (a tied output matrix is still read; the embedding
-    table is not: a step gathers a few rows of it)."""
-    d, f, v = cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size
-    hq, hk = cfg.num_attention_heads * cfg.head_size, cfg.kv_heads * cfg.head_size
-    per_layer = (hq + 2 * hk) * d + d * hq + 3 * f * d
-    return 2 * (cfg.num_hidden_layers * per_layer + v * d) + 4 * (2 * cfg.num_hidden_layers + 1) * d
+    return cfg, model, llm, how
 
 
 def time_serve(llm, cfg, n_requests: int, seed: int = 3):
@@ -189,14 +99,6 @@ def time_serve(llm, cfg, n_requests: int, seed: int = 3):
     return n_out / res.wall_s, n_in, n_out, res.wall_s, res.stats.steps
 
 
-def prefill_flops(cfg, t: int) -> float:
-    d, f, v = cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size
-    hq, hk = cfg.num_attention_heads * cfg.head_size, cfg.kv_heads * cfg.head_size
-    linear = 2.0 * t * cfg.num_hidden_layers * ((hq + 2 * hk) * d + d * hq + 3 * f * d)
-    attn = cfg.num_hidden_layers * 4.0 * hq * (t * (t + 1) / 2)   # causal half of QK^T and PV
-    return linear + attn + 2.0 * v * d   # the output matrix on the one wanted row
-
-
 def random_prompts(n: int, length: int, vocab: int, seed: int):
     import torch
     g = torch.Generator().manual_seed(seed)
@@ -204,7 +106,8 @@ def random_prompts(n: int, length: int, vocab: int, seed: int):
 
 
 def time_decode_device(llm, cfg, batch: int, context: int, steps: int, warmup: int, tag: str):
-    """Device time of `steps` decode steps at `batch` x `context`; returns (ms/step, launches)."""
+    """Device time of `steps` decode steps at `batch` x `context`: (ms/step over the whole
+    timed region, launches, per-step times).  One CUDA event after every step."""
     import torch
 
     from scratch_llm_b200.engine import RowInput
@@ -230,16 +133,18 @@ def time_decode_device(llm, cfg, batch: int, context: int, steps: int, warmup: i
         one(k)
     torch.cuda.synchronize()
     before = ops.launch_count + runner.replayed_kernels
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for k in range(warmup, warmup + steps):
-        one(k)
-    e1.record()
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+    marks[0].record()
+    for k in range(steps):
+        one(warmup + k)
+        marks[k + 1].record()
     torch.cuda.synchronize()
     launches = ops.launch_count + runner.replayed_kernels - before
     for rid in ids:
         runner.release(rid)
-    return e0.elapsed_time(e1) / steps, launches
+    ops.check_kernel_errors()
+    per_step = [marks[k].elapsed_time(marks[k + 1]) for k in range(steps)]
+    return marks[0].elapsed_time(marks[-1]) / steps, launches, per_step
 
 
 def time_decode_e2e(llm, cfg, batch: int, context: int, steps: int, warmup: int):
@@ -275,7 +180,9 @@ def time_decode_e2e(llm, cfg, batch: int, context: int, steps: int, warmup: int)
     return wall * 1e3 / steps, h2d, d2h
 
 
-def time_prefill(llm, cfg, tokens: int, reps: int = 3):
+def time_prefill(llm, cfg, tokens: int, reps: int = 5):
+    """Times of `reps` prompt steps of `tokens` tokens (after two untimed ones), each from an
+    empty cache."""
     import torch
 
     from scratch_llm_b200.engine import RowInput
@@ -294,14 +201,14 @@ def time_prefill(llm, cfg, tokens: int, reps: int = 3):
         if r >= 2:
             times.append(e0.elapsed_time(e1))
         runner.release("prefill")
-    return statistics.median(times)
+    return times
 
 
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
-    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=SIZES["num_hidden_layers"])
     ap.add_argument("--batch", type=int, default=8)
@@ -317,12 +224,13 @@ def main() -> int:
     sizes = SIZES_BY_NAME[args.sizes]
     if args.layers == SIZES["num_hidden_layers"] and args.sizes != "llama-3-8b":
         args.layers = sizes["num_hidden_layers"]
-    if args.impl == "reference":
-        return reference_arm()
     if args.gpus != 1:
         print(f"bench.py measures one GPU: this engine has no multi-GPU path (--gpus {args.gpus})")
         return 2
     args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        from baseline import reference_arm
+        return reference_arm.main(args, sizes)
 
     import torch
 
@@ -332,21 +240,25 @@ def main() -> int:
     capacity = big * (args.context + args.warmup + args.steps + 64) + 4096
     if args.serve:
         capacity = max(capacity, min(args.serve, 64) * 2600)
-    cfg, model, llm = build_engine(args.layers, capacity, big + 1, args.page_size, sizes)
+    cfg, model, llm, how = build_engine(args.layers, capacity, big + 1, args.page_size, sizes)
 
     with torch.no_grad():
-        prefill_ms = time_prefill(llm, cfg, args.prefill_tokens)
+        with ClockSampler(0) as clk_prefill:
+            prefill_times = time_prefill(llm, cfg, args.prefill_tokens)
         with ClockSampler(0) as clk:
-            ms, launches = time_decode_device(llm, cfg, args.batch, args.context, args.steps,
-                                              args.warmup, "d")
-        e2e_ms, h2d, d2h = time_decode_e2e(llm, cfg, args.batch, args.context, args.steps,
-                                           args.warmup)
+            ms, launches, per_step = time_decode_device(llm, cfg, args.batch, args.context,
+                                                        args.steps, args.warmup, "d")
+        with ClockSampler(0) as clk_e2e:
+            e2e_ms, h2d, d2h = time_decode_e2e(llm, cfg, args.batch, args.context, args.steps,
+                                               args.warmup)
         points = {}
-        if not args.no_points:
-            for b in (1, 64):
-                pms, _ = time_decode_device(llm, cfg, b, args.context, max(8, args.steps // 2),
-                                            args.warmup, f"p{b}_")
-                points[f"decode_b{b}"] = round(b / pms * 1e3, 1)
+        with ClockSampler(0) as clk_points:
+            if not args.no_points:
+                for b in (1, 64):
+                    pms, _, _ = time_decode_device(llm, cfg, b, args.context,
+                                                   max(8, args.steps // 2), args.warmup,
+                                                   f"p{b}_")
+                    points[f"decode_b{b}"] = round(b / pms * 1e3, 1)
         serve = None
         if args.serve:
             tok_s, n_in, n_out, seconds, steps = time_serve(llm, cfg, args.serve)
@@ -354,39 +266,37 @@ def main() -> int:
                      "prompt_tokens": n_in, "generated_tokens": n_out,
                      "seconds": round(seconds, 3), "steps": steps}
 
+    prefill_ms = statistics.median(prefill_times)
     value = args.batch / ms * 1e3
     ctx_mid = args.context + args.warmup + args.steps / 2
-    kv_bytes = args.batch * ctx_mid * 2 * cfg.kv_heads * cfg.head_size * 2 * cfg.num_hidden_layers
-    step_bytes = weight_bytes(cfg) + kv_bytes
+    step_bytes = weight_bytes(sizes, args.layers) + \
+        args.batch * ctx_mid * kv_bytes_per_token(sizes, args.layers)
     achieved = step_bytes / (ms * 1e-3) / 1e9
-    flops = prefill_flops(cfg, args.prefill_tokens)
+    flops = prefill_flops(sizes, args.layers, args.prefill_tokens)
     out = {
         "metric": f"decode tok/s at batch {args.batch} ({SIZE_LABELS[args.sizes]} sizes, "
                   "random weights)",
         "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "impl": "ours",
-        "config": {"model": f"{args.sizes}-sizes", "layers": cfg.num_hidden_layers,
-                   "layers_of_config": sizes["num_hidden_layers"], "hidden": cfg.hidden_size,
-                   "heads": cfg.num_attention_heads, "kv_heads": cfg.kv_heads,
-                   "head_dim": cfg.head_size, "intermediate": cfg.intermediate_size,
-                   "vocab": cfg.vocab_size, "global_batch": args.batch, "seq_len": args.context,
-                   "prefill_tokens": args.prefill_tokens, "page_size": args.page_size,
-                   "parallelism": "single-gpu", "weights": "random N(0,0.02)",
-                   "l2": "inputs larger than L2 (weights read once per step)",
-                   "peaks": pk["source"]},
+        "warmup": args.warmup, "ms_per_step": round(ms, 4), "spread": spread(per_step),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic", "impl": "ours",
+        "config": model_config(args.sizes, sizes, args.layers, args.batch, args.context,
+                               args.prefill_tokens, pk["source"]),
+        "engine": {"page_size": args.page_size, "weights_from": how},
         "e2e": {"value": round(args.batch / e2e_ms * 1e3, 1), "unit": "tok/s",
                 "ms_per_step": round(e2e_ms, 4), "h2d_bytes_per_step": int(h2d),
                 "d2h_bytes_per_step": int(d2h)},
         "gpu_launches": launches,
         "prefill": {"value": round(args.prefill_tokens / prefill_ms * 1e3, 1),
                     "tokens": args.prefill_tokens, "ms": round(prefill_ms, 3),
-                    "frac": round(flops / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)},
+                    "frac": round(flops / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
+                    "spread": spread(prefill_times)},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"],
                      "unit": "GB/s", "frac": round(achieved / pk["hbm_gbs"], 4)},
         "points": points,
         "clocks": clk.summary,
+        "clocks_regions": {"prefill": clk_prefill.summary, "e2e": clk_e2e.summary,
+                           "points": clk_points.summary},
     }
     if serve is not None:
         out["serve"] = serve

@@ -106,6 +106,9 @@ struct AttnArgs {
     const int* row_start; const int* row_pos0; const int* row_list;
     bf16* out; int64_t out_stride;
     float* part_o; float* part_lse; int n_splits;
+    // tokens that part_o / part_lse have room for: a partial result of a token at or beyond
+    // this index is not written (and *part_error is set, if given) instead of landing outside
+    int64_t part_tokens; int* part_error;
     int H; int G; float scale_log2; int window;
     // attn_decode_cs_kernel only.  cos_t != nullptr: q, k and v are taken from the step's fused
     // projection as they are (q points at its first column): the kernel rotates q and the row's
@@ -393,10 +396,12 @@ __global__ void __launch_bounds__(THREADS, SPLIT ? 3 : 2) attn_mma_kernel(const 
         if (n_splits == 1) {
             a.out[(int64_t)(t0 + tok) * a.out_stride + (int64_t)(g * GS + j) * HD + d] =
                 __float2bfloat16_rn(val);
-        } else {
+        } else if (t0 + tok < a.part_tokens) {
             a.part_o[(qh * n_splits + split) * HD + d] = val;
             if (d == 0)
                 a.part_lse[qh * n_splits + split] = den > 0.f ? mm + log2f(den) : -INFINITY;
+        } else if (a.part_error && d == 0) {
+            *a.part_error = 1;   // the caller's token count does not cover this row
         }
     }
 }
@@ -733,6 +738,8 @@ __global__ void __launch_bounds__(THREADS, 3) attn_decode_cs_kernel(const AttnAr
             for (int dn = 0; dn < CS_OT; ++dn)
                 *reinterpret_cast<__nv_bfloat162*>(dst + dn * 8) =
                     __floats2bfloat162_rn(o[dn][2 * h] * inv, o[dn][2 * h + 1] * inv);
+        } else if (t0 + tok >= a.part_tokens) {
+            if (a.part_error && warp == 0 && (lane & 3) == 0) *a.part_error = 1;
         } else {
             const int64_t qh = (int64_t)(t0 + tok) * a.H + g * GS + j;
             float* dst = a.part_o + (qh * n_splits + split) * HD + col0;
@@ -759,13 +766,15 @@ constexpr int MERGE_WARPS = 4;
 __global__ void __launch_bounds__(MERGE_WARPS * 32) attn_merge_kernel(
         const float* __restrict__ part_o, const float* __restrict__ part_lse, int n_splits,
         const int* __restrict__ row_start, const int* __restrict__ row_list,
-        bf16* __restrict__ out, int64_t out_stride, int H) {
+        bf16* __restrict__ out, int64_t out_stride, int H, int64_t part_tokens) {
     pdl_wait();
     pdl_trigger();
     const int r = row_list ? row_list[blockIdx.x] : blockIdx.x;
     const int head = blockIdx.y * MERGE_WARPS + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (head >= H) return;
-    for (int t = row_start[r]; t < row_start[r + 1]; ++t) {
+    // (tokens beyond what the partial arrays cover were not written: they are left out here too)
+    const int t_end = (int)min((int64_t)row_start[r + 1], part_tokens);
+    for (int t = row_start[r]; t < t_end; ++t) {
         const int64_t qh = (int64_t)t * H + head;
         const float* lse = part_lse + qh * n_splits;
         float mm = -INFINITY;
@@ -834,6 +843,7 @@ SLLM_EXPORT int sllm_attn_mma(const void* q, int64_t q_stride, const void* pages
     a.page_size = page_size; a.row_start = row_start; a.row_pos0 = row_pos0; a.row_list = row_list;
     a.out = (bf16*)out; a.out_stride = out_stride;
     a.part_o = nullptr; a.part_lse = nullptr; a.n_splits = 1;
+    a.part_tokens = n_tokens_total; a.part_error = nullptr;
     a.cos_t = nullptr; a.sin_t = nullptr; a.interleaved = 1; a.write_kv = 0;
     a.H = H; a.G = G; a.scale_log2 = scale * 1.4426950408889634f; a.window = window;
     const int GS = H / G;
@@ -871,7 +881,7 @@ SLLM_EXPORT int sllm_attn_mma(const void* q, int64_t q_stride, const void* pages
         dim3 mgrid(n_list, (H + MERGE_WARPS - 1) / MERGE_WARPS);
         e = sllm_launch_pdl(attn_merge_kernel, mgrid, dim3(MERGE_WARPS * 32), 0, stream,
                             (const float*)a.part_o, (const float*)a.part_lse, n_splits, row_start,
-                            row_list, (bf16*)out, out_stride, H);
+                            row_list, (bf16*)out, out_stride, H, a.part_tokens);
         if (e != cudaSuccess) return (int)e;
     }
     return 0;
@@ -908,6 +918,7 @@ SLLM_EXPORT int sllm_attn_mma_decode(const void* qkv, int64_t qkv_stride, void* 
     a.page_size = page_size; a.row_start = row_start; a.row_pos0 = row_pos0; a.row_list = row_list;
     a.out = (bf16*)out; a.out_stride = out_stride;
     a.part_o = nullptr; a.part_lse = nullptr; a.n_splits = n_splits;
+    a.part_tokens = n_tokens_total; a.part_error = nullptr;
     a.H = H; a.G = G; a.scale_log2 = scale * 1.4426950408889634f; a.window = window;
     a.cos_t = cos_t; a.sin_t = sin_t; a.interleaved = interleaved; a.write_kv = write_kv;
     if (n_splits > 1) {
@@ -926,7 +937,7 @@ SLLM_EXPORT int sllm_attn_mma_decode(const void* qkv, int64_t qkv_stride, void* 
         dim3 mgrid(n_list, (H + MERGE_WARPS - 1) / MERGE_WARPS);
         e = sllm_launch_pdl(attn_merge_kernel, mgrid, dim3(MERGE_WARPS * 32), 0, stream,
                             (const float*)a.part_o, (const float*)a.part_lse, n_splits, row_start,
-                            row_list, (bf16*)out, out_stride, H);
+                            row_list, (bf16*)out, out_stride, H, a.part_tokens);
         if (e != cudaSuccess) return (int)e;
     }
     return 0;
@@ -944,8 +955,12 @@ SLLM_EXPORT int sllm_attn_mma_decode_fused_supported() { return 0; }
 // Scratch for the partial results.  In host code this name is only a handle for
 // cudaGetSymbolAddress: it is not a device address and must never be passed to a kernel.
 static __device__ __align__(256) float g_noalloc_scratch[SLLM_NOALLOC_SCRATCH_FLOATS];
+// Set by a kernel that met a token at or beyond n_tokens_total (its partial result was left out
+// instead of being written outside the array).
+static __device__ int g_noalloc_overrun;
 
-static float* g_noalloc_ptr[64];  // device address of the array, per device ordinal
+static float* g_noalloc_ptr[64];     // device address of the array, per device ordinal
+static int* g_noalloc_flag_ptr[64];  // device address of the overrun flag, per device ordinal
 static char g_noalloc_error[256] = "";
 
 SLLM_EXPORT int64_t sllm_attn_mma_noalloc_capacity_floats(void) {
@@ -953,6 +968,13 @@ SLLM_EXPORT int64_t sllm_attn_mma_noalloc_capacity_floats(void) {
 }
 
 SLLM_EXPORT const char* sllm_attn_mma_noalloc_error(void) { return g_noalloc_error; }
+
+SLLM_EXPORT int sllm_attn_mma_noalloc_overrun(void) {
+    int flag = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&flag, g_noalloc_overrun, sizeof(int)) != cudaSuccess) return -1;
+    if (flag && cudaMemcpyToSymbol(g_noalloc_overrun, &zero, sizeof(int)) != cudaSuccess) return -1;
+    return flag;
+}
 
 SLLM_EXPORT int sllm_attn_mma_split_noalloc(const void* q, int64_t q_stride, const void* pages,
                                             const int* block_table, int table_stride,
@@ -963,9 +985,17 @@ SLLM_EXPORT int sllm_attn_mma_split_noalloc(const void* q, int64_t q_stride, con
                                             int64_t n_tokens_total, cudaStream_t stream) {
     if (n_list <= 0 || max_new <= 0) return 0;
     if (H <= 0 || G <= 0 || H % G != 0 || page_size <= 0 || window < 0 || n_list > 65535 ||
-        G > 65535 || (q_stride % 8) != 0 || (out_stride % 2) != 0 || n_splits < 1 ||
-        n_tokens_total < 0)
+        G > 65535 || H > 65535 || (q_stride % 8) != 0 || (out_stride % 2) != 0 || n_splits < 1 ||
+        n_splits > SLLM_NOALLOC_MAX_SPLITS || n_tokens_total < 0 ||
+        n_tokens_total > (int64_t)SLLM_NOALLOC_SCRATCH_FLOATS) {
+        // (the bounds on H, n_splits and n_tokens_total also keep the product below from
+        // overflowing 64 bits)
+        snprintf(g_noalloc_error, sizeof(g_noalloc_error),
+                 "sllm_attn_mma_split_noalloc: an argument is out of range (1 <= n_splits <= %d, "
+                 "0 <= n_tokens_total <= %lld, strides of q a multiple of 8 and of out even)",
+                 SLLM_NOALLOC_MAX_SPLITS, (long long)SLLM_NOALLOC_SCRATCH_FLOATS);
         return (int)cudaErrorInvalidValue;
+    }
     if (((uintptr_t)q & 15) || ((uintptr_t)pages & 15) || ((uintptr_t)out & 3))
         return (int)cudaErrorInvalidValue;
     const int64_t need = sllm_attn_mma_scratch_floats(n_tokens_total, H, n_splits);
@@ -985,13 +1015,17 @@ SLLM_EXPORT int sllm_attn_mma_split_noalloc(const void* q, int64_t q_stride, con
     if (dev < 0 || dev >= 64) return (int)cudaErrorInvalidDevice;
     if (g_noalloc_ptr[dev] == nullptr) {
         float* ptr = nullptr;
+        int* flag = nullptr;
         e = cudaGetSymbolAddress((void**)&ptr, g_noalloc_scratch);
         if (e != cudaSuccess) return (int)e;
+        e = cudaGetSymbolAddress((void**)&flag, g_noalloc_overrun);
+        if (e != cudaSuccess) return (int)e;
+        g_noalloc_flag_ptr[dev] = flag;
         g_noalloc_ptr[dev] = ptr;
     }
     float* scratch = g_noalloc_ptr[dev];
 
-    AttnArgs a;
+    AttnArgs a{};   // (the fields of the fused decode kernel stay null / 0: it is not used here)
     a.q = (const bf16*)q; a.q_stride = q_stride;
     a.pages = (const bf16*)pages; a.block_table = block_table; a.table_stride = table_stride;
     a.page_size = page_size; a.row_start = row_start; a.row_pos0 = row_pos0; a.row_list = row_list;
@@ -999,6 +1033,8 @@ SLLM_EXPORT int sllm_attn_mma_split_noalloc(const void* q, int64_t q_stride, con
     a.part_o = n_splits > 1 ? scratch : nullptr;
     a.part_lse = n_splits > 1 ? scratch + n_tokens_total * H * n_splits * HD : nullptr;
     a.n_splits = n_splits;
+    a.part_tokens = n_tokens_total; a.part_error = g_noalloc_flag_ptr[dev];
+    a.cos_t = nullptr; a.sin_t = nullptr; a.interleaved = 1; a.write_kv = 0;
     a.H = H; a.G = G; a.scale_log2 = scale * 1.4426950408889634f; a.window = window;
     const int GS = H / G;
     const size_t smem = smem_bytes<true>();
@@ -1011,7 +1047,8 @@ SLLM_EXPORT int sllm_attn_mma_split_noalloc(const void* q, int64_t q_stride, con
     if (n_splits > 1) {
         dim3 mgrid(n_list, (H + MERGE_WARPS - 1) / MERGE_WARPS);
         attn_merge_kernel<<<mgrid, MERGE_WARPS * 32, 0, stream>>>(
-            a.part_o, a.part_lse, n_splits, row_start, row_list, (bf16*)out, out_stride, H);
+            a.part_o, a.part_lse, n_splits, row_start, row_list, (bf16*)out, out_stride, H,
+            a.part_tokens);
         SLLM_LAUNCH_CHECK();
     }
     return 0;

@@ -15,8 +15,16 @@
 // process exits, used or not; one such array exists per compiled head size.
 //
 // Contract.
-//  * Same arguments and results as sllm_attn_mma with split = 1, without `scratch`; inputs
-//    and outputs are still the caller's.
+//  * Same arguments as sllm_attn_mma with split = 1, without `scratch`; inputs and outputs are
+//    still the caller's.  Results equal sllm_attn_mma's up to bfloat16 rounding (for head
+//    sizes that are multiples of 64 that entry point runs another kernel of the same math).
+//  * n_tokens_total is the token count of the WHOLE batch that row_start describes: one past
+//    the largest token index of any listed row (row_start[r + 1] for the last listed row r),
+//    not the number of tokens in the listed rows.  Partial results are indexed by a token's
+//    index in the batch.  A listed row that reaches beyond n_tokens_total is not written
+//    outside the array: the tokens beyond it are left out of the output, and
+//    sllm_attn_mma_noalloc_overrun() then returns 1.
+//  * 1 <= n_splits <= SLLM_NOALLOC_MAX_SPLITS.
 //  * Calls no cudaMalloc, cudaFree or any allocating library routine.
 //  * Size limit: n_tokens_total * H * n_splits * (head size + 1) floats must fit the array
 //    (n_splits = 1 needs none).  A larger request is refused: the call returns
@@ -38,6 +46,7 @@
 #ifndef SLLM_NOALLOC_SCRATCH_FLOATS
 #define SLLM_NOALLOC_SCRATCH_FLOATS (2 * 1024 * 1024)
 #endif
+#define SLLM_NOALLOC_MAX_SPLITS 1024
 
 extern "C" {
 
@@ -52,6 +61,13 @@ int sllm_attn_mma_split_noalloc(const void* q, int64_t q_stride, const void* pag
 // The capacity of the built-in scratch array, in floats.
 int64_t sllm_attn_mma_noalloc_capacity_floats(void);
 
-// Text of the last refusal of sllm_attn_mma_split_noalloc in this process ("" if none).
+// Text of the last refusal of sllm_attn_mma_split_noalloc in this process ("" if none).  One
+// buffer per process, written without a lock: read it from the thread that got the refusal,
+// before another thread calls the entry point.
 const char* sllm_attn_mma_noalloc_error(void);
+
+// 1 if a kernel of an earlier call on the current device met a token at or beyond its
+// n_tokens_total (see above), 0 if none did, -1 if the flag could not be read.  Waits for the
+// device (a copy from device memory) and clears the flag.
+int sllm_attn_mma_noalloc_overrun(void);
 }

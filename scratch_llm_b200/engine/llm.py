@@ -58,6 +58,10 @@ class _InFlight:
     pending: PendingSample | None
 
 
+#: :meth:`LLM.step` reads the kernels' error words every this many steps
+CHECK_ERRORS_EVERY = 128
+
+
 def _seed_of(request: Request) -> int:
     if request.params.seed is not None:
         return int(request.params.seed)
@@ -93,6 +97,7 @@ class LLM:
         self._sched: Scheduler | None = None
         self.lookahead = lookahead
         self._in_flight: _InFlight | None = None
+        self._unchecked_steps = 0
 
     def _scheduler(self, policy: str = "continuous") -> Scheduler:
         return Scheduler(self.runner.cache, self.runner.max_position, self.max_batch_tokens,
@@ -149,6 +154,13 @@ class LLM:
                 self._in_flight = self._launch([r for r, _ in ahead], [j for _, j in ahead],
                                                want_logprobs)
         tokens, lps = cur.pending.result() if cur.pending is not None else ([], None)
+        # kernels with bounded waits record a code and go on with invalid results when a wait
+        # gives up: reading the codes waits for the device, so they are read every so many
+        # steps (and at the end of serve), and the error is raised before more tokens are kept
+        self._unchecked_steps += 1
+        if self._unchecked_steps >= CHECK_ERRORS_EVERY:
+            self._unchecked_steps = 0
+            ops.check_kernel_errors()
         alive = [not s.finish_reason for s in cur.sampling]
         sched.complete(cur.rows, tokens, lps)
         return {s.request.request_id: t for s, t, a in zip(cur.sampling, tokens, alive) if a}

@@ -1,7 +1,8 @@
 """Compiles the CUDA sources of ``csrc/`` for sm_100a with nvcc and caches the shared
 libraries.
 
-Each library is keyed by a hash of its sources, the headers beside them and its flags, so an
+Each library is keyed by a hash of its sources, the headers beside them (``*.cuh`` and
+``*.h``) and its flags, so an
 edited kernel is rebuilt and an unchanged one is loaded as is.  Libraries are kept in
 ``scratch_llm_b200/_build`` when that folder can be written, else in a per-user folder under
 the system's temporary directory; no home directory is needed.  What a model needs is compiled
@@ -80,7 +81,7 @@ def _pick_build_dir() -> Path:
 
 def _digest(sources: Sequence[Path], flags: Sequence[str]) -> str:
     h = hashlib.sha256()
-    for p in sorted(CSRC.glob("*.cuh")):
+    for p in sorted([*CSRC.glob("*.cuh"), *CSRC.glob("*.h")]):
         h.update(p.name.encode())
         h.update(p.read_bytes())
     for p in sources:

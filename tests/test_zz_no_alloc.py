@@ -40,21 +40,31 @@ def build_case(seed):
     return [t.cuda() for t in (q, pages, table, row_start, row_pos0)]
 
 
-def call_noalloc(lib, q, pages, table, row_start, row_pos0, out, n_splits):
+def call_noalloc(lib, q, pages, table, row_start, row_pos0, out, n_splits, row_list=None,
+                 n_list=None, max_new=1, window=0, n_tokens_total=None):
     ptr = lambda t: c_void_p(t.data_ptr())  # noqa: E731
     return lib.sllm_attn_mma_split_noalloc(
         ptr(q), c_int64(q.stride(0)), ptr(pages), ptr(table), c_int(table.stride(0)), c_int(PAGE),
-        ptr(row_start), ptr(row_pos0), c_void_p(0), c_int(q.shape[0]), c_int(1), ptr(out),
-        c_int64(out.stride(0)), c_int(H), c_int(G), c_float(1.0 / math.sqrt(HD)), c_int(0),
-        c_int(n_splits), c_int64(q.shape[0]), c_void_p(torch.cuda.current_stream().cuda_stream))
+        ptr(row_start), ptr(row_pos0), ptr(row_list) if row_list is not None else c_void_p(0),
+        c_int(q.shape[0] if n_list is None else n_list), c_int(max_new), ptr(out),
+        c_int64(out.stride(0)), c_int(H), c_int(G), c_float(1.0 / math.sqrt(HD)), c_int(window),
+        c_int(n_splits), c_int64(q.shape[0] if n_tokens_total is None else n_tokens_total),
+        c_void_p(torch.cuda.current_stream().cuda_stream))
 
 
-def test_no_alloc_entry_point_matches_the_allocating_one():
+def load_library():
     from scratch_llm_b200.kernels import build, ops
 
     lib = ctypes.CDLL(str(build.compile_library(*ops.attention_mma_library(HD), verbose=False)))
     lib.sllm_attn_mma_noalloc_capacity_floats.restype = c_int64
     lib.sllm_attn_mma_noalloc_error.restype = ctypes.c_char_p
+    return lib
+
+
+def test_no_alloc_entry_point_matches_the_allocating_one():
+    from scratch_llm_b200.kernels import ops
+
+    lib = load_library()
     capacity = lib.sllm_attn_mma_noalloc_capacity_floats()
     assert capacity == 2 * 1024 * 1024
 
@@ -85,3 +95,86 @@ def test_no_alloc_entry_point_matches_the_allocating_one():
     text = lib.sllm_attn_mma_noalloc_error().decode()
     assert "scratch floats" in text and str(capacity) in text
     assert not got.any()   # nothing was launched
+
+
+# rows of a larger batch: (keys cached before this step, new tokens).  The call lists rows 1, 3
+# and 4 only; their tokens lie in the middle and at the end of the batch.
+ROWS = [(40, 5), (70, 3), (0, 9), (129, 1), (15, 2)]
+LISTED = [1, 3, 4]
+WINDOW = 37
+
+
+def test_no_alloc_entry_point_with_a_row_list_several_tokens_and_a_window():
+    """Listed rows of a larger batch, rows of several new tokens and a window of keys, against
+    the plain attention; then the same call with a token count that covers only the listed
+    rows' tokens (a caller's likely mistake): nothing is written outside the array, the tokens
+    beyond the count are left out and the overrun flag says so."""
+    from plain import llama_plain as P
+
+    lib = load_library()
+    g = torch.Generator().manual_seed(11)
+    ks = [torch.randn(G, a + n, HD, generator=g).to(torch.bfloat16).float() for a, n in ROWS]
+    vs = [torch.randn(G, a + n, HD, generator=g).to(torch.bfloat16).float() for a, n in ROWS]
+    qs = [torch.randn(H, n, HD, generator=g).to(torch.bfloat16).float() for a, n in ROWS]
+    n_pages = sum(-(-(a + n) // PAGE) for a, n in ROWS) + 1
+    pages = torch.full((n_pages, 2, G, PAGE, HD), float("nan")).to(torch.bfloat16)
+    order = torch.randperm(n_pages, generator=g).tolist()
+    table = torch.full((len(ROWS), max(-(-(a + n) // PAGE) for a, n in ROWS)), -1,
+                       dtype=torch.int32)
+    for r, (k, v) in enumerate(zip(ks, vs)):
+        for p in range(-(-k.shape[1] // PAGE)):
+            phys = order.pop()
+            table[r, p] = phys
+            m = min(PAGE, k.shape[1] - p * PAGE)
+            pages[phys, 0, :, :m] = k[:, p * PAGE:p * PAGE + m].to(torch.bfloat16)
+            pages[phys, 1, :, :m] = v[:, p * PAGE:p * PAGE + m].to(torch.bfloat16)
+    q = torch.cat([x.transpose(0, 1).reshape(x.shape[1], H * HD) for x in qs]).to(torch.bfloat16)
+    starts = [0]
+    for _, n in ROWS:
+        starts.append(starts[-1] + n)
+    dev = [t.cuda() for t in (q, pages, table, torch.tensor(starts, dtype=torch.int32),
+                              torch.tensor([a for a, _ in ROWS], dtype=torch.int32),
+                              torch.tensor(LISTED, dtype=torch.int32))]
+    q, pages, table, row_start, row_pos0, row_list = dev
+    max_new = max(ROWS[r][1] for r in LISTED)
+
+    def plain_row(r):
+        a, n = ROWS[r]
+        out = P.attention(qs[r], ks[r], vs[r], torch.arange(a, a + n), torch.arange(a + n),
+                          1.0 / math.sqrt(HD), WINDOW)
+        return out.transpose(0, 1).reshape(n, H * HD)
+
+    for n_splits in (4, 1):
+        got = torch.full_like(q, float("nan"))
+        code = call_noalloc(lib, q, pages, table, row_start, row_pos0, got, n_splits,
+                            row_list=row_list, n_list=len(LISTED), max_new=max_new, window=WINDOW)
+        assert code == 0, lib.sllm_attn_mma_noalloc_error()
+        torch.cuda.synchronize()
+        assert lib.sllm_attn_mma_noalloc_overrun() == 0
+        got = got.cpu().float()
+        for r in range(len(ROWS)):
+            mine = got[starts[r]:starts[r + 1]]
+            if r in LISTED:
+                torch.testing.assert_close(mine, plain_row(r), rtol=1.6e-2, atol=1e-2)
+            else:
+                assert torch.isnan(mine).all()   # rows that were not listed are not touched
+
+    # a token count that covers only the listed rows' tokens (6) while their indices reach 20
+    listed_tokens = sum(ROWS[r][1] for r in LISTED)
+    got = torch.full_like(q, float("nan"))
+    code = call_noalloc(lib, q, pages, table, row_start, row_pos0, got, 4, row_list=row_list,
+                        n_list=len(LISTED), max_new=max_new, window=WINDOW,
+                        n_tokens_total=listed_tokens)
+    assert code == 0
+    torch.cuda.synchronize()
+    assert lib.sllm_attn_mma_noalloc_overrun() == 1
+    assert lib.sllm_attn_mma_noalloc_overrun() == 0        # reading the flag clears it
+    got = got.cpu().float()
+    r = LISTED[0]                                           # tokens 5, 6, 7: index 5 is covered
+    torch.testing.assert_close(got[5:6], plain_row(r)[:1], rtol=1.6e-2, atol=1e-2)
+    assert torch.isnan(got[listed_tokens:]).all()           # the rest was left out, not written
+
+    # out-of-range split counts are refused before anything is computed from them
+    for bad in (0, 1025, 1 << 30):
+        assert call_noalloc(lib, q, pages, table, row_start, row_pos0, got.cuda().bfloat16(), bad,
+                            row_list=row_list, n_list=len(LISTED), max_new=max_new) == 1
