@@ -8,14 +8,16 @@ of its group, as one block table serves all layers in the reference
 (src/scratch_llm/kv_cache.py:326-333).  Groups whose mixers keep every key and groups that keep
 a window of keys therefore have pages of their own; a window group gives pages back as soon as
 the window has passed them.  Pages are given back when a request ends.  Page contents are
-never cleared: nothing may depend on what a reused page held
-(tests/test_paged_cache.py:164-184 of the reference poisons free blocks for the same reason).
+never cleared, not even once: nothing may depend on what a fresh or a reused page holds
+(tests/test_paged_cache.py:164-184 of the reference poisons free blocks for the same reason;
+``poison_free_pages=True`` does that here: the pool starts as NaN and every page that is given
+back is filled with NaN again, so that a kernel that lets a stale place reach a result shows).
 
 Beside the pages the manager owns ``max_requests`` *state slots*.  A request holds one slot
 while it is live; entries whose mixer declares a :class:`StateSpec` get a tensor
 ``[max_requests, *shape]`` indexed by slot, zeroed when a request is admitted.  The Llama
-architecture has no such state; the slots still carry each request's sampling state
-(seed and counter) for the engine.
+architecture has no such state.  (A request's position and its sampling seed and counter live
+on the host, with the scheduler, and are sent with every step's descriptor.)
 
 The manager is host-side bookkeeping plus the device tensors; with ``device=None`` it allocates
 no tensor and can be exercised on a machine without a GPU.
@@ -57,12 +59,14 @@ class CacheManager:
     def __init__(self, kv_specs: Sequence[KVSpec | None],
                  state_specs: Sequence[StateSpec | None], page_size: int,
                  n_pages: int, max_requests: int, dtype: torch.dtype = torch.float32,
-                 device: torch.device | str | None = None) -> None:
+                 device: torch.device | str | None = None,
+                 poison_free_pages: bool = False) -> None:
         if page_size < 1:
             raise ValueError(f"page size must be positive, got {page_size}")
         if max_requests < 1:
             raise ValueError("max_requests must be positive")
         self.page_size, self.max_requests = page_size, max_requests
+        self.poison_free_pages = poison_free_pages
         self.dtype, self.device = dtype, (torch.device(device) if device is not None else None)
         self.groups: list[Group] = []
         self.entry_group: list[tuple[int, int] | None] = []  # entry -> (group, index in group)
@@ -82,12 +86,11 @@ class CacheManager:
         if self.device is not None:
             for group in self.groups:
                 s = group.spec
-                # zero-filled once: the contents of a reused page never matter, but the
-                # tcgen05 attention kernel multiplies values beyond a request's context by
-                # probabilities that are exactly zero, which needs them to be finite
-                group.pages = torch.zeros((len(group.entries), n_pages, 2, s.n_kv_heads,
+                group.pages = torch.empty((len(group.entries), n_pages, 2, s.n_kv_heads,
                                            page_size, s.head_dim), dtype=dtype,
                                           device=self.device)
+                if poison_free_pages:
+                    group.pages.fill_(float("nan"))
             for entry, st in enumerate(self.state_specs):
                 if st is not None:
                     self.states[entry] = torch.zeros((max_requests, *st.shape), dtype=st.dtype,
@@ -162,7 +165,7 @@ class CacheManager:
             n_dead_pages = max(0, (last_dead + 1) // self.page_size)
             dead = [table[i] for i in range(min(n_dead_pages, len(table))) if table[i] >= 0]
             if dead:
-                g.pool.free(dead, request_id)
+                self._give_back(g, dead, request_id)
                 for i in range(min(n_dead_pages, len(table))):
                     table[i] = -1
                 rc.tables_np[gi][:min(n_dead_pages, len(table))] = -1
@@ -171,8 +174,13 @@ class CacheManager:
         """The request has ended (or is set back): give its pages and its slot back."""
         rc = self.requests.pop(request_id)
         for g, table in zip(self.groups, rc.tables):
-            g.pool.free([p for p in table if p >= 0], request_id)
+            self._give_back(g, [p for p in table if p >= 0], request_id)
         self._free_slots.append(rc.slot)
+
+    def _give_back(self, group: Group, pages: list[int], request_id: Hashable) -> None:
+        group.pool.free(pages, request_id)
+        if self.poison_free_pages and pages and group.pages is not None:
+            group.pages[:, torch.tensor(pages, device=group.pages.device)] = float("nan")
 
     # ---------------------------------------------------------------------------- views
 

@@ -23,10 +23,12 @@
 //   S(t) the tensor pipe computes S(t+1), and P(t) V runs beside the softmax of S(t+1).
 //
 // Takes head sizes that are multiples of 64 up to 256, group sizes that divide 128, page sizes
-// that divide 128, no window; other shapes use attention_mma.cu.  Cache memory beyond a
-// request's context must hold finite values (the cache manager zero-fills the pool once and
-// only finite keys and values are ever stored): such values are multiplied by probabilities
-// that are exactly zero.  Every mbarrier wait is bounded; errors land in g_attn_tc_error.
+// that divide 128, no window; other shapes use attention_mma.cu.  What the cache holds beyond
+// a row's last position never reaches a result: scores of such keys are overwritten with -inf
+// before the softmax, and the rows of V beyond the last position in the row's last key tile
+// (the only tile that can hold any) are zeroed in shared memory by the producer warp after
+// the copy has landed and before P V is issued, because their probabilities are exactly zero
+// and 0 x NaN would be NaN.  Every mbarrier wait is bounded; errors land in g_attn_tc_error.
 #include <cuda.h>
 
 #include "common.cuh"
@@ -222,7 +224,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     uint64_t* p_full = s_full + 2;                           // [2]
     uint64_t* pv_done = p_full + 2;
     uint64_t* o_done = pv_done + 1;                          // the last P V is over
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 1);
+    uint64_t* v_clean = o_done + 1;                          // the last tile's V holds no stale rows
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(v_clean + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = a.row_list ? a.row_list[blockIdx.y] : blockIdx.y;
@@ -252,6 +255,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         }
         atc_init(pv_done, 1);
         atc_init(o_done, 1);
+        atc_init(v_clean, 1);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     }
@@ -278,7 +282,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         const int64_t rows_per_page = (int64_t)2 * a.G * a.page_size;
         const int* table = a.block_table + (int64_t)r * a.table_stride;
         const int n_pages_held = last_pos / a.page_size + 1;
-        const int spare = table[0];   // a page that certainly holds finite values
+        const int spare = table[0];   // stands in for pages the row does not hold (masked keys)
+        bool cleaned = false;
         for (int t = 0; t < n_tiles; ++t) {
             const int s = t % KV_STAGES;
             // next tile's page numbers are requested before the wait for a free stage
@@ -311,7 +316,30 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                                c * 64, (int)row_v);
                 }
             }
+            if (t == n_tiles - 1) {
+                // Keys beyond last_pos (the rest of the row's last page, pages it does not hold)
+                // are whatever earlier requests left there.  Their probabilities are exactly
+                // zero, but 0 x NaN is NaN: zero those rows of V (generic-proxy stores), make
+                // them visible to the tensor pipe's reads (async proxy), then tell the MMA warp.
+                // A key's row is 128 contiguous bytes per 64-column block (the swizzle permutes
+                // 16-byte pieces inside a row only).
+                if (atc_wait(&kv_full[s], (t / KV_STAGES) & 1, 9)) {
+                    const int first_stale = last_pos - t * TKV + 1;      // 1..128
+                    const int n16 = (TKV - first_stale) * 8;             // 16-byte pieces per block
+                    for (int c = 0; c < NCB; ++c) {
+                        uint4* base = reinterpret_cast<uint4*>(v_dst + c * SUB_BYTES +
+                                                               first_stale * 128);
+                        for (int i = lane; i < n16; i += 32) base[i] = make_uint4(0u, 0u, 0u, 0u);
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                }
+                __syncwarp();
+                if (lane == 0) atc_arrive(v_clean);
+                cleaned = true;
+            }
         }
+        // (a producer that gave up still releases the MMA warp, which then meets its own limit)
+        if (!cleaned && lane == 0) atc_arrive(v_clean);
     } else if (warp == 1) {
         if (lane == 0) {
             // instruction descriptors: D f32, A and B bf16; QK^T: both K-major, N = 128;
@@ -356,6 +384,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 // O += P V once the softmax warps have written P: K steps of 16 keys
                 ok = atc_wait(&p_full[atc_buf(t)], atc_phase(t), 4);
                 if (!ok) break;
+                if (t == n_tiles - 1) {       // the producer has zeroed the stale rows of V
+                    ok = atc_wait(v_clean, 0, 10);
+                    if (!ok) break;
+                }
                 atc_fence_after();
                 const uint32_t v_addr = atc_u32(kv_s + (size_t)s * 2 * KV_BYTES) + KV_BYTES;
 #pragma unroll
@@ -535,7 +567,7 @@ SLLM_EXPORT int sllm_attn_tc_error() {
 }
 
 // q / out: [n_tokens, stride] bfloat16, head h at columns [h*HD, (h+1)*HD).  pages:
-// [n_pages, 2, G, page_size, HD] bfloat16, finite everywhere.  row_list: the n_list rows served
+// [n_pages, 2, G, page_size, HD] bfloat16 (places no listed row uses may hold anything).  row_list: the n_list rows served
 // (nullptr: rows 0..n_list-1); max_new: the largest number of new tokens among them.
 SLLM_EXPORT int sllm_attn_tc(const void* q, int64_t q_stride, int64_t n_tokens, const void* pages,
                              int64_t n_pages, const int* block_table, int table_stride,

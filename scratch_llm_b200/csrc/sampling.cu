@@ -231,9 +231,54 @@ argmax_kernel(const float* __restrict__ logits, int64_t ld, int V, ArgMax* __res
     }
 }
 
+// log_softmax of each row in 32-bit (maximum subtracted, expf and logf at full precision).
+// rows_out != nullptr: the whole row [n_rows, V]; taken != nullptr: taken_out[r] =
+// log_softmax(logits[r])[taken[r]] (the log-probability of a given token, the reference's
+// LocalBackend.score: src/scratch_llm/rollout/local.py:50-79).  One block per row.
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+log_softmax_kernel(const float* __restrict__ logits, int64_t ld, int V,
+                   float* __restrict__ rows_out, const int* __restrict__ taken,
+                   float* __restrict__ taken_out) {
+    __shared__ float fscratch[33];
+    __shared__ float red[33];
+    const int row = blockIdx.x, tid = threadIdx.x;
+    const float* z = logits + (int64_t)row * ld;
+    float mx = -INFINITY;
+    for (int i = tid; i < V; i += blockDim.x) mx = fmaxf(mx, z[i]);
+    mx = warp_max(mx);
+    if ((tid & 31) == 0) red[tid >> 5] = mx;
+    __syncthreads();
+    mx = red[0];
+    for (int w = 1; w < (int)((blockDim.x + 31) >> 5); ++w) mx = fmaxf(mx, red[w]);
+    float part = 0.f;
+    for (int i = tid; i < V; i += blockDim.x) part += expf(z[i] - mx);
+    const float lz = mx + logf(block_sum(part, fscratch));
+    if (rows_out) {
+        float* o = rows_out + (int64_t)row * V;
+        for (int i = tid; i < V; i += blockDim.x) o[i] = z[i] - lz;
+    }
+    if (taken && taken_out && tid == 0) {
+        const int t = taken[row];
+        taken_out[row] = (t >= 0 && t < V) ? z[t] - lz : __int_as_float(0x7fc00000);
+    }
+}
+
 }  // namespace sllm
 
 using namespace sllm;
+
+// See log_softmax_kernel.  rows_out, or taken and taken_out, may be nullptr.
+SLLM_EXPORT int sllm_log_softmax(const float* logits, int64_t ld, int n_rows, int V,
+                                 float* rows_out, const int* taken, float* taken_out,
+                                 cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (V <= 0 || ld < V || (taken != nullptr) != (taken_out != nullptr))
+        return (int)cudaErrorInvalidValue;
+    log_softmax_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(logits, ld, V, rows_out, taken,
+                                                              taken_out);
+    SLLM_LAUNCH_CHECK();
+    return 0;
+}
 
 // Bytes of scratch sllm_argmax needs for n_rows rows (partial results and tickets).  The
 // tickets (the last 4 * n_rows bytes) must be zero before the first call.

@@ -256,6 +256,67 @@ class LLM:
         return toks, lps
 
 
+    # ------------------------------------------------------------------------------ score
+
+    @torch.no_grad()
+    def _response_rows(self, prompt_ids: Sequence[int], response_ids: Sequence[int],
+                       whole_rows: bool):
+        """The rows that predict each response token (position p-1+i predicts response token i),
+        through the step function in portions of at most the token budget: the taken tokens'
+        log-probabilities [T], or the whole log_softmax rows [T, vocab] on the device."""
+        prompt, resp = list(prompt_ids), list(response_ids)
+        if not prompt or not resp:
+            raise ValueError("score needs a non-empty prompt and a non-empty response")
+        if self.has_work:
+            raise RuntimeError("score() needs an idle engine: requests from submit() are live")
+        tokens = (prompt + resp)[:-1]       # the last response token predicts nothing asked for
+        first = len(prompt) - 1
+        rid = ("score", id(tokens))
+        runner = self.runner
+        if not runner.admit(rid):
+            raise RuntimeError("no free request slot")
+        out = []
+        try:
+            for a in range(0, len(tokens), self.max_batch_tokens):
+                part = tokens[a:a + self.max_batch_tokens]
+                want = [i for i in range(len(part)) if a + i >= first]
+                logits = runner.step([RowInput(rid, part, want)])
+                if not want:
+                    continue
+                if whole_rows:
+                    rows = torch.empty_like(logits)
+                    ops.log_softmax(logits, rows_out=rows)
+                    out.append(rows)
+                else:
+                    taken = torch.tensor([resp[a + i - first] for i in want], dtype=torch.int32,
+                                         device=logits.device)
+                    lp = torch.empty(len(want), dtype=torch.float32, device=logits.device)
+                    ops.log_softmax(logits, taken=taken, taken_out=lp)
+                    out.append(lp)
+        finally:
+            runner.release(rid)
+        return torch.cat(out)
+
+    def score(self, prompt_ids, response_ids):
+        """Log-probabilities of the given response tokens under the model at temperature 1, one
+        forward over prompt + response (the reference's ``LocalBackend.score``,
+        src/scratch_llm/rollout/local.py:50-62).  One pair (lists of ints -> a list of floats)
+        or several (lists of lists -> a list of lists)."""
+        if len(prompt_ids) > 0 and isinstance(prompt_ids[0], int):
+            return self._response_rows(prompt_ids, response_ids, False).tolist()
+        if len(prompt_ids) != len(response_ids):
+            raise ValueError("one response per prompt")
+        return [self._response_rows(p, r, False).tolist()
+                for p, r in zip(prompt_ids, response_ids)]
+
+    def distribution_logprobs(self, prompt_ids: Sequence[int], response_ids: Sequence[int]
+                              ) -> torch.Tensor:
+        """The whole log_softmax rows [len(response), vocab] at the response positions, on the
+        device (the reference's ``LocalBackend.distribution_logprobs``,
+        src/scratch_llm/rollout/local.py:64-70)."""
+        return self._response_rows(prompt_ids, response_ids, True)
+
+
 def generate(llm: LLM, prompt_ids: Sequence[int], params: SamplingParams) -> list[int]:
     """The reference's ``generate`` with the engine in the model's place."""
     return llm.generate(list(prompt_ids), params)

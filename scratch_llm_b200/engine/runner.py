@@ -69,17 +69,19 @@ class ModelRunner:
     kernels read contexts and pages on the device.  Other steps of up to PAD_MAX_TOKENS tokens
     (portions of prompts, alone or beside decoded tokens) are padded to a few sizes
     (engine/batch.py::pad_plan) and captured per padded shape, if every mixer and feed-forward
-    is ``pad_safe``: launched plainly, such a step costs the host more than the device."""
+    is ``pad_safe``: launched plainly, such a step costs the host more than the device.
+    ``poison_free_pages``: a debugging aid of the cache manager (free pages hold NaN)."""
 
     def __init__(self, model: DecoderModel, page_size: int, n_pages: int, max_requests: int,
-                 cuda_graphs: bool = True) -> None:
+                 cuda_graphs: bool = True, poison_free_pages: bool = False) -> None:
         if model.ctx is None:
             raise ValueError("load the model's weights before building a runner")
         self.model = model
         self.device = model.ctx.device
         kv, st = model.cache_specs()
         self.cache = CacheManager(kv, st, page_size, n_pages, max_requests,
-                                  dtype=model.ctx.dtype, device=self.device)
+                                  dtype=model.ctx.dtype, device=self.device,
+                                  poison_free_pages=poison_free_pages)
         self._stager = BatchStager(self.device)
         self.vocab_size = model.spec.vocab_size
         self.max_position = model.spec.max_position

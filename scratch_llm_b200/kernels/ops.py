@@ -98,11 +98,15 @@ def prepare(head_dims: Sequence[int] = (), verbose: bool = True) -> None:
 
 #: kernels of this package launched so far in this process (one per successful op call)
 launch_count = 0
+#: the same per op name ("gemv_tma", "attention_tc", ...): which kernels a workload reached.
+#: Calls recorded into a CUDA graph count once, at the capture; replays are counted by the runner.
+launch_counts: dict[str, int] = {}
 
 
 def _check(code: int, what: str) -> None:
     global launch_count
     launch_count += 1
+    launch_counts[what] = launch_counts.get(what, 0) + 1
     if code != 0:
         raise KernelError(f"{what} failed with CUDA error {code} "
                           f"({'invalid value: a size this kernel does not take' if code == 1 else 'see cudaError_t'})")
@@ -532,8 +536,8 @@ def attention_tc(q: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor
                  row_list: torch.Tensor | None, n_list: int, max_new: int, n_heads: int,
                  n_kv_heads: int, head_dim: int, scale: float) -> torch.Tensor:
     """Causal attention of the listed rows (prompt portions) over the paged cache on tcgen05
-    tensor cores with S, P and O in tensor memory.  The cache must hold finite values
-    everywhere (also in places no request uses)."""
+    tensor cores with S, P and O in tensor memory.  What the cache holds in places beyond a
+    row's context never reaches a result (NaN included)."""
     _need(q, torch.bfloat16, "q", contiguous=False)
     _need(pages, torch.bfloat16, "pages")
     _need(out, torch.bfloat16, "out", contiguous=False)
@@ -637,3 +641,28 @@ def sample(logits: torch.Tensor, out: torch.Tensor, temperature: torch.Tensor | 
         _ptr(top_p), _ptr(seed), _ptr(counter), _ptr(out), _ptr(logprob_out), _ptr(probs_out),
         _stream()), "sample")
     return out
+
+
+def log_softmax(logits: torch.Tensor, rows_out: torch.Tensor | None = None,
+                taken: torch.Tensor | None = None, taken_out: torch.Tensor | None = None) -> None:
+    """log_softmax of each row of ``logits`` [n, V] (32-bit).  ``rows_out`` [n, V] gets the whole
+    rows; ``taken`` (int32 [n]) and ``taken_out`` (float32 [n]) the log-probability of one given
+    token per row."""
+    _need(logits, torch.float32, "logits", contiguous=False)
+    n, v = logits.shape
+    if logits.stride(1) != 1:
+        raise KernelError("log_softmax: rows must be contiguous")
+    if rows_out is not None:
+        _need(rows_out, torch.float32, "rows_out")
+        if rows_out.shape != (n, v):
+            raise KernelError("rows_out shape")
+    if (taken is None) != (taken_out is None):
+        raise KernelError("taken and taken_out come together")
+    if taken is not None:
+        _need(taken, torch.int32, "taken")
+        _need(taken_out, torch.float32, "taken_out")
+        if taken.numel() != n or taken_out.numel() != n:
+            raise KernelError("taken / taken_out must have one entry per row")
+    _check(_core("sllm_sampling").sllm_log_softmax(
+        _ptr(logits), c_int64(logits.stride(0)), c_int(n), c_int(v), _ptr(rows_out), _ptr(taken),
+        _ptr(taken_out), _stream()), "log_softmax")

@@ -67,4 +67,7 @@ class Tokenizer:
         return ids
 
     def decode(self, ids) -> str:
-        return b"".join(self.vocab[i] for i in ids).decode("utf-8", errors="replace")
+        """The text of ``ids``; an id the vocabulary does not hold (a model whose output matrix
+        is larger than its tokenizer) becomes the replacement character."""
+        unknown = "\ufffd".encode("utf-8")
+        return b"".join(self.vocab.get(i, unknown) for i in ids).decode("utf-8", errors="replace")

@@ -33,6 +33,7 @@ def test_tokenizer_merges_in_learned_order_and_round_trips(tokenizer):
     assert tokenizer.decode(ids) == "the cat in the hat"
     text = "héllo  wörld\n\n 123"
     assert tokenizer.decode(tokenizer.encode(text)) == text
+    assert tokenizer.decode([257, 100000]) == "the\ufffd"   # an id the vocabulary does not hold
 
 
 def test_specials_are_single_ids_and_split_out(tokenizer):

@@ -184,3 +184,39 @@ def test_integer_tables_become_int32(tmp_path):
                       {"t": torch.tensor([1, 2], dtype=torch.int64), "h": torch.ones(2, dtype=torch.float16)})
     got = load_tensors(tmp_path, {"t": ParamSpec((2,), "int"), "h": ParamSpec((2,), "gain")})
     assert got["t"].dtype == torch.int32 and got["h"].dtype == torch.bfloat16
+
+
+def test_sharded_model_folder(tmp_path):
+    """A model stored as two shards with ``model.safetensors.index.json``: the loader opens every
+    shard the index names and finds each tensor by name; a tensor that is missing from its shard
+    is reported by name in the one error."""
+    from scratch_llm_b200.weights import write_safetensors
+    cfg = config_from_dict(TINY_A)
+    whole = write_random_model(cfg, tmp_path / "whole", 7)
+    specs = build_model(cfg).param_specs()
+    want = load_tensors(whole, specs)
+    names = sorted(want)
+    first, second = names[:len(names) // 2], names[len(names) // 2:]
+
+    def write(folder, parts):
+        folder.mkdir()
+        (folder / "config.json").write_text((whole / "config.json").read_text())
+        weight_map = {}
+        for k, part in enumerate(parts, 1):
+            shard = f"model-{k:05d}-of-{len(parts):05d}.safetensors"
+            write_safetensors(folder / shard, {n: want[n] for n in part})
+            weight_map.update({n: shard for n in part})
+        (folder / "model.safetensors.index.json").write_text(json.dumps(
+            {"metadata": {}, "weight_map": weight_map}))
+
+    write(tmp_path / "sharded", [first, second])
+    got = load_tensors(tmp_path / "sharded", specs)
+    assert got.keys() == want.keys()
+    for n in names:
+        assert torch.equal(got[n], want[n])
+
+    gone = second[0]
+    write(tmp_path / "short", [first, second[1:]])
+    with pytest.raises(WeightError) as err:
+        load_tensors(tmp_path / "short", specs)
+    assert err.value.missing == [gone] and not err.value.unexpected

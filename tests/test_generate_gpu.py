@@ -202,6 +202,8 @@ def test_small_steps_padded_and_replayed_as_graphs(dtype, tol, model_dirs):
     g = torch.Generator().manual_seed(3)
     toks = lambda n: torch.randint(0, vocab, (n,), generator=g).tolist()  # noqa: E731
     for r in runners:
+        for grp in r.cache.groups:
+            grp.pages.zero_()    # the pools are compared whole below, and start as they came
         for rid in "abcd":
             assert r.admit(rid)
     # shapes repeat (19 and 21 tokens both pad to 32, ...), rows change places, some steps want
@@ -370,3 +372,93 @@ def test_decode_steps_of_many_rows_are_padded_to_eights(dtype, slack, model_dirs
         cfg, w = plain_weights(model_dirs["C"], dtype)
         for r, c in list(zip(reqs, got.completed))[::3]:
             assert_greedy_consistent(cfg, w, list(r.prompt_ids), list(c.token_ids), slack)
+
+
+def run_cli(args, stdin_text):
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+    root = Path(__file__).resolve().parent.parent
+    env = dict(os.environ, PYTHONPATH=str(root), PYTHONIOENCODING="utf-8")
+    proc = subprocess.run([sys.executable, "-m", "scratch_llm_b200.chat_cli", *args],
+                          input=stdin_text, capture_output=True, text=True, encoding="utf-8",
+                          timeout=600, env=env, cwd=str(root))
+    assert proc.returncode == 0, proc.stderr[-3000:]
+    return proc.stdout
+
+
+def test_command_line_with_token_ids(tmp_path):
+    """``python -m scratch_llm_b200.chat_cli`` as a child process: it writes the model folder
+    from a configuration (--random-weights), opens it, reads token ids from standard input and
+    prints the greedy continuation, which is the plain model's."""
+    import json
+    (tmp_path / "cfg.json").write_text(json.dumps(CONFIGS["A"]))
+    model = tmp_path / "model"
+    prompts = prompts_for(CONFIGS["A"]["vocab_size"], [7, 19], seed=3)
+    text = "".join(" ".join(map(str, p)) + "\n" for p in prompts)
+    out = run_cli(["--model", str(model), "--random-weights", str(tmp_path / "cfg.json"),
+                   "--seed", "4", "--max-tokens", "8", "--dtype", "float32"], text)
+    cfg, w = P.read_model_dir(model)
+    replies = [line.split("bot> ", 1)[1] for line in out.splitlines() if "bot> " in line]
+    assert [[int(t) for t in r.split()] for r in replies] == \
+        [P.greedy(cfg, w, p, 8) for p in prompts]
+
+
+def test_command_line_with_a_tokenizer(tmp_path, model_dirs):
+    """The same with a ``tokenizer.json`` in the reference's format beside the model: text in,
+    chat template around it, greedy reply out until the end-of-turn token or --max-tokens."""
+    import json
+    import shutil
+    from scratch_llm_b200.chat_cli import EOT, SPECIALS, render_for_completion, special_id
+    from scratch_llm_b200.tokenizer import Tokenizer
+    model = tmp_path / "model"
+    shutil.copytree(model_dirs["C"], model)          # vocabulary 331 >= the tokenizer's 265 ids
+    vocab = {str(i): bytes([i]).decode("latin-1") for i in range(256)}
+    merges = [["t", "h"], ["th", "e"], [" ", "the"], ["i", "n"], [" ", "c"]]
+    for k, (a, b) in enumerate(merges):
+        vocab[str(256 + k)] = a + b
+    for k, sp in enumerate(SPECIALS):
+        vocab[str(261 + k)] = sp
+    for i in range(265, CONFIGS["C"]["vocab_size"]):     # every id the model can produce has a text
+        vocab[str(i)] = f"[{i}]"
+    data = tmp_path / "data"
+    data.mkdir()
+    (data / "tokenizer.json").write_text(json.dumps(
+        {"vocab": vocab, "merges": merges, "special_tokens": SPECIALS}))
+    tok = Tokenizer.load(data / "tokenizer.json")
+    out = run_cli(["--ckpt", str(model), "--data-dir", str(data), "--max-tokens", "6",
+                   "--dtype", "float32"], "the cat in the hat\n")
+    cfg, w = P.read_model_dir(model)
+    eot = special_id(tok, EOT)
+    specials = {special_id(tok, sp) for sp in SPECIALS}
+    gen = P.greedy(cfg, w, render_for_completion([("user", "the cat in the hat")], tok), 6)
+    if eot in gen:
+        gen = gen[:gen.index(eot)]
+    want = tok.decode([t for t in gen if t not in specials])
+    assert f"bot> {want}\n" in out
+
+
+def test_score_gives_the_log_probabilities_of_given_tokens(model_dirs):
+    """``LLM.score`` (the reference's LocalBackend.score, src/scratch_llm/rollout/local.py:50-79):
+    log-probabilities of given continuation tokens under the model, against the plain model's
+    log-softmax; a long pair is cut into portions by the token budget."""
+    from scratch_llm_b200 import LLM
+    cfg, w = plain_weights(model_dirs["B"], "float32")
+    llm = LLM(model_dirs["B"], dtype="float32", max_tokens=1024, page_size=8,
+              max_batch_tokens=48)
+    prompts = prompts_for(cfg["vocab_size"], [1, 9, 70], seed=8)
+    conts = prompts_for(cfg["vocab_size"], [5, 1, 60], seed=9)
+    got = llm.score(prompts, conts)
+    for p, c, g in zip(prompts, conts, got):
+        logp = torch.log_softmax(P.forward(cfg, w, p + c), dim=-1)
+        want = [float(logp[len(p) - 1 + i, t]) for i, t in enumerate(c)]
+        torch.testing.assert_close(torch.tensor(g), torch.tensor(want), rtol=1e-4, atol=1e-4)
+    one = llm.score(prompts[1], conts[1])
+    torch.testing.assert_close(torch.tensor(one), torch.tensor(got[1]), rtol=1e-5, atol=1e-5)
+    dist = llm.distribution_logprobs(prompts[2], conts[2])
+    p, c = prompts[2], conts[2]
+    want = torch.log_softmax(P.forward(cfg, w, p + c), dim=-1)[len(p) - 1:len(p) - 1 + len(c)]
+    assert dist.shape == (len(c), cfg["vocab_size"])
+    torch.testing.assert_close(dist.cpu(), want, rtol=1e-4, atol=1e-4)
+    assert not llm.runner.cache.requests

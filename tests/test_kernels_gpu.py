@@ -25,6 +25,21 @@ def rand(*shape, dtype=torch.float32, seed=0, scale=1.0):
     return (torch.randn(*shape, generator=g) * scale).to(dtype)
 
 
+@pytest.mark.parametrize("v", [331, 128256])
+def test_log_softmax(ops, v):
+    logits = rand(5, v + 3, seed=v, scale=4.0)[:, :v]          # rows inside a wider buffer
+    logits[2, 7] = 60.0                                        # one token takes all the mass
+    taken = torch.tensor([0, v - 1, 7, 123, 5], dtype=torch.int32)
+    want = torch.log_softmax(logits.double(), dim=-1).float()
+    x = logits.cuda()
+    x = torch.cat([x, torch.zeros(5, 3, device="cuda")], 1)[:, :v]
+    rows = torch.empty(5, v, dtype=torch.float32, device="cuda")
+    lp = torch.empty(5, dtype=torch.float32, device="cuda")
+    ops.log_softmax(x, rows_out=rows, taken=taken.cuda(), taken_out=lp)
+    torch.testing.assert_close(rows.cpu(), want, rtol=1e-5, atol=2e-5)
+    torch.testing.assert_close(lp.cpu(), want[torch.arange(5), taken.long()], rtol=1e-5, atol=2e-5)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_embed(ops, dtype):
     table = rand(1000, 200, dtype=DT[dtype])
@@ -381,8 +396,9 @@ def test_decode_attention_fused_with_rotation(ops, H, G, hd, page, window, n_spl
                                            (2, 2, 192, 32)])
 def test_attention_tcgen05(ops, H, G, hd, page):
     """Prompt portions on the tcgen05 kernel: long rows (several key tiles, several query
-    tiles), rows that start deep in a context, short rows; unused cache places hold large
-    finite values (the kernel's contract) that must not reach a result."""
+    tiles), rows that start deep in a context, short rows; unused cache places hold NaN, as for
+    the other attention kernels, and must not reach a result (rows that end in the middle of a
+    page and of a key tile leave stale keys and values right behind their last position)."""
     ops.prepare([hd], verbose=False)
     rows = [(0, 300), (450, 40), (0, 17), (127, 2), (128, 129), (1000, 30)]
     global ATTN_ROWS
@@ -390,7 +406,8 @@ def test_attention_tcgen05(ops, H, G, hd, page):
     ATTN_ROWS = rows
     try:
         case = attention_case("bfloat16", H, G, hd, page)
-        pages = torch.nan_to_num(case["pages"].float(), nan=3e4).to(torch.bfloat16)
+        pages = case["pages"]
+        assert torch.isnan(pages.float()).any()
         q = case["wide"][:, :H * hd]
         out = torch.full((q.shape[0], H * hd), float("nan"), dtype=torch.bfloat16, device="cuda")
         every = list(range(len(rows)))

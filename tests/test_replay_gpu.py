@@ -12,7 +12,13 @@ pytestmark = pytest.mark.gpu
 
 LENGTHS = {"A": [5, 17, 33, 70, 128, 64, 15, 16, 90, 31, 120],
            "B": [2, 9, 40, 64, 100, 130, 47, 17, 80, 33, 200, 8, 150],
-           "C": [34, 95, 200, 61, 150, 333, 16, 640, 48, 100]}
+           "C": [34, 95, 200, 61, 150, 333, 16, 640, 48, 100],
+           "D": [2, 700, 130, 64, 450, 17, 333, 65, 600, 31, 129, 512]}
+# D's shapes select the kernels of the full-size models; its mixed traces cut prompts into
+# portions of up to 500 tokens, so that steps of more than 512 tokens with several long portions
+# beside single tokens occur (launched as they are, not padded), the tcgen05 attention gets a
+# row list of several entries and the fused tcgen05 gate/up product runs
+MIXED = {"D": dict(sizes=(2, 3, 40, 130, 300, 500), prefill_part=0.9)}
 # 32-bit: a few ulp of the largest logit per reduction; bfloat16: operands rounded to 8 bits
 TOL = {"float32": dict(rtol=2e-5, atol=5e-6), "bfloat16": dict(rtol=3e-2, atol=3e-2)}
 
@@ -34,10 +40,16 @@ def expected(model_dirs):
     return get
 
 
-def make_runner(model_dir, dtype, page_size, max_tokens, max_requests=4):
+def make_runner(model_dir, dtype, page_size, max_tokens, max_requests=4, **kw):
     from scratch_llm_b200.engine import ModelRunner, load_model
     model = load_model(model_dir, dtype, verbose=False)
-    return ModelRunner(model, page_size, -(-max_tokens // page_size), max_requests)
+    return ModelRunner(model, page_size, -(-max_tokens // page_size), max_requests, **kw)
+
+
+def ways(name):
+    mixed = (lambda r: T.mixed(r, **MIXED[name])) if name in MIXED else T.mixed
+    return {"whole": T.whole, "tail": T.tail_one_by_one, "portions": T.changing_portions,
+            "mixed": mixed}
 
 
 def compare(got, want_logits, dtype):
@@ -52,24 +64,85 @@ def compare(got, want_logits, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name, page", [("A", 16), ("B", 8), ("C", 16), ("D", 16), ("D", 64)])
 @pytest.mark.parametrize("way", ["whole", "tail", "portions", "mixed"])
-def test_replay_matches_plain(way, name, dtype, model_dirs, expected):
+def test_replay_matches_plain(way, name, page, dtype, model_dirs, expected):
+    """Free pages hold NaN (the pool at the start, and every page that is given back): a
+    kernel that lets a place beyond a request's context reach a result fails here."""
+    from scratch_llm_b200.kernels import ops
     reqs, want = expected(name, dtype)
-    steps = {"whole": T.whole, "tail": T.tail_one_by_one, "portions": T.changing_portions,
-             "mixed": T.mixed}[way](reqs)
-    peak = T.peak_tokens(steps)
-    runner = make_runner(model_dirs[name], dtype, PAGE_SIZE[name], peak)
+    steps = ways(name)[way](reqs)
+    peak = T.peak_tokens(steps, round_to=max(64, page))
+    runner = make_runner(model_dirs[name], dtype, page, peak, poison_free_pages=True)
+    before = dict(ops.launch_counts)
     with torch.no_grad():
         got = T.run_in_process(runner, steps)
+    ops.check_kernel_errors()
     assert len(got) == sum(len(t) for t in reqs.values())
     compare(got, want, dtype)
     assert not runner.cache.requests and all(
         g.pool.n_free == g.pool.n_pages for g in runner.cache.groups)
     if way == "mixed":
         # the pool is smaller than what all requests need together: pages were used again
-        total_pages = sum(-(-len(t) // PAGE_SIZE[name]) for t in reqs.values())
+        total_pages = sum(-(-len(t) // page) for t in reqs.values())
         assert runner.cache.groups[0].pool.n_pages < total_pages
+    if way == "mixed" and name == "D":
+        ran = {k: v - before.get(k, 0) for k, v in ops.launch_counts.items()}
+        if dtype == "bfloat16":
+            # the kernels that the full-size models spend their time in all ran in this trace
+            for op in ("gemv_tma", "attention_mma_decode", "attention_tc", "gemm_tc"):
+                assert ran.get(op, 0) > 0, f"{op} never ran: {ran}"
+
+
+def is_large_mixed(step):
+    """More than 512 tokens (launched as it is, not padded), at least two portions that fill a
+    128-query tile of the tcgen05 attention (32 tokens x 4 heads of a group), a single token."""
+    sizes = [len(e["tokens"]) for e in step["entries"]]
+    return sum(sizes) > 512 and sum(n >= 32 for n in sizes) >= 2 and 1 in sizes
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_large_mixed_steps(dtype, model_dirs):
+    """Steps of several hundred tokens that hold two or three long prompt portions beside
+    decoded tokens of other requests, as a scheduler with a large token budget builds them all
+    the time; pages are used again and free pages hold NaN."""
+    from scratch_llm_b200.kernels import ops
+    cfg, w = P.read_model_dir(model_dirs["D"])
+    if dtype == "bfloat16":
+        w = {k: v.to(torch.bfloat16).float() for k, v in w.items()}
+    lengths = [700, 450, 130, 600, 512, 333, 650, 280, 520, 64, 400]
+    reqs = T.make_requests(cfg["vocab_size"], lengths, seed=31)
+    want = {rid: P.forward(cfg, w, toks) for rid, toks in reqs.items()}
+    steps = T.large_mixed(reqs)
+    assert sum(is_large_mixed(s) for s in steps) >= 2
+    peak = T.peak_tokens(steps)
+    assert peak < sum(-(-n // 64) * 64 for n in lengths) // 2
+    runner = make_runner(model_dirs["D"], dtype, 16, peak, poison_free_pages=True)
+    with torch.no_grad():
+        got = T.run_in_process(runner, steps)
+    ops.check_kernel_errors()
+    assert len(got) == sum(lengths)
+    compare(got, want, dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("chunk", [1, 2, 4, 7, 8, 16, 32, 128])
+def test_chunk_sizes_and_lengths_around_them(chunk, dtype, model_dirs):
+    """Prompts of C-1, C, C+1 and 3C+1 tokens (plus three decoded ones) fed in chunks of C, for
+    the chunk sizes of the reference's sweep (tests/test_chunked_prefill.py:99-140 there): one
+    chunk, exactly one chunk, two chunks, a ragged last chunk."""
+    cfg, w = P.read_model_dir(model_dirs["D"])
+    if dtype == "bfloat16":
+        w = {k: v.to(torch.bfloat16).float() for k, v in w.items()}
+    lengths = [n + 3 for n in (chunk - 1, chunk, chunk + 1, 3 * chunk + 1) if n >= 1]
+    reqs = T.make_requests(cfg["vocab_size"], lengths, seed=100 + chunk)
+    want = {rid: P.forward(cfg, w, toks) for rid, toks in reqs.items()}
+    steps = T.chunks_of(reqs, chunk)
+    runner = make_runner(model_dirs["D"], dtype, 16, T.peak_tokens(steps), poison_free_pages=True)
+    with torch.no_grad():
+        got = T.run_in_process(runner, steps)
+    assert len(got) == sum(lengths)
+    compare(got, want, dtype)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -98,6 +171,44 @@ def test_cutting_does_not_change_logits_beyond_rounding(model_dirs, expected):
     for key in a:
         torch.testing.assert_close(a[key], b[key], rtol=1e-5, atol=2e-6)
         torch.testing.assert_close(a[key], c[key], rtol=1e-5, atol=2e-6)
+
+
+#: bfloat16, the four cuttings against each other, as a fraction of the row's largest logit.
+#: The cuttings share every rounding point (norm output, q and k after the rotation, the cache,
+#: probabilities, attention output, activation, product outputs) but not their kernels, so they
+#: differ by a few bfloat16 roundings that fall the other way, never by a key that one of them
+#: masks and another does not (which moves a row by tens of percent).
+BF16_CUTTING_BOUND = {"C": 0.03, "D": 0.03}
+
+
+@pytest.mark.parametrize("name", ["C", "D"])
+def test_cutting_does_not_change_bfloat16_logits_beyond_rounding(name, model_dirs, expected):
+    """The four ways of cutting against EACH OTHER in bfloat16, and their greedy tokens equal
+    wherever the plain model's margin between its two best tokens exceeds the bound."""
+    reqs, want = expected(name, "bfloat16")
+    page = PAGE_SIZE[name]
+    results = {}
+    for way, make in ways(name).items():
+        steps = make(reqs)
+        runner = make_runner(model_dirs[name], "bfloat16", page,
+                             T.peak_tokens(steps, round_to=max(64, page)))
+        with torch.no_grad():
+            results[way] = T.run_in_process(runner, steps)
+    base = results["whole"]
+    worst = 0.0
+    for way, got in results.items():
+        assert got.keys() == base.keys()
+        for key, row in got.items():
+            top = float(base[key].abs().max())
+            worst = max(worst, float((row - base[key]).abs().max()) / top)
+    print(f"config {name}: worst difference between two cuttings = {worst:.4f} of the row maximum")
+    assert worst <= BF16_CUTTING_BOUND[name]
+    for key, ref_row in base.items():
+        ref = want[key[0]][key[1]]
+        best2 = torch.topk(ref, 2).values
+        if float(best2[0] - best2[1]) > 2 * BF16_CUTTING_BOUND[name] * float(ref.abs().max()):
+            tokens = {int(results[way][key].argmax()) for way in results}
+            assert tokens == {int(ref.argmax())}, f"{key}: greedy tokens {tokens}"
 
 
 def test_long_prompt_takes_the_fused_tensor_core_path(tmp_path):

@@ -48,7 +48,7 @@ def changing_portions(requests, sizes=(7, 2, 16, 3, 33, 2, 5, 64, 2, 17)):
     return steps
 
 
-def mixed(requests, seed=0, max_live=4, prefill_part=0.6):
+def mixed(requests, seed=0, max_live=4, prefill_part=0.6, sizes=(2, 3, 5, 8, 13, 21, 40)):
     """Up to ``max_live`` requests live at a time; each first gets the larger part of its tokens
     in portions of random size (a 'prompt') and then the rest one token per step (as decoding
     would feed them), so that steps hold portions of some requests beside single tokens of
@@ -68,7 +68,7 @@ def mixed(requests, seed=0, max_live=4, prefill_part=0.6):
             if len(live) > 1 and rng.random() < 0.15:
                 continue  # left out of this step
             if fed < prompt:
-                n = min(prompt - fed, rng.choice([2, 3, 5, 8, 13, 21, 40]))
+                n = min(prompt - fed, rng.choice(list(sizes)))
                 if prompt - fed - n == 1:
                     n += 1
             else:
@@ -80,6 +80,35 @@ def mixed(requests, seed=0, max_live=4, prefill_part=0.6):
                 del live[rid]
         if entries:
             steps.append({"step": len(steps), "entries": entries, "end": end})
+    return steps
+
+
+def large_mixed(requests, max_live=4, tail=3, sizes=(300, 150, 260, 130, 340)):
+    """Up to ``max_live`` requests live; each gets all but its last ``tail`` tokens in portions
+    whose sizes cycle through ``sizes`` (hundreds of tokens), then the rest one by one: steps of
+    several hundred tokens with two or three long portions beside single tokens of others."""
+    waiting = list(requests.items())
+    live, steps, k = {}, [], 0
+    while waiting or live:
+        while waiting and len(live) < max_live:
+            rid, toks = waiting.pop(0)
+            live[rid] = [toks, 0, max(1, len(toks) - tail)]
+        entries, end = [], []
+        for rid, st in list(live.items()):
+            toks, fed, prompt = st
+            if fed < prompt:
+                n = min(prompt - fed, sizes[k % len(sizes)])
+                k += 1
+                if prompt - fed - n == 1:
+                    n += 1
+            else:
+                n = 1
+            entries.append({"id": rid, "tokens": toks[fed:fed + n], "want": list(range(n))})
+            st[1] = fed + n
+            if st[1] == len(toks):
+                end.append(rid)
+                del live[rid]
+        steps.append({"step": len(steps), "entries": entries, "end": end})
     return steps
 
 
@@ -149,6 +178,21 @@ def run_program(model_dir, dtype, steps, out_dir, max_tokens, vocab, extra=()):
                 k += 1
             fed[e["id"]] += len(e["tokens"])
     return out
+
+
+def chunks_of(requests, chunk, tail=3):
+    """Each request alone: its tokens but the last ``tail`` in chunks of ``chunk`` (the last one
+    ragged), then the rest one by one, as a scheduler with that chunk size would feed them."""
+    steps = []
+    for rid, toks in requests.items():
+        head = max(1, len(toks) - tail)
+        cuts = [(a, min(head, a + chunk)) for a in range(0, head, chunk)]
+        cuts += [(i, i + 1) for i in range(head, len(toks))]
+        for k, (a, b) in enumerate(cuts):
+            steps.append({"step": len(steps), "entries": [
+                {"id": rid, "tokens": toks[a:b], "want": list(range(b - a))}],
+                "end": [rid] if k == len(cuts) - 1 else []})
+    return steps
 
 
 def make_requests(vocab, lengths, seed):
