@@ -177,8 +177,9 @@ def test_cutting_does_not_change_logits_beyond_rounding(model_dirs, expected):
 #: The cuttings share every rounding point (norm output, q and k after the rotation, the cache,
 #: probabilities, attention output, activation, product outputs) but not their kernels, so they
 #: differ by a few bfloat16 roundings that fall the other way, never by a key that one of them
-#: masks and another does not (which moves a row by tens of percent).
-BF16_CUTTING_BOUND = {"C": 0.03, "D": 0.03}
+#: masks and another does not (which moves a row by tens of percent).  Worst seen: 0.0066 (C)
+#: and 0.0106 (D) of the row's largest logit; the bounds are about twice that.
+BF16_CUTTING_BOUND = {"C": 0.015, "D": 0.02}
 
 
 @pytest.mark.parametrize("name", ["C", "D"])
