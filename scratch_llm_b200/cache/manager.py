@@ -125,6 +125,20 @@ class CacheManager:
         total = -(-(rc.n_tokens + n_new) // self.page_size)
         return [max(0, total - len(t)) for t in rc.tables]
 
+    def max_pages_held(self, n_tokens: int, step_tokens: int = 1) -> list[int]:
+        """Per group, the most pages a request holds at any time on its way to ``n_tokens``
+        cached tokens when no step feeds it more than ``step_tokens``: all of them where every
+        key is kept; where a window of w keys is kept, the pages that the window and one step's
+        new tokens can touch (pages behind the window are given back at every commit)."""
+        ps = self.page_size
+        full = -(-n_tokens // ps)
+        out = []
+        for g in self.groups:
+            w = g.spec.window
+            out.append(full if w is None else
+                       min(full, -(-(w - 1 + max(1, step_tokens)) // ps) + 1))
+        return out
+
     def reserve(self, request_id: Hashable, n_new: int) -> bool:
         """Hold pages for the next ``n_new`` tokens in every group, or change nothing and
         return False if some group has too few free pages."""

@@ -31,7 +31,7 @@ import math
 from dataclasses import asdict, dataclass
 from typing import Any, Mapping
 
-from .spec import LayerSpec, ModelSpec, PartSpec, sequential_order
+from .spec import ModelSpec, PartSpec, sequential_order, standard_layer
 
 _UNSUPPORTED_TRUE = ("attention_bias", "mlp_bias")
 
@@ -141,9 +141,9 @@ class LlamaConfig:
                  "mixer_norm": "input_layernorm",
                  "feed_forward_norm": "post_attention_layernorm"}
         layers = tuple(
-            LayerSpec(prefix=f"model.layers.{i}", block="pre_norm", mixer=attention,
-                      feed_forward=swiglu, mixer_norm=norm, feed_forward_norm=norm,
-                      position=rotary, names=names)
+            standard_layer(f"model.layers.{i}", "pre_norm", mixer=attention,
+                           feed_forward=swiglu, mixer_norm=norm, feed_forward_norm=norm,
+                           position=rotary, names=names)
             for i in range(self.num_hidden_layers))
         return ModelSpec(
             hidden_size=self.hidden_size, vocab_size=self.vocab_size,

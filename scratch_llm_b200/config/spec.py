@@ -29,17 +29,28 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """What one layer is made of.  ``prefix`` is the tensor-name prefix of the layer's weights;
-    ``names`` gives the sub-prefix of each part below it."""
+    """What one layer is made of: ``block`` names the arrangement (a key of BLOCKS), ``parts``
+    gives a :class:`PartSpec` for every role that arrangement has.  Which roles there are, and
+    which registry each role's part comes from, is the block class's statement (its ``ROLES``):
+    a layer with other roles (no feed-forward, four norms) needs another block class and
+    nothing else.  ``prefix`` is the tensor-name prefix of the layer's weights; ``names`` gives
+    the sub-prefix of each role below it (default: the role's name)."""
 
     prefix: str
-    block: str  # arrangement of the parts, a key of BLOCKS ("pre_norm")
-    mixer: PartSpec
-    feed_forward: PartSpec
-    mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
-    position: PartSpec
+    block: str
+    parts: Mapping[str, PartSpec]
     names: Mapping[str, str] = field(default_factory=dict)
+
+
+def standard_layer(prefix: str, block: str, mixer: PartSpec, feed_forward: PartSpec,
+                   mixer_norm: PartSpec, feed_forward_norm: PartSpec, position: PartSpec,
+                   names: Mapping[str, str] | None = None) -> LayerSpec:
+    """A layer of the five roles that ``pre_norm`` (and any block of the same roles) arranges:
+    mixer, feed-forward, a norm before each, and the mixer's position encoding."""
+    return LayerSpec(prefix, block, {"mixer": mixer, "feed_forward": feed_forward,
+                                     "mixer_norm": mixer_norm,
+                                     "feed_forward_norm": feed_forward_norm,
+                                     "position": position}, dict(names or {}))
 
 
 @dataclass(frozen=True)

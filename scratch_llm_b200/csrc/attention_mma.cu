@@ -813,6 +813,27 @@ using namespace sllm;
 
 SLLM_EXPORT int sllm_attn_mma_head_dim() { return HD; }
 
+// CTAs of the split (decode) kernel that the current device holds at once: SMs x the CTAs of
+// that kernel resident on one SM (from the occupancy calculator).  0 on an error.
+SLLM_EXPORT int sllm_attn_mma_decode_slots() {
+    int dev = 0, sms = 0, per_sm = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+    const size_t smem = smem_bytes<true>();
+#if SLLM_HEAD_DIM % 64 == 0
+    if (cudaFuncSetAttribute(attn_decode_cs_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)smem) != cudaSuccess) return 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_decode_cs_kernel, THREADS,
+                                                      smem) != cudaSuccess) return 0;
+#else
+    if (cudaFuncSetAttribute(attn_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)smem) != cudaSuccess) return 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_mma_kernel<true>, THREADS,
+                                                      smem) != cudaSuccess) return 0;
+#endif
+    return sms * per_sm;
+}
+
 // Scratch floats the split kernel needs for `n_tokens` tokens in its listed rows.
 SLLM_EXPORT int64_t sllm_attn_mma_scratch_floats(int64_t n_tokens, int H, int n_splits) {
     return n_splits > 1 ? n_tokens * H * n_splits * (HD + 1) : 0;

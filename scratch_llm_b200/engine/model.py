@@ -25,6 +25,11 @@ def _spec_key(spec: PartSpec):
     return (spec.kind, tuple(sorted((k, repr(v)) for k, v in spec.args.items())))
 
 
+#: kind of part (a value of a block's ``ROLES``) -> (registry, name used in error messages)
+PART_KINDS = {"mixer": (MIXERS, "mixer"), "feed_forward": (FEED_FORWARDS, "feed-forward"),
+              "norm": (NORMS, "norm"), "position": (POSITION_ENCODINGS, "position encoding")}
+
+
 class DecoderModel:
     def __init__(self, spec: ModelSpec) -> None:
         self.spec = spec
@@ -33,27 +38,54 @@ class DecoderModel:
         self.blocks = []
         self._named_parts: list[tuple[str, object]] = []
         for layer in spec.layers:
-            key = _spec_key(layer.position)
-            if key not in positions:  # one table serves every layer that asks for the same
-                positions[key] = make(POSITION_ENCODINGS, "position encoding", layer.position)
-            mixer = make(MIXERS, "mixer", layer.mixer)
-            ff = make(FEED_FORWARDS, "feed-forward", layer.feed_forward)
-            n1 = make(NORMS, "norm", layer.mixer_norm)
-            n2 = make(NORMS, "norm", layer.feed_forward_norm)
             try:
                 block_cls = BLOCKS[layer.block]
             except KeyError:
                 raise ValueError(f"unknown block {layer.block!r}; registered: "
                                  f"{', '.join(sorted(BLOCKS))}") from None
-            self.blocks.append(block_cls(mixer, ff, n1, n2, positions[key]))
-            for role, part in (("mixer", mixer), ("feed_forward", ff), ("mixer_norm", n1),
-                               ("feed_forward_norm", n2)):
-                self._named_parts.append((f"{layer.prefix}.{layer.names.get(role, role)}", part))
+            roles = dict(getattr(block_cls, "ROLES", {}))
+            if set(roles) != set(layer.parts):
+                raise ValueError(f"layer {layer.prefix!r}: block {layer.block!r} has the roles "
+                                 f"{sorted(roles)}, the layer's spec gives {sorted(layer.parts)}")
+            if sum(kind == "mixer" for kind in roles.values()) > 1:
+                raise ValueError(f"block {layer.block!r} has several mixers: a layer has one "
+                                 "cache entry, which one mixer owns")
+            built = {}
+            for role, kind in roles.items():
+                part_spec = layer.parts[role]
+                if kind not in PART_KINDS:
+                    raise ValueError(f"block {layer.block!r}: role {role!r} has the unknown kind "
+                                     f"{kind!r} (kinds: {', '.join(PART_KINDS)})")
+                table, what = PART_KINDS[kind]
+                if kind == "position":   # one table serves every layer that asks for the same
+                    key = _spec_key(part_spec)
+                    if key not in positions:
+                        positions[key] = make(table, what, part_spec)
+                    built[role] = positions[key]
+                else:
+                    built[role] = make(table, what, part_spec)
+                    self._named_parts.append(
+                        (f"{layer.prefix}.{layer.names.get(role, role)}", built[role]))
+            block = block_cls(**built)
+            block.parts = built          # role -> part, for whoever walks the model's parts
+            block.cache_owner = next((built[r] for r, k in roles.items() if k == "mixer"), None)
+            self.blocks.append(block)
         self._positions = list(positions.values())
         self.final_norm = make(NORMS, "norm", spec.final_norm)
         self._named_parts.append((spec.final_norm_name, self.final_norm))
         self.embedding: torch.Tensor | None = None
         self.lm_head: Linear | None = None
+
+    def all_parts(self):
+        """Every part of the model and every block, once (a position encoding that several
+        layers share comes once)."""
+        seen: dict[int, object] = {}
+        for block in self.blocks:
+            seen.setdefault(id(block), block)
+            for part in block.parts.values():
+                seen.setdefault(id(part), part)
+        seen.setdefault(id(self.final_norm), self.final_norm)
+        return list(seen.values())
 
     # --------------------------------------------------------------------------- weights
 
@@ -92,12 +124,14 @@ class DecoderModel:
         st: list[StateSpec | None] = [None] * n
         for run in self.spec.order:
             if run.write:
-                mixer = self.blocks[run.layer].mixer
-                kv[run.cache], st[run.cache] = mixer.kv_spec(), mixer.state_spec()
+                mixer = self.blocks[run.layer].cache_owner
+                if mixer is not None:
+                    kv[run.cache], st[run.cache] = mixer.kv_spec(), mixer.state_spec()
         return kv, st
 
     def head_dims(self) -> list[int]:
-        return sorted({b.mixer.head_dim for b in self.blocks if hasattr(b.mixer, "head_dim")})
+        return sorted({p.head_dim for p in self.all_parts()
+                       if isinstance(getattr(p, "head_dim", None), int)})
 
     # --------------------------------------------------------------------------- forward
 

@@ -68,7 +68,7 @@ class ModelRunner:
     arrays, the block tables (at their full width) and the pools keep their addresses, the
     kernels read contexts and pages on the device.  Other steps of up to PAD_MAX_TOKENS tokens
     (portions of prompts, alone or beside decoded tokens) are padded to a few sizes
-    (engine/batch.py::pad_plan) and captured per padded shape, if every mixer and feed-forward
+    (engine/batch.py::pad_plan) and captured per padded shape, if every part of the model
     is ``pad_safe``: launched plainly, such a step costs the host more than the device.
     ``poison_free_pages``: a debugging aid of the cache manager (free pages hold NaN)."""
 
@@ -85,12 +85,12 @@ class ModelRunner:
         self._stager = BatchStager(self.device)
         self.vocab_size = model.spec.vocab_size
         self.max_position = model.spec.max_position
+        # every part of every layer has a say (mixers, feed-forwards, norms, position
+        # encodings, the blocks themselves, the final norm), with the same defaults
         self.cuda_graphs = cuda_graphs and all(
-            getattr(part, "capturable", True) for block in model.blocks
-            for part in (block.mixer, block.feed_forward))
+            getattr(part, "capturable", True) for part in model.all_parts())
         self.pad_small_steps = self.cuda_graphs and all(
-            getattr(part, "pad_safe", False) for block in model.blocks
-            for part in (block.mixer, block.feed_forward))
+            getattr(part, "pad_safe", False) for part in model.all_parts())
         self._table_width = self.cache.max_pages_per_request(self.max_position)
         self._captured: dict[tuple, _CapturedStep] = {}
         self._graph_pool = None     # memory shared by the captured steps (they never overlap)

@@ -125,8 +125,13 @@ class Scheduler:
 
     # ---------------------------------------------------------------------------- submit
 
-    def _pool_pages(self) -> int:
-        return min(g.pool.n_pages for g in self.cache.groups) if self.cache.groups else 1 << 60
+    def _pool_pages(self) -> list[int]:
+        return [g.pool.n_pages for g in self.cache.groups]
+
+    def _pages_by_last_token(self, n_prompt: int, max_tokens: int, step_tokens: int) -> list[int]:
+        """Per cache group, the most pages a request holds on its way to its last token (the
+        cache manager knows which groups keep every key and which a window of them)."""
+        return self.cache.max_pages_held(n_prompt + max_tokens - 1, step_tokens)
 
     def submit(self, request: Request) -> None:
         prompt = list(request.prompt_ids)
@@ -140,11 +145,12 @@ class Scheduler:
         if len(prompt) + p.max_tokens > self.max_position:
             raise ValueError(f"prompt ({len(prompt)}) + max_tokens ({p.max_tokens}) exceeds "
                              f"max_position {self.max_position}")
-        need = -(-(len(prompt) + p.max_tokens - 1) // self.cache.page_size)
-        if need > self._pool_pages():
+        # (fed one token per step if need be: portions are cut to the pages that are free)
+        need = self._pages_by_last_token(len(prompt), p.max_tokens, 1)
+        if any(n > have for n, have in zip(need, self._pool_pages())):
             raise ValueError(f"request {request.request_id!r} needs {need} pages by its last "
-                             f"token but the pool has {self._pool_pages()}: it could never "
-                             "finish")
+                             f"token but the pool has {self._pool_pages()} (per cache group): "
+                             "it could never finish")
         self._known.add(request.request_id)
         self.queue.append(Sequence_(request, prompt, len(prompt)))
 
@@ -177,9 +183,17 @@ class Scheduler:
             return m
         return 0
 
-    def _committed_pages(self) -> int:
-        ps = self.cache.page_size
-        return sum(-(-(s.n_prompt + s.request.params.max_tokens - 1) // ps) for s in self.running)
+    def _step_cap(self) -> int:
+        return min(self.max_batch_tokens, self.chunk_size or self.max_batch_tokens)
+
+    def _committed_pages(self) -> list[int]:
+        """Per group, what the live requests may come to hold by their last tokens."""
+        total = [0] * len(self.cache.groups)
+        for s in self.running:
+            need = self._pages_by_last_token(s.n_prompt, s.request.params.max_tokens,
+                                             self._step_cap())
+            total = [a + b for a, b in zip(total, need)]
+        return total
 
     def plan(self) -> list[PlannedRow]:
         """Decide the next step's batch.  Reserves the pages its rows need."""
@@ -235,9 +249,10 @@ class Scheduler:
         while self.queue and budget >= 1 and self.cache.n_free_slots > 0:
             seq = self.queue[0]
             if self.admission == "reserve_full":
-                ps = self.cache.page_size
-                need = -(-(seq.n_prompt + seq.request.params.max_tokens - 1) // ps)
-                if self._committed_pages() + need > self._pool_pages():
+                need = self._pages_by_last_token(seq.n_prompt, seq.request.params.max_tokens,
+                                                 self._step_cap())
+                if any(c + n > have for c, n, have in
+                       zip(self._committed_pages(), need, self._pool_pages())):
                     break
             n = min(len(seq.tokens), budget, self.chunk_size or len(seq.tokens))
             rid = seq.request.request_id

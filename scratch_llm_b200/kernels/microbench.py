@@ -167,7 +167,8 @@ def bench_attn_decode(args) -> list[dict]:
         o = torch.empty_like(q)
         row_start = torch.arange(b + 1, dtype=torch.int32, device="cuda")
         pos0 = torch.full((b,), ctx - 1, dtype=torch.int32, device="cuda")
-        n_splits = decode_splits(b * G * (-(-(H // G) // 16)), ctx)
+        n_splits = decode_splits(b * G * (-(-(H // G) // 16)), ctx,
+                                 ops.attention_decode_slots(hd))
         scratch = torch.empty(max(1, ops.attention_mma_scratch_floats(b, H, hd, n_splits)),
                               dtype=torch.float32, device="cuda")
 

@@ -467,6 +467,21 @@ def attention_mma(q: torch.Tensor, pages: torch.Tensor, block_table: torch.Tenso
     return out
 
 
+_decode_slots: dict[tuple[int, int], int] = {}
+
+
+def attention_decode_slots(head_dim: int) -> int:
+    """CTAs of the split decode attention kernel that the current device holds at once (SMs x
+    resident CTAs per SM, asked of the occupancy calculator once per device and head size)."""
+    key = (torch.cuda.current_device(), head_dim)
+    if key not in _decode_slots:
+        n = int(_load(*attention_mma_library(head_dim)).sllm_attn_mma_decode_slots())
+        if n <= 0:
+            raise KernelError("the occupancy of the decode attention kernel could not be read")
+        _decode_slots[key] = n
+    return _decode_slots[key]
+
+
 def attention_decode_fused_supported(head_dim: int) -> bool:
     """Whether this head size has the decode attention kernel that rotates q and the new key and
     stores the new key and value itself (head sizes that are multiples of 64)."""

@@ -26,11 +26,12 @@ from .registry import register_mixer
 TC_MIN_PACKED_QUERIES = 128
 
 
-def decode_splits(base_ctas: int, context: int, slots: int = 3 * 148) -> int:
+def decode_splits(base_ctas: int, context: int, slots: int) -> int:
     """How many CTAs share the keys of one (row, kv head) in the split decode kernel: the count
     that minimises waves x (key tiles per CTA + fixed cost), a function of the batch's shape
     and of the context bucket alone, so that it is the same for every step that replays one
-    captured graph.  ``slots``: CTAs of the split kernel resident on the GPU at once."""
+    captured graph.  ``slots``: CTAs of the split kernel resident on the GPU at once
+    (:func:`scratch_llm_b200.kernels.ops.attention_decode_slots` reads it from the device)."""
     tiles = max(1, -(-context // 64))
     best, best_cost = 1, None
     for n in range(1, min(64, tiles) + 1):
@@ -113,7 +114,8 @@ class GQAttention(Mixer):
         H, G = self.n_heads, self.n_kv_heads
         return decode_splits(batch.n_single * G * (-(-(H // G) // 16)),
                              batch.context_bucket if self.window is None
-                             else min(batch.context_bucket, self.window + 64))
+                             else min(batch.context_bucket, self.window + 64),
+                             ops.attention_decode_slots(self.head_dim))
 
     def _decode_fused(self, qkv, out, batch, cache: CacheView, rope) -> None:
         H, G, hd = self.n_heads, self.n_kv_heads, self.head_dim

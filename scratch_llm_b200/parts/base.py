@@ -18,7 +18,9 @@ Mixer              ``forward(x, batch, cache, write, position) -> [N, hidden]``;
                    (fixed-size state per request)
 FeedForward        ``forward(x) -> [N, hidden]``
 Block              ``forward(resid, pending, batch, cache, write) -> pending``: the arrangement
-                   of the four parts around the residual stream
+                   of a layer's parts around the residual stream; its ``ROLES`` says which
+                   parts it has (role -> kind of part), and it is built with one keyword
+                   argument per role
 =================  ==========================================================================
 """
 
@@ -120,4 +122,20 @@ class Mixer(Part):
 
 class FeedForward(Part):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Block:
+    """An arrangement of a layer's parts.  ``ROLES`` maps each role the arrangement has onto
+    the kind of part that fills it: ``"mixer"``, ``"feed_forward"``, ``"norm"`` or
+    ``"position"`` (the registry the part's spec is looked up in).  The model builds the parts
+    from the layer's specs and constructs the block with one keyword argument per role.  At most
+    one role may be a mixer: it owns the layer's cache entry."""
+
+    ROLES: dict[str, str] = {}
+    capturable = True
+    pad_safe = False
+
+    def forward(self, resid: torch.Tensor, pending: torch.Tensor | None, batch: "StepBatch",
+                cache: CacheView, write: bool) -> torch.Tensor:
         raise NotImplementedError

@@ -11,12 +11,16 @@ from __future__ import annotations
 
 import torch
 
-from .base import CacheView, FeedForward, Mixer, Norm, PositionEncoding
+from .base import Block, CacheView, FeedForward, Mixer, Norm, PositionEncoding
 from .registry import register_block
 
 
 @register_block("pre_norm")
-class PreNormBlock:
+class PreNormBlock(Block):
+    ROLES = {"mixer": "mixer", "feed_forward": "feed_forward", "mixer_norm": "norm",
+             "feed_forward_norm": "norm", "position": "position"}
+    pad_safe = True   # the arrangement itself touches no token: its parts decide
+
     def __init__(self, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm,
                  feed_forward_norm: Norm, position: PositionEncoding) -> None:
         self.mixer, self.feed_forward = mixer, feed_forward

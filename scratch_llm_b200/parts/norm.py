@@ -19,6 +19,8 @@ from .registry import register_norm
 
 @register_norm("rmsnorm")
 class RMSNorm(Norm):
+    pad_safe = True   # every token by itself
+
     def __init__(self, size: int, eps: float) -> None:
         self.size, self.eps = size, float(eps)
         self.weight: torch.Tensor | None = None

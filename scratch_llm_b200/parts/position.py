@@ -23,6 +23,7 @@ from .registry import register_position_encoding
 @register_position_encoding("rotary")
 class Rotary(PositionEncoding):
     rotary_tables = True
+    pad_safe = True   # a table lookup per token; padding tokens have position 0
 
     def __init__(self, head_dim: int, theta: float, max_position: int,
                  interleaved: bool = True) -> None:
@@ -51,6 +52,8 @@ class Rotary(PositionEncoding):
 
 @register_position_encoding("none")
 class NoPosition(PositionEncoding):
+    pad_safe = True
+
     def __init__(self, **_: object) -> None:
         pass
 

@@ -22,8 +22,8 @@ def test_config_reads_its_keys():
     assert cfg.tie_word_embeddings and cfg.max_position_embeddings == 256
     spec = cfg.model_spec()
     assert len(spec.layers) == 3 and [r.layer for r in spec.order] == [0, 1, 2]
-    assert spec.layers[1].mixer.args["n_kv_heads"] == 1
-    assert spec.layers[1].mixer_norm.args["eps"] == 1e-6
+    assert spec.layers[1].parts["mixer"].args["n_kv_heads"] == 1
+    assert spec.layers[1].parts["mixer_norm"].args["eps"] == 1e-6
     assert config_from_dict(cfg.to_dict()) == cfg
 
 
@@ -83,9 +83,15 @@ def test_unknown_part_names_the_registered_ones():
     spec = cfg.model_spec()
     import dataclasses
     from scratch_llm_b200.engine.model import DecoderModel
-    bad = dataclasses.replace(spec.layers[0], mixer=PartSpec("no_such_mixer"))
+    first = spec.layers[0]
+    bad = dataclasses.replace(first, parts={**first.parts, "mixer": PartSpec("no_such_mixer")})
     with pytest.raises(ValueError, match="unknown mixer 'no_such_mixer'.*gqa_attention"):
         DecoderModel(dataclasses.replace(spec, layers=(bad, spec.layers[1])))
+    # a layer must give exactly the roles its block arrangement has
+    short = dataclasses.replace(first, parts={k: v for k, v in first.parts.items()
+                                              if k != "feed_forward_norm"})
+    with pytest.raises(ValueError, match="has the roles.*feed_forward_norm"):
+        DecoderModel(dataclasses.replace(spec, layers=(short, spec.layers[1])))
 
 
 def test_safetensors_roundtrip(tmp_path):

@@ -167,7 +167,7 @@ def make_toy():
     Its state per request is (sum of inputs, count): fixed size, carried from step to step in
     the cache manager's state slots."""
     from scratch_llm_b200.config import LlamaConfig, register_architecture, ARCHITECTURES
-    from scratch_llm_b200.config.spec import LayerSpec, ModelSpec, PartSpec, Run
+    from scratch_llm_b200.config.spec import ModelSpec, PartSpec, Run, standard_layer as LayerSpec
     from scratch_llm_b200.parts import MIXERS, Mixer, StateSpec, register_mixer
     from scratch_llm_b200.weights import ParamSpec
 
@@ -295,7 +295,7 @@ def make_toy_routed():
     is not rotary: it adds alpha * sin(position * 2^-j) to component j of every query and key
     head.  A model with one layer of each beside a standard layer."""
     from scratch_llm_b200.config import register_architecture, ARCHITECTURES
-    from scratch_llm_b200.config.spec import LayerSpec, ModelSpec, PartSpec, sequential_order
+    from scratch_llm_b200.config.spec import ModelSpec, PartSpec, sequential_order, standard_layer as LayerSpec
     from scratch_llm_b200.parts import (FEED_FORWARDS, POSITION_ENCODINGS, FeedForward,
                                         PositionEncoding, register_feed_forward,
                                         register_position_encoding)
@@ -447,8 +447,9 @@ def make_toy_parallel():
     feed-forward side by side, x + Mixer(Norm(x)) + FeedForward(Norm(x)).  A model with such
     a layer before a standard one, and the toy norm before the output matrix."""
     from scratch_llm_b200.config import register_architecture, ARCHITECTURES
-    from scratch_llm_b200.config.spec import LayerSpec, ModelSpec, PartSpec, sequential_order
-    from scratch_llm_b200.parts import BLOCKS, NORMS, Norm, register_block, register_norm
+    from scratch_llm_b200.config.spec import ModelSpec, PartSpec, sequential_order, standard_layer as LayerSpec
+    from scratch_llm_b200.config.spec import LayerSpec as RolesLayerSpec
+    from scratch_llm_b200.parts import BLOCKS, NORMS, Block, Norm, register_block, register_norm
     from scratch_llm_b200.weights import ParamSpec
 
     if "centred_norm" not in NORMS:
@@ -479,10 +480,15 @@ def make_toy_parallel():
 
     if "parallel" not in BLOCKS:
         @register_block("parallel")
-        class ParallelBlock:
-            def __init__(self, mixer, feed_forward, mixer_norm, feed_forward_norm, position):
+        class ParallelBlock(Block):
+            # other roles than the standard arrangement's: ONE norm feeds both branches
+            ROLES = {"mixer": "mixer", "feed_forward": "feed_forward", "norm": "norm",
+                     "position": "position"}
+            pad_safe = True
+
+            def __init__(self, mixer, feed_forward, norm, position):
                 self.mixer, self.feed_forward = mixer, feed_forward
-                self.norm, self.position = mixer_norm, position     # the second norm is not used
+                self.norm, self.position = norm, position
 
             def forward(self, resid, pending, batch, cache, write):
                 h = self.norm.forward(resid, pending)
@@ -514,7 +520,10 @@ def make_toy_parallel():
                 rope = PartSpec("rotary", {"head_dim": 16, "theta": 1000.0, "max_position": 128})
                 names = {"mixer": "mixer", "feed_forward": "ff", "mixer_norm": "n1",
                          "feed_forward_norm": "n2"}
-                layers = (LayerSpec("l0", "parallel", att, ff, centred, centred, rope, names),
+                layers = (RolesLayerSpec("l0", "parallel",
+                                         {"mixer": att, "feed_forward": ff, "norm": centred,
+                                          "position": rope},
+                                         {"feed_forward": "ff", "norm": "n1"}),
                           LayerSpec("l1", "pre_norm", att, ff, rms, rms, rope, names))
                 return ModelSpec(d, self.n_vocab, 128, layers, sequential_order(2), centred,
                                  "emb.weight", "out_norm", "head.weight", tie_embeddings=False)
@@ -583,7 +592,7 @@ def make_toy_windowed():
     last 12 keys only while the second attends to all of them: two groups of cache entries with
     pages of their own, and pages of the windowed group go back while a request is live."""
     from scratch_llm_b200.config import register_architecture, ARCHITECTURES
-    from scratch_llm_b200.config.spec import LayerSpec, ModelSpec, PartSpec, sequential_order
+    from scratch_llm_b200.config.spec import ModelSpec, PartSpec, sequential_order, standard_layer as LayerSpec
 
     if "ToyWindowedForCausalLM" not in ARCHITECTURES:
         @dataclass(frozen=True)

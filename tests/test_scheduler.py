@@ -354,3 +354,37 @@ def test_wave_policy_admits_only_into_an_empty_engine():
     assert results["wave"] == results["continuous"]
     assert all(results["wave"][i] == oracle([i + 1] * (5 + i), greedy(2 + 3 * (i % 3)))
                for i in range(7))
+
+
+def test_a_windowed_cache_needs_only_the_window(tmp_path):
+    """A model whose cache groups all keep a window of keys: a request far longer than the pool
+    is taken, because pages behind the window come back at every step; the same request is
+    refused where every key is kept.  The reserve-full guard counts the window too."""
+    page, window = 4, 10
+    def build(win, n_pages, **kw):
+        cache = CacheManager([KVSpec(1, 16, win)], [None], page, n_pages, 4)
+        return Scheduler(cache, 1000, vocab_size=VOCAB, **kw), cache
+
+    long_req = Request("long", list(range(60)), greedy(40))          # 99 cached tokens = 25 pages
+    sched, cache = build(None, 8)
+    with pytest.raises(ValueError, match="could never"):
+        sched.submit(long_req)
+    # window 10, one token per step: ceil(10 / 4) + 1 = 4 pages suffice
+    assert cache.max_pages_held(99, 1) == [25]
+    sched, cache = build(window, 4, max_batch_tokens=8)
+    assert cache.max_pages_held(99, 1) == [4]
+    sched.submit(long_req)
+    run(sched, cache)
+    assert sched.finished["long"].generated == oracle(long_req.prompt_ids, long_req.params)
+    # reserve-full admission: two such requests fit a pool of 12 pages side by side (steps of up
+    # to 8 tokens: ceil(17 / 4) + 1 = 6 pages each), which 2 x 25 pages never would
+    sched, cache = build(window, 12, max_batch_tokens=8, admission="reserve_full")
+    reqs = [Request(i, [(7 * i + j) % VOCAB for j in range(50)], greedy(30)) for i in range(2)]
+    for r in reqs:
+        sched.submit(r)
+    log = []
+    run(sched, cache, log)
+    assert any(len({rid for rid, *_ in step}) == 2 for step in log)   # they ran side by side
+    assert sched.stats.preemptions == 0
+    for r in reqs:
+        assert sched.finished[r.request_id].generated == oracle(r.prompt_ids, r.params)
