@@ -529,6 +529,364 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     }
 }
 
+// ------------------------------------------------------------------------------------------
+// Two query tiles per CTA (head sizes up to 128).  The kernel above leaves the tensor pipe idle
+// three quarters of the time: its four softmax warps are one warp per scheduler, each a chain of
+// dependent instructions.  Here a CTA owns 256 packed queries, tile A and tile B, which share
+// every key/value tile in shared memory (half the traffic per query) and have a softmax
+// warpgroup each (warps 2-5 and 6-9), so that two independent chains run per scheduler.
+//   tensor memory: S/P of A at columns 0..127, S/P of B at 128..255, O of A at 256.., O of B
+//   at 256 + HD.. (exactly the 512 columns at head size 128).
+//   tensor pipe order: QK_A(0) QK_B(0) | PV_A(t) QK_A(t+1) PV_B(t) QK_B(t+1) | ...: while the
+//   softmax of B(t) runs, the pipe does PV_A(t) and QK_A(t+1), and the other way round.  A
+//   tile's S(t+1) takes the place of its P(t): the products of one thread execute in order, so
+//   QK_X(t+1), issued after PV_X(t), cannot overtake it.
+// Tile A holds the earlier queries, so it needs at most as many key tiles as B; a tile that
+// lies beyond the row's queries takes no part.
+#if SLLM_HEAD_DIM <= 128
+constexpr int KV_STAGES2 = HD <= 64 ? 4 : 2;
+constexpr int ATC2_THREADS = 320;
+constexpr size_t ATC2_SMEM = (size_t)2 * Q_BYTES + (size_t)KV_STAGES2 * 2 * KV_BYTES + 1024 + 256;
+
+__global__ void __launch_bounds__(ATC2_THREADS, 1)
+attn_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
+                const AtcArgs a) {
+    extern __shared__ unsigned char atc_smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>(
+        ((uintptr_t)atc_smem_raw + 1023) & ~(uintptr_t)1023);
+    unsigned char* q_s = smem;                               // tile A, then tile B
+    unsigned char* kv_s = smem + 2 * Q_BYTES;                // stage s: K at s*2*KV_BYTES, V after
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 2 * Q_BYTES +
+                                                 (size_t)KV_STAGES2 * 2 * KV_BYTES);
+    uint64_t* q_full = bars;
+    uint64_t* kv_full = bars + 1;                            // [KV_STAGES2]
+    uint64_t* kv_empty = kv_full + KV_STAGES2;               // [KV_STAGES2]
+    uint64_t* s_full = kv_empty + KV_STAGES2;                // [2], one per query tile
+    uint64_t* p_full = s_full + 2;                           // [2]
+    uint64_t* pv_done = p_full + 2;                          // [2]
+    uint64_t* o_done = pv_done + 2;                          // the last P V of both tiles is over
+    uint64_t* v_clean = o_done + 1;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(v_clean + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r = a.row_list ? a.row_list[blockIdx.y] : blockIdx.y;
+    const int g = blockIdx.z;
+    const int GS = a.H / a.G;
+    const int t0 = a.row_start[r];
+    const int n_new = a.row_start[r + 1] - t0;
+    const int pos0 = a.row_pos0[r];
+    const int n_packed = n_new * GS;
+    // heavy (late) query tiles first
+    const int pair = (int)gridDim.x - 1 - (int)blockIdx.x;
+    const int q0 = pair * 2 * TQ;
+    if (q0 >= n_packed) return;
+    // per tile: does it exist, its last position, its key tiles
+    int n_tiles_x[2], last_pos_x[2];
+#pragma unroll
+    for (int x = 0; x < 2; ++x) {
+        const int qx = q0 + x * TQ;
+        const bool there = qx < n_packed;
+        last_pos_x[x] = there ? pos0 + min(n_packed - 1, qx + TQ - 1) / GS : -1;
+        n_tiles_x[x] = there ? last_pos_x[x] / TKV + 1 : 0;
+    }
+    const int n_tiles = max(n_tiles_x[0], n_tiles_x[1]);
+    const int last_pos = max(last_pos_x[0], last_pos_x[1]);
+
+    if (threadIdx.x == 0) {
+        atc_init(q_full, 1);
+        for (int s = 0; s < KV_STAGES2; ++s) {
+            atc_init(&kv_full[s], 1);
+            atc_init(&kv_empty[s], 1);
+        }
+        for (int x = 0; x < 2; ++x) {
+            atc_init(&s_full[x], 1);
+            atc_init(&p_full[x], 4);
+            atc_init(&pv_done[x], 1);
+        }
+        atc_init(o_done, 1);
+        atc_init(v_clean, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
+                     ::"r"(atc_u32(tmem_slot)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    atc_fence_before();
+    __syncthreads();
+    atc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0) {
+        // producer, as in the kernel above: lane 0 owns the barriers, every lane copies pages
+        if (lane == 0) {
+            atc_expect_tx(q_full, 2 * Q_BYTES);
+            for (int x = 0; x < 2; ++x)
+                for (int c = 0; c < NCB; ++c)
+                    atc_tma_3d(q_s + x * Q_BYTES + c * SUB_BYTES, &map_q, q_full, c * 64, g * GS,
+                               t0 + (q0 + x * TQ) / GS);
+        }
+        const int pages_per_tile = TKV / a.page_size;
+        const int64_t rows_per_page = (int64_t)2 * a.G * a.page_size;
+        const int* table = a.block_table + (int64_t)r * a.table_stride;
+        const int n_pages_held = last_pos / a.page_size + 1;
+        const int spare = table[0];   // stands in for pages the row does not hold (masked keys)
+        bool cleaned = false;
+        for (int t = 0; t < n_tiles; ++t) {
+            const int s = t % KV_STAGES2;
+            int my_page[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = lane + 32 * u, lp = t * pages_per_tile + i;
+                my_page[u] = (i < pages_per_tile && lp < n_pages_held) ? table[lp] : spare;
+                if (my_page[u] < 0) my_page[u] = spare;
+            }
+            int ok = 1;
+            if (lane == 0) {
+                ok = atc_wait(&kv_empty[s], ((t / KV_STAGES2) & 1) ^ 1, 1) ? 1 : 0;
+                if (ok) atc_expect_tx(&kv_full[s], 2 * KV_BYTES);
+            }
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) break;
+            unsigned char* k_dst = kv_s + (size_t)s * 2 * KV_BYTES;
+            unsigned char* v_dst = k_dst + KV_BYTES;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = lane + 32 * u;
+                if (i >= pages_per_tile) break;
+                const int64_t row_k = (int64_t)my_page[u] * rows_per_page + (int64_t)g * a.page_size;
+                const int64_t row_v = row_k + (int64_t)a.G * a.page_size;
+                for (int c = 0; c < NCB; ++c) {
+                    atc_tma_2d(k_dst + c * SUB_BYTES + i * a.page_size * 128, &map_kv, &kv_full[s],
+                               c * 64, (int)row_k);
+                    atc_tma_2d(v_dst + c * SUB_BYTES + i * a.page_size * 128, &map_kv, &kv_full[s],
+                               c * 64, (int)row_v);
+                }
+            }
+            if (t == n_tiles - 1) {
+                // stale rows of V beyond the CTA's last position are zeroed (see the kernel above)
+                if (atc_wait(&kv_full[s], (t / KV_STAGES2) & 1, 9)) {
+                    const int first_stale = last_pos - t * TKV + 1;
+                    const int n16 = (TKV - first_stale) * 8;
+                    for (int c = 0; c < NCB; ++c) {
+                        uint4* base = reinterpret_cast<uint4*>(v_dst + c * SUB_BYTES +
+                                                               first_stale * 128);
+                        for (int i = lane; i < n16; i += 32) base[i] = make_uint4(0u, 0u, 0u, 0u);
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                }
+                __syncwarp();
+                if (lane == 0) atc_arrive(v_clean);
+                cleaned = true;
+            }
+        }
+        if (!cleaned && lane == 0) atc_arrive(v_clean);
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) |
+                                      ((uint32_t)(TKV >> 3) << 17) | ((uint32_t)(TQ >> 4) << 24);
+            const uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) |
+                                      ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(TQ >> 4) << 24);
+            bool ok = atc_wait(q_full, 0, 2);
+            // S_x(t) = Q_x K(t)^T (the stage's keys must have landed: the caller has waited)
+            auto issue_qk = [&](int x, int t) {
+                const int s = t % KV_STAGES2;
+                const uint32_t k_addr = atc_u32(kv_s + (size_t)s * 2 * KV_BYTES);
+                const uint32_t q_addr = atc_u32(q_s + x * Q_BYTES);
+#pragma unroll
+                for (int kk = 0; kk < HD / 16; ++kk) {
+                    const uint64_t dq = atc_desc(q_addr + (kk / 4) * SUB_BYTES, 16, 1024) + 2 * (kk % 4);
+                    const uint64_t dk = atc_desc(k_addr + (kk / 4) * SUB_BYTES, 16, 1024) + 2 * (kk % 4);
+                    atc_mma_ss(tmem + SP_COLS * x, dq, dk, idesc_qk, kk > 0);
+                }
+                atc_commit(&s_full[x]);
+            };
+            // O_x += P_x(t) V(t)
+            auto issue_pv = [&](int x, int t) {
+                const int s = t % KV_STAGES2;
+                const uint32_t v_addr = atc_u32(kv_s + (size_t)s * 2 * KV_BYTES) + KV_BYTES;
+#pragma unroll
+                for (int kk = 0; kk < TKV / 16; ++kk) {
+                    const uint64_t dv = atc_desc(v_addr + kk * 2048, SUB_BYTES, 1024);
+                    atc_mma_ts(tmem + O_COL + HD * x, tmem + SP_COLS * x + kk * 8, dv, idesc_pv,
+                               (t | kk) != 0);
+                }
+                atc_commit(&pv_done[x]);
+            };
+            if (ok) ok = atc_wait(&kv_full[0], 0, 3);
+            if (ok) {
+                atc_fence_after();
+                for (int x = 0; x < 2; ++x)
+                    if (n_tiles_x[x] > 0) issue_qk(x, 0);
+            }
+            for (int t = 0; t < n_tiles && ok; ++t) {
+                const int s = t % KV_STAGES2;
+                bool next_ready = false;
+                for (int x = 0; x < 2 && ok; ++x) {
+                    if (t >= n_tiles_x[x]) continue;
+                    ok = atc_wait(&p_full[x], t & 1, 4);
+                    if (!ok) break;
+                    if (t == n_tiles - 1) {   // the producer has zeroed the stale rows of V
+                        ok = atc_wait(v_clean, 0, 10);
+                        if (!ok) break;
+                    }
+                    atc_fence_after();
+                    issue_pv(x, t);
+                    if (t + 1 < n_tiles_x[x]) {
+                        if (!next_ready) {
+                            ok = atc_wait(&kv_full[(t + 1) % KV_STAGES2], ((t + 1) / KV_STAGES2) & 1, 3);
+                            if (!ok) break;
+                            atc_fence_after();
+                            next_ready = true;
+                        }
+                        issue_qk(x, t + 1);
+                    }
+                }
+                if (!ok) break;
+                // every product that reads this stage's keys and values has been issued
+                atc_commit(&kv_empty[s]);
+            }
+            if (ok) atc_commit(o_done);
+        }
+    } else {
+        const int x = warp >= 6 ? 1 : 0;                     // this warpgroup's query tile
+        const int quad = warp & 3;
+        const int row = quad * 32 + lane;
+        const uint32_t lane_base = tmem + ((uint32_t)(quad * 32) << 16);
+        const uint32_t sp_col = SP_COLS * x, o_col = O_COL + HD * x;
+        const int p = q0 + x * TQ + row;
+        const bool valid = p < n_packed;
+        const int tok = valid ? p / GS : 0, j = valid ? p - tok * GS : 0;
+        const int qpos = pos0 + tok;
+        const int my_tiles = n_tiles_x[x];
+        float m_ref = -INFINITY, l_sum = 0.f;
+        bool ok = true;
+        for (int t = 0; t < my_tiles; ++t) {
+            ok = atc_wait(&s_full[x], t & 1, 5);
+            if (!ok) break;
+            atc_fence_after();
+            const int kt = t * TKV;
+            const bool masked = !valid || kt + TKV - 1 > qpos;
+            // pass 1: the row's maximum over the tile, 64 scores at a time (the scores are read
+            // from tensor memory again in pass 2: that is cheaper than keeping 128 registers)
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                float sv[2][32];
+#pragma unroll
+                for (int c = 0; c < 2; ++c)
+                    atc_ld32_nowait(lane_base + sp_col + (2 * h + c) * 32, sv[c]);
+                atc_ld_wait();
+                if (masked) {
+#pragma unroll
+                    for (int c = 0; c < 2; ++c)
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (!valid || kt + (2 * h + c) * 32 + i > qpos) sv[c][i] = -INFINITY;
+                }
+#pragma unroll
+                for (int c = 0; c < 2; ++c)
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2)
+                        mx4[(i >> 1) & 3] = atc_max3(mx4[(i >> 1) & 3], sv[c][i], sv[c][i + 1]);
+            }
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * a.scale_log2;
+            float corr = 1.f;
+            if (mx > m_ref + RESCALE_THRESHOLD || (m_ref == -INFINITY && mx != -INFINITY)) {
+                corr = m_ref == -INFINITY ? 0.f : exp2f(m_ref - mx);
+                m_ref = mx;
+                l_sum *= corr;
+            }
+            // O_x may be rescaled once this tile's previous P V has finished; S_x(t) exists, so
+            // that product was issued, and its phase is the one the parity names
+            if (t > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
+                ok = atc_wait(&pv_done[x], (t - 1) & 1, 6);
+                if (!ok) break;
+                atc_fence_after();
+#pragma unroll 1
+                for (int c = 0; c < HD / 32; ++c) {
+                    float ov[32];
+                    atc_ld32(lane_base + o_col + c * 32, ov);
+                    uint32_t w[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) w[i] = __float_as_uint(ov[i] * corr);
+                    atc_st32(lane_base + o_col + c * 32, w);
+                }
+            }
+            // pass 2: probabilities 2^(s * scale - m_ref), their sum, P as bfloat16 in the place
+            // of S (the 64 scores of a half are in registers before its 32 columns of P are
+            // written, and P's columns 32 h .. lie inside S's columns 64 h ..)
+            const float neg_ref = m_ref == -INFINITY ? 0.f : -m_ref;
+            const float2 scale2 = make_float2(a.scale_log2, a.scale_log2);
+            const float2 ref2 = make_float2(neg_ref, neg_ref);
+            float2 l2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                float sv[2][32];
+#pragma unroll
+                for (int c = 0; c < 2; ++c)
+                    atc_ld32_nowait(lane_base + sp_col + (2 * h + c) * 32, sv[c]);
+                atc_ld_wait();
+                if (masked) {
+#pragma unroll
+                    for (int c = 0; c < 2; ++c)
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (!valid || kt + (2 * h + c) * 32 + i > qpos) sv[c][i] = -INFINITY;
+                }
+                uint32_t w[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const int k0 = 2 * i;                    // keys 64 h + k0, + 1 of the tile
+                    const float2 xx = __ffma2_rn(make_float2(sv[k0 / 32][k0 % 32],
+                                                             sv[(k0 + 1) / 32][(k0 + 1) % 32]),
+                                                 scale2, ref2);
+                    const float2 pr = make_float2(atc_ex2(xx.x), atc_ex2(xx.y));
+                    l2[i & 1] = __fadd2_rn(l2[i & 1], pr);
+                    w[i] = atc_pack(pr.x, pr.y);
+                }
+                atc_st32(lane_base + sp_col + h * 32, w);
+            }
+            l_sum += (l2[0].x + l2[0].y) + (l2[1].x + l2[1].y);
+            atc_st_wait();
+            atc_fence_before();
+            __syncwarp();
+            if (lane == 0) atc_arrive(&p_full[x]);
+        }
+        if (ok && my_tiles > 0 && atc_wait(o_done, 0, 7)) {
+            atc_fence_after();
+            const float inv = l_sum > 0.f ? 1.0f / l_sum : 0.f;
+            bf16* dst = a.out + (int64_t)(t0 + tok) * a.out_stride + (int64_t)(g * GS + j) * HD;
+#pragma unroll 1
+            for (int c = 0; c < HD / 32; ++c) {
+                float ov[32];
+                atc_ld32(lane_base + o_col + c * 32, ov);
+                if (valid) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        uint4 q4;
+                        q4.x = atc_pack(ov[8 * i + 0] * inv, ov[8 * i + 1] * inv);
+                        q4.y = atc_pack(ov[8 * i + 2] * inv, ov[8 * i + 3] * inv);
+                        q4.z = atc_pack(ov[8 * i + 4] * inv, ov[8 * i + 5] * inv);
+                        q4.w = atc_pack(ov[8 * i + 6] * inv, ov[8 * i + 7] * inv);
+                        reinterpret_cast<uint4*>(dst + c * 32)[i] = q4;
+                    }
+                }
+            }
+        }
+    }
+    atc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        atc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n"
+                     ::"r"(tmem), "r"(512u) : "memory");
+    }
+}
+
+#endif  // SLLM_HEAD_DIM <= 128
+
 typedef CUresult (*AtcEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                 const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                 const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -551,6 +909,14 @@ static AtcEncodeFn atc_encode_fn() {
 using namespace sllm;
 
 SLLM_EXPORT int sllm_attn_tc_head_dim() { return HD; }
+
+// Which kernel head sizes up to 128 run.  1 (the default): two query tiles per CTA when the
+// launch has at least five rounds of such CTAs, else one tile per CTA; 2: always two tiles;
+// 0: always one (head sizes above 128 have that kernel only).
+static int g_atc_two_tiles = 1;
+SLLM_EXPORT void sllm_attn_tc_set_two_tiles(int mode) {
+    g_atc_two_tiles = mode < 0 ? 0 : (mode > 2 ? 2 : mode);
+}
 
 // 1 if this kernel takes the shape, 0 if attention_mma.cu must serve it.
 SLLM_EXPORT int sllm_attn_tc_supports(int H, int G, int page_size, int window) {
@@ -610,8 +976,32 @@ SLLM_EXPORT int sllm_attn_tc(const void* q, int64_t q_stride, int64_t n_tokens, 
     a.row_start = row_start; a.row_pos0 = row_pos0; a.row_list = row_list;
     a.out = (bf16*)out; a.out_stride = out_stride; a.H = H; a.G = G;
     a.scale_log2 = scale * 1.4426950408889634f;
-    cudaError_t e = cudaFuncSetAttribute(attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)ATC_SMEM);
+    cudaError_t e;
+#if SLLM_HEAD_DIM <= 128
+    // Two query tiles per CTA halve the number of CTAs: that pays once the launch still fills
+    // the device several times over (measured at 32 heads over 8 kv heads of size 128: 600
+    // against 655 us at 8,192 tokens, but 186 against 177 us at 4,096 and 70.6 against 64.3 us
+    // at 2,048, where two and four rounds of CTAs are left).
+    static int n_sm = 0;
+    if (!n_sm) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+            n_sm = 148;
+    }
+    const int64_t pair_ctas = (((int64_t)max_new * GS + 2 * TQ - 1) / (2 * TQ)) * n_list * G;
+    if (g_atc_two_tiles == 1 ? pair_ctas >= 5 * (int64_t)n_sm : g_atc_two_tiles == 2) {
+        e = cudaFuncSetAttribute(attn_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)ATC2_SMEM);
+        if (e != cudaSuccess) return (int)e;
+        dim3 grid2(((int64_t)max_new * GS + 2 * TQ - 1) / (2 * TQ), n_list, G);
+        attn_tc2_kernel<<<grid2, ATC2_THREADS, ATC2_SMEM, stream>>>(map_q, map_kv, a);
+        SLLM_LAUNCH_CHECK();
+        return 0;
+    }
+#endif
+    e = cudaFuncSetAttribute(attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)ATC_SMEM);
     if (e != cudaSuccess) return (int)e;
     dim3 grid(((int64_t)max_new * GS + TQ - 1) / TQ, n_list, G);
     attn_tc_kernel<<<grid, ATC_THREADS, ATC_SMEM, stream>>>(map_q, map_kv, a);

@@ -137,12 +137,18 @@ def bench_attn_prefill(args) -> list[dict]:
         row = {"kernel": "attn_prefill", "tokens": t, "heads": H, "kv_heads": G, "head_dim": hd,
                "page": page, "peaks": src}
         if ops.attention_tc_supports(H, G, hd, page, None):
-            r = time_us(lambda i: ops.attention_tc(q, pages, table, page, row_start, pos0, o, None,
-                                                   1, t, H, G, hd, scale), args.reps)
-            assert ops.attention_tc_error(hd) == 0
-            row["tcgen05"] = r
-            row["tcgen05_tflops"] = round(flops / r["median_us"] / 1e6, 1)
-            row["tcgen05_tensor_frac"] = round(flops / r["median_us"] / 1e6 / tf, 3)
+            for name, two in (("tcgen05", None), ("tcgen05_two_tiles", True),
+                              ("tcgen05_one_tile", False)):
+                if two and hd > 128:
+                    continue
+                ops.attention_tc_set_two_tiles(hd, two)
+                r = time_us(lambda i: ops.attention_tc(q, pages, table, page, row_start, pos0, o,
+                                                       None, 1, t, H, G, hd, scale), args.reps)
+                assert ops.attention_tc_error(hd) == 0
+                row[name] = r
+                row[name + "_tflops"] = round(flops / r["median_us"] / 1e6, 1)
+                row[name + "_tensor_frac"] = round(flops / r["median_us"] / 1e6 / tf, 3)
+            ops.attention_tc_set_two_tiles(hd, None)
         r = time_us(lambda i: ops.attention_mma(q, pages, table, page, row_start, pos0, o, None, 1,
                                                 t, H, G, hd, scale, None, split=False), args.reps)
         row["mma_sync"] = r

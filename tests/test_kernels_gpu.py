@@ -394,16 +394,21 @@ def test_decode_attention_fused_with_rotation(ops, H, G, hd, page, window, n_spl
 @pytest.mark.parametrize("H, G, hd, page", [(8, 2, 64, 16), (32, 8, 128, 16), (8, 1, 128, 32),
                                            (4, 4, 64, 8), (2, 1, 128, 128), (4, 2, 256, 16),
                                            (2, 2, 192, 32)])
-def test_attention_tcgen05(ops, H, G, hd, page):
-    """Prompt portions on the tcgen05 kernel: long rows (several key tiles, several query
+@pytest.mark.parametrize("two_tiles", [True, False])
+def test_attention_tcgen05(ops, H, G, hd, page, two_tiles):
+    """Prompt portions on the tcgen05 kernels (two query tiles per CTA, which head sizes up to
+    128 use, and one): long rows (several key tiles, several query
     tiles), rows that start deep in a context, short rows; unused cache places hold NaN, as for
     the other attention kernels, and must not reach a result (rows that end in the middle of a
     page and of a key tile leave stale keys and values right behind their last position)."""
     ops.prepare([hd], verbose=False)
-    rows = [(0, 300), (450, 40), (0, 17), (127, 2), (128, 129), (1000, 30)]
+    if hd > 128 and two_tiles:
+        pytest.skip("head sizes above 128 have the one-tile kernel only")
+    rows = [(0, 300), (450, 40), (0, 17), (127, 2), (128, 129), (1000, 30), (60, 65), (0, 64)]
     global ATTN_ROWS
     saved = ATTN_ROWS
     ATTN_ROWS = rows
+    ops.attention_tc_set_two_tiles(hd, two_tiles)
     try:
         case = attention_case("bfloat16", H, G, hd, page)
         pages = case["pages"]
@@ -420,6 +425,7 @@ def test_attention_tcgen05(ops, H, G, hd, page):
             check_attention(case, out.cpu().float(), every, "bfloat16", H, hd, None)
     finally:
         ATTN_ROWS = saved
+        ops.attention_tc_set_two_tiles(hd, None)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
