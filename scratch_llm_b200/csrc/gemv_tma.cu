@@ -56,6 +56,23 @@ struct GemvTmaArgs {
     int stages;           // ring depth
     int x_stride;         // elements between token rows of the activations in shared memory
     int ring_offset;      // bytes from the start of shared memory to the ring
+    // A product that STARTS a branch of a pre-norm layer may take activations whose RMS norm is
+    // not finished: X = stream * gain, and every output of token t still has to be multiplied by
+    // rsqrt(sum_p ss_in[p][t] * ss_inv_dim + ss_eps), the factor that is one number per token
+    // and so commutes with the product.  ss_in = nullptr: X is what it is.
+    const float* ss_in;   // [ss_parts][8]: shares of the tokens' sums of squares
+    int ss_parts;
+    float ss_inv_dim, ss_eps;
+    // A product that ENDS a branch (not with SWIGLU) may put its output into the 32-bit residual
+    // stream itself and prepare the next norm: with r = resid[t][f] + round_bf16(y[t][f]),
+    //   resid[t][f] = r,   x_out[t][f] = bf16(r * gain[f]),   ss_out[tile][t] = sum_f r^2
+    // over the tile's 8 features.  resid = nullptr: Y is stored.
+    float* resid;
+    int64_t ld_resid;
+    const float* gain;
+    bf16* x_out;
+    int64_t ld_xout;
+    float* ss_out;        // [row tiles][8]
 };
 
 // Shared memory: [barriers] | the warps' partial sums | activations | ring
@@ -157,6 +174,28 @@ __global__ void __launch_bounds__(GT_THREADS, 1) gemv_tma_kernel(const __grid_co
         pdl_wait();
         pdl_trigger();
         const int f = warp - GT_CWARPS - GT_PWARPS;
+        // (the barrier page has room left behind its 104 barriers: 32 + 8 floats)
+        float* ss_share = reinterpret_cast<float*>(smem + 832);      // [4 warps][8 tokens]
+        float* inv_rms = ss_share + GT_FWARPS * GT_TOK;              // [8 tokens]
+        if (a.ss_in != nullptr && split == S - 1) {
+            // the tokens' factors: the shares are added in a fixed tree (16 strided sums, four
+            // of them per warp combined by shuffles, then the warps in order), so the factor
+            // does not depend on timing or on the batch
+            const int tok = lane & (GT_TOK - 1), sub = f * 4 + (lane >> 3);
+            float part = 0.f;
+            for (int p = sub; p < a.ss_parts; p += 16) part += __ldcg(a.ss_in + (size_t)p * GT_TOK + tok);
+            part += __shfl_xor_sync(0xffffffffu, part, 8);
+            part += __shfl_xor_sync(0xffffffffu, part, 16);
+            if (lane < GT_TOK) ss_share[f * GT_TOK + lane] = part;
+            gt_bar_sync(2, GT_FWARPS * 32);
+            if (f == 0 && lane < GT_TOK) {
+                float sum = 0.f;
+#pragma unroll
+                for (int i = 0; i < GT_FWARPS; ++i) sum += ss_share[i * GT_TOK + lane];
+                inv_rms[lane] = rsqrtf(sum * a.ss_inv_dim + a.ss_eps);
+            }
+            gt_bar_sync(2, GT_FWARPS * 32);
+        }
         if (f >= F) return;
         int round = 0;
         for (int tile = tile0 + f * tile_step; tile < tiles; tile += F * tile_step, ++round) {
@@ -214,7 +253,26 @@ __global__ void __launch_bounds__(GT_THREADS, 1) gemv_tma_kernel(const __grid_co
                 for (int w = 0; w < NW; ++w) v[w] = total[w][j] + part[w][j];
                 const int idx = lane + 32 * j;
                 const int tok = idx / GT_ROWS, feat = tile * GT_ROWS + (idx % GT_ROWS);
-                if (tok < a.M && feat < n_out) {
+                const bool there = tok < a.M && feat < n_out;
+                if (a.ss_in != nullptr) {
+#pragma unroll
+                    for (int w = 0; w < NW; ++w) v[w] *= inv_rms[tok];
+                }
+                if (!SWIGLU && a.resid != nullptr) {
+                    // into the residual stream, and the next norm's input and share of squares
+                    float r = 0.f;
+                    if (there) {
+                        r = a.resid[(int64_t)tok * a.ld_resid + feat] +
+                            __bfloat162float(__float2bfloat16_rn(v[0]));
+                        a.resid[(int64_t)tok * a.ld_resid + feat] = r;
+                        a.x_out[(int64_t)tok * a.ld_xout + feat] = __float2bfloat16_rn(r * a.gain[feat]);
+                    }
+                    float sq = r * r;               // the 8 features of a token sit in 8 lanes
+                    sq += __shfl_xor_sync(0xffffffffu, sq, 1);
+                    sq += __shfl_xor_sync(0xffffffffu, sq, 2);
+                    sq += __shfl_xor_sync(0xffffffffu, sq, 4);
+                    if ((lane & 7) == 0) a.ss_out[(size_t)tile * GT_TOK + tok] = sq;
+                } else if (there) {
                     float y = v[0];
                     if (SWIGLU) {
                         // the unfused path rounds gate and up to bfloat16 before the activation
@@ -404,13 +462,24 @@ SLLM_EXPORT int sllm_gemv_tma_supports(int M, int N, int K, int swiglu, int n_sm
 // `workspace` holds sllm_gemv_tma_workspace_bytes(...) bytes that are zero before the first
 // launch; launches leave them zero, so products of any sizes can share a workspace if their
 // launches are ordered by their stream.  `n_sm`: SMs of the device.
+// Deferred norm (see GemvTmaArgs): `ss_in` [ss_parts][8] with ss_dim and ss_eps makes the kernel
+// multiply token t's outputs by rsqrt(sum_p ss_in[p][t] / ss_dim + ss_eps); `resid` (with
+// ld_resid, gain [N], x_out with ld_xout, ss_out [ceil(N / 8)][8]; not with swiglu) makes it add
+// its output into the residual stream and write the next norm's input and shares of squares
+// instead of Y (which may then be nullptr).  nullptr switches either off.
 SLLM_EXPORT int sllm_gemv_tma(const void* X, const void* W, void* Y, void* workspace, int M, int N,
                               int K, int64_t ldx, int64_t ldw, int64_t ldy, int swiglu,
-                              int out_dtype, int n_sm, cudaStream_t stream) {
+                              int out_dtype, int n_sm, const float* ss_in, int ss_parts,
+                              int ss_dim, float ss_eps, float* resid, int64_t ld_resid,
+                              const float* gain, void* x_out, int64_t ld_xout, float* ss_out,
+                              cudaStream_t stream) {
     if (!sllm_gemv_tma_supports(M, N, K, swiglu, n_sm)) return (int)cudaErrorInvalidValue;
     if ((ldx % 8) || (ldw % 8) || ((uintptr_t)X & 15) || ((uintptr_t)W & 15) ||
         ((uintptr_t)workspace & 15))
         return (int)cudaErrorInvalidValue;
+    if (ss_in && (ss_parts < 1 || ss_dim < 1)) return (int)cudaErrorInvalidValue;
+    if (resid && (swiglu || !gain || !x_out || !ss_out)) return (int)cudaErrorInvalidValue;
+    if (!resid && !Y) return (int)cudaErrorInvalidValue;
     const int nw = swiglu ? 2 : 1;
     const int n_out = swiglu ? N / 2 : N;
     const int tiles = (n_out + GT_ROWS - 1) / GT_ROWS;
@@ -423,6 +492,10 @@ SLLM_EXPORT int sllm_gemv_tma(const void* X, const void* W, void* Y, void* works
     a.M = M; a.N = N; a.K = K;
     a.ldx = ldx; a.ldw = ldw; a.ldy = ldy;
     a.splits = S;
+    a.ss_in = ss_in; a.ss_parts = ss_parts;
+    a.ss_inv_dim = ss_in ? 1.0f / (float)ss_dim : 0.f; a.ss_eps = ss_eps;
+    a.resid = resid; a.ld_resid = ld_resid; a.gain = gain;
+    a.x_out = (bf16*)x_out; a.ld_xout = ld_xout; a.ss_out = ss_out;
     a.x_stride = (int)gt_x_stride(K, S);
     const int64_t fixed = gt_fixed_smem(K, S);
     const int stage_bytes = nw * GT_BLOCK_BYTES;

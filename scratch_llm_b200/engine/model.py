@@ -143,12 +143,20 @@ class DecoderModel:
                             device=self.ctx.device)
         ops.embed(batch.token_ids, self.embedding, resid, batch.pending_tokens)
         pending = None
-        for run in s.order:
+        for i, run in enumerate(s.order):
             pages, group = cache.entry_pages(run.cache)
             view = CacheView(pages=pages,
                              block_table=batch.block_tables[group] if group is not None else None,
                              page_size=cache.page_size, state=cache.states[run.cache])
-            pending = self.blocks[run.layer].forward(resid, pending, batch, view, run.write)
+            block = self.blocks[run.layer]
+            if getattr(block, "takes_next_entry", False):
+                # what the next run starts with, so that this block's last product may prepare
+                # it (the final norm works on gathered rows: nothing is prepared for it)
+                nxt = self.blocks[s.order[i + 1].layer] if i + 1 < len(s.order) else None
+                entry = nxt.entry() if nxt is not None and hasattr(nxt, "entry") else None
+                pending = block.forward(resid, pending, batch, view, run.write, next_entry=entry)
+            else:
+                pending = block.forward(resid, pending, batch, view, run.write)
         if batch.n_out == 0:
             return None
         h = self.final_norm.forward(resid, pending, out_rows=batch.logit_index)

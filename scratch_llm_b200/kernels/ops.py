@@ -289,29 +289,66 @@ def gemv_tma_reserve(n: int, k: int, swiglu: bool, device: torch.device) -> torc
     return held[-1]
 
 
-def gemv_tma(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool = False
-             ) -> torch.Tensor:
+def gemv_tma(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None, swiglu: bool = False,
+             scale: tuple[torch.Tensor, int, float] | None = None,
+             sink: tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor] | None = None
+             ) -> torch.Tensor | None:
     """out[M, N] = x[M, K] @ w[N, K]^T for M <= 8 tokens by the persistent kernel that streams w
     through shared memory with bulk copies (one CTA per SM, four ranges of K whose partial sums
     the last CTA of a row tile adds in a fixed order).  ``swiglu`` as in :func:`gemv_mma`.
-    Launches share one workspace per device and must be ordered by their stream."""
+    Launches share one workspace per device and must be ordered by their stream.
+
+    ``scale = (shares, dim, eps)``: x is a stream times a norm's gain whose RMS norm is not
+    finished; every output of token t is multiplied by ``rsqrt(shares[:, t].sum() / dim + eps)``
+    (``shares`` float32 [parts, 8]).  ``sink = (resid, gain, x_out, shares_out)`` (not with
+    ``swiglu``): the output is added into the 32-bit stream ``resid`` [M, N] instead of being
+    stored (``out`` may be None), ``x_out`` [M, N] bfloat16 gets ``resid * gain`` and
+    ``shares_out`` float32 [ceil(N / 8), 8] the tokens' sums of squares over each 8 features."""
     _need(x, torch.bfloat16, "x", contiguous=False)
     _need(w, torch.bfloat16, "w", contiguous=False)
-    _need(out, None, "out", contiguous=False)
     (m, k), (n, k2) = x.shape, w.shape
     n_out = n // 2 if swiglu else n
-    if k != k2 or out.shape != (m, n_out) or x.stride(1) != 1 or w.stride(1) != 1 \
-            or out.stride(1) != 1:
-        raise KernelError(f"gemv shapes/strides: x {list(x.shape)}, w {list(w.shape)}, "
-                          f"out {list(out.shape)}")
+    if out is not None:
+        _need(out, None, "out", contiguous=False)
+        if out.shape != (m, n_out) or out.stride(1) != 1:
+            raise KernelError(f"gemv out must be [{m}, {n_out}] with contiguous rows")
+    elif sink is None:
+        raise KernelError("gemv_tma needs an output or a sink")
+    if k != k2 or x.stride(1) != 1 or w.stride(1) != 1:
+        raise KernelError(f"gemv shapes/strides: x {list(x.shape)}, w {list(w.shape)}")
     if not gemv_tma_supports(m, n, k, swiglu) or x.stride(0) % 8 or w.stride(0) % 8:
         raise KernelError(f"gemv_tma takes 1 to 8 tokens, K a multiple of 256 and at least 1024, "
                           f"and rows that are multiples of 8 elements; got M={m}, N={n}, K={k}")
+    ss_in, ss_parts, ss_dim, ss_eps = None, 0, 1, 0.0
+    if scale is not None:
+        ss_in, ss_dim, ss_eps = scale
+        _need(ss_in, torch.float32, "scale shares")
+        if ss_in.dim() != 2 or ss_in.shape[1] != 8 or ss_dim < 1:
+            raise KernelError("scale shares must be float32 [parts, 8]")
+        ss_parts = ss_in.shape[0]
+    resid = gain = x_out = ss_out = None
+    if sink is not None:
+        if swiglu:
+            raise KernelError("a sink cannot follow the fused activation")
+        resid, gain, x_out, ss_out = sink
+        _need(resid, torch.float32, "resid", contiguous=False)
+        _need(gain, torch.float32, "gain")
+        _need(x_out, torch.bfloat16, "x_out", contiguous=False)
+        _need(ss_out, torch.float32, "shares_out")
+        if resid.shape != (m, n) or x_out.shape != (m, n) or gain.numel() != n \
+                or resid.stride(1) != 1 or x_out.stride(1) != 1 \
+                or ss_out.numel() < -(-n // 8) * 8:
+            raise KernelError("sink shapes: resid and x_out [M, N], gain [N], shares [ceil(N/8), 8]")
     workspace = gemv_tma_reserve(n, k, swiglu, x.device)
     _check(_core("sllm_gemv_tma").sllm_gemv_tma(
         _ptr(x), _ptr(w), _ptr(out), _ptr(workspace), c_int(m), c_int(n), c_int(k),
-        c_int64(x.stride(0)), c_int64(w.stride(0)), c_int64(out.stride(0)), c_int(int(swiglu)),
-        c_int(_code(out.dtype)), c_int(_sm_count(x.device)), _stream()), "gemv_tma")
+        c_int64(x.stride(0)), c_int64(w.stride(0)), c_int64(out.stride(0) if out is not None else 0),
+        c_int(int(swiglu)), c_int(_code(out.dtype) if out is not None else 1),
+        c_int(_sm_count(x.device)), _ptr(ss_in), c_int(ss_parts), c_int(ss_dim), c_float(ss_eps),
+        _ptr(resid), c_int64(resid.stride(0) if resid is not None else 0), _ptr(gain), _ptr(x_out),
+        c_int64(x_out.stride(0) if x_out is not None else 0), _ptr(ss_out), _stream()), "gemv_tma")
+    if sink is not None:    # (counted beside "gemv_tma": which steps handed a norm over)
+        launch_counts["gemv_tma_sink"] = launch_counts.get("gemv_tma_sink", 0) + 1
     return out
 
 

@@ -45,6 +45,10 @@ def decode_splits(base_ctas: int, context: int, slots: int) -> int:
 @register_mixer("gqa_attention")
 class GQAttention(Mixer):
     pad_safe = True   # padding tokens are not stored, rows without tokens leave the kernels at once
+    accepts_sink = True   # forward() takes sink=: the output projection may feed the stream itself
+
+    def accepts_normed(self, n_tokens: int) -> bool:
+        return self.qkv is not None and self.qkv.takes_normed(n_tokens)
 
     def __init__(self, hidden_size: int, n_heads: int, n_kv_heads: int, head_dim: int,
                  scale: float, window: int | None = None,
@@ -77,7 +81,15 @@ class GQAttention(Mixer):
         self.qkv = Linear(torch.cat([put(tensors[self.names[n]]) for n in "qkv"], 0).contiguous())
         self.o = Linear(put(tensors[self.names["o"]]).contiguous())
 
-    def forward(self, x: torch.Tensor, batch, cache: CacheView, write: bool,
+    def forward(self, x, batch, cache: CacheView, write: bool, position: PositionEncoding,
+                sink=None):
+        """``x``: the normed activations (or a :class:`~.stream.Normed`, see accepts_normed);
+        ``sink``: where the output projection may put its result (a
+        :class:`~.stream.StreamSink`), else the result is returned."""
+        out = self._attend(x, batch, cache, write, position)
+        return self.o(out) if sink is None else sink.finish(self.o, out)
+
+    def _attend(self, x, batch, cache: CacheView, write: bool,
                 position: PositionEncoding) -> torch.Tensor:
         H, G, hd = self.n_heads, self.n_kv_heads, self.head_dim
         qkv = self.qkv(x)
@@ -98,7 +110,7 @@ class GQAttention(Mixer):
             # a step of single tokens: the decode kernel rotates q and the new keys itself and
             # stores the new keys and values (one launch fewer, q and k make no round trip)
             self._decode_fused(qkv, out, batch, cache, (cos, sin, interleaved, write))
-            return self.o(out)
+            return out
         ops.rope_kv_write(qkv, batch.positions, batch.token_row, cos, sin, cache.pages,
                           cache.block_table, cache.page_size, H, G, hd, interleaved, write)
         q = qkv[:, :H * hd]
@@ -108,7 +120,7 @@ class GQAttention(Mixer):
             ops.attention_simt(q, cache.pages, cache.block_table, cache.page_size,
                                batch.row_start, batch.row_pos0, out, batch.n_rows,
                                batch.max_new, H, G, hd, self.scale, self.window)
-        return self.o(out)
+        return out
 
     def _n_splits(self, batch) -> int:
         H, G = self.n_heads, self.n_kv_heads

@@ -135,6 +135,13 @@ class Block:
     ROLES: dict[str, str] = {}
     capturable = True
     pad_safe = False
+    #: True if forward() takes ``next_entry=``: the (norm, part) that the next block in the run
+    #: order starts with (None at the end), so that the block's last product may prepare it
+    takes_next_entry = False
+
+    def entry(self):
+        """(norm, part) this block starts with, for the block before it; None: not said."""
+        return None
 
     def forward(self, resid: torch.Tensor, pending: torch.Tensor | None, batch: "StepBatch",
                 cache: CacheView, write: bool) -> torch.Tensor:

@@ -13,6 +13,7 @@ import torch
 
 from .base import Block, CacheView, FeedForward, Mixer, Norm, PositionEncoding
 from .registry import register_block
+from .stream import StreamSink
 
 
 @register_block("pre_norm")
@@ -27,9 +28,35 @@ class PreNormBlock(Block):
         self.mixer_norm, self.feed_forward_norm = mixer_norm, feed_forward_norm
         self.position = position
 
-    def forward(self, resid: torch.Tensor, pending: torch.Tensor | None, batch,
-                cache: CacheView, write: bool) -> torch.Tensor:
+    #: forward() takes next_entry=: what follows this block in the run order
+    takes_next_entry = True
+
+    def entry(self):
+        """(the norm that takes the pending delta, the part that takes the norm's output)."""
+        return self.mixer_norm, self.mixer
+
+    @staticmethod
+    def _sink(resid: torch.Tensor, producer, norm, consumer, n_tokens: int):
+        """A sink for ``producer``'s output if it, the norm after it and the part after that
+        all can hand the norm over (scratch_llm_b200.parts.stream), else None."""
+        if norm is None or consumer is None or not getattr(producer, "accepts_sink", False) \
+                or not getattr(norm, "deferrable", False):
+            return None
+        can = getattr(consumer, "accepts_normed", None)
+        return StreamSink(resid, norm) if can is not None and can(n_tokens) else None
+
+    def forward(self, resid: torch.Tensor, pending, batch, cache: CacheView, write: bool,
+                next_entry=None):
+        n = resid.shape[0]
         h = self.mixer_norm.forward(resid, pending)
-        a = self.mixer.forward(h, batch, cache, write, self.position)
+        sink = self._sink(resid, self.mixer, self.feed_forward_norm, self.feed_forward, n)
+        if sink is None:
+            a = self.mixer.forward(h, batch, cache, write, self.position)
+        else:
+            a = self.mixer.forward(h, batch, cache, write, self.position, sink=sink)
         h = self.feed_forward_norm.forward(resid, a)
-        return self.feed_forward.forward(h)
+        norm, consumer = next_entry if next_entry is not None else (None, None)
+        sink = self._sink(resid, self.feed_forward, norm, consumer, n)
+        if sink is None:
+            return self.feed_forward.forward(h)
+        return self.feed_forward.forward(h, sink=sink)

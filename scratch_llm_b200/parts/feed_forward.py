@@ -18,6 +18,10 @@ from .registry import register_feed_forward
 @register_feed_forward("swiglu")
 class SwiGLU(FeedForward):
     pad_safe = True   # every token by itself
+    accepts_sink = True   # forward() takes sink=: the down projection may feed the stream itself
+
+    def accepts_normed(self, n_tokens: int) -> bool:
+        return self.gate_up is not None and self.gate_up.takes_normed(n_tokens, swiglu=True)
 
     def __init__(self, hidden_size: int, intermediate_size: int,
                  names: Mapping[str, str] | None = None) -> None:
@@ -38,5 +42,6 @@ class SwiGLU(FeedForward):
                                          put(tensors[self.names["up"]])], 0).contiguous())
         self.down = Linear(put(tensors[self.names["down"]]).contiguous())
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return self.down(self.gate_up.swiglu(x))
+    def forward(self, x, sink=None):
+        y = self.gate_up.swiglu(x)
+        return self.down(y) if sink is None else sink.finish(self.down, y)

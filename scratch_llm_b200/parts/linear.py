@@ -12,6 +12,7 @@ from __future__ import annotations
 import torch
 
 from ..kernels import ops
+from .stream import Normed
 
 
 #: up to this many tokens the streaming small-batch kernel runs instead of the library product
@@ -39,9 +40,28 @@ class Linear:
             if self._persistent or self._persistent_swiglu:
                 ops.gemv_tma_reserve(n, k, False, weight.device)
 
-    def __call__(self, x: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    def takes_normed(self, n_tokens: int, swiglu: bool = False) -> bool:
+        """Whether this product can start from activations whose norm is not finished
+        (:class:`~scratch_llm_b200.parts.stream.Normed`): the persistent small-batch kernel
+        applies the tokens' factors to its outputs."""
+        return n_tokens <= SMALL_BATCH and (self._persistent_swiglu if swiglu
+                                            else self._persistent)
+
+    def can_sink(self, x: torch.Tensor) -> bool:
+        """Whether this product can add its output into the residual stream itself."""
+        return (self._persistent and isinstance(x, torch.Tensor) and x.shape[0] <= SMALL_BATCH
+                and x.dtype == torch.bfloat16 and x.stride(0) % 8 == 0)
+
+    def __call__(self, x, out_dtype: torch.dtype | None = None) -> torch.Tensor:
         w = self.weight
         out_dtype = out_dtype or w.dtype
+        if isinstance(x, Normed):
+            if not self.takes_normed(x.x.shape[0]):
+                raise ValueError("this product cannot finish a deferred norm (the part that "
+                                 "handed it over must ask takes_normed first)")
+            out = torch.empty((x.x.shape[0], self.out_features), dtype=out_dtype,
+                              device=x.x.device)
+            return ops.gemv_tma(x.x, w, out, scale=(x.shares, x.dim, x.eps))
         if x.dtype != w.dtype:
             raise ValueError(f"Linear: input is {x.dtype}, weight is {w.dtype}")
         if w.dtype == torch.float32:
@@ -66,6 +86,12 @@ class Linear:
         takes the shape."""
         w = self.weight
         half = self.out_features // 2
+        if isinstance(x, Normed):
+            if not self.takes_normed(x.x.shape[0], swiglu=True):
+                raise ValueError("this product cannot finish a deferred norm (the part that "
+                                 "handed it over must ask takes_normed first)")
+            out = torch.empty((x.x.shape[0], half), dtype=x.x.dtype, device=x.x.device)
+            return ops.gemv_tma(x.x, w, out, swiglu=True, scale=(x.shares, x.dim, x.eps))
         out = torch.empty((x.shape[0], half), dtype=x.dtype, device=x.device)
         fits = (w.dtype == torch.bfloat16 and self.in_features % 8 == 0
                 and x.stride(0) % 8 == 0)

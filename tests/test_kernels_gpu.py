@@ -194,6 +194,61 @@ def test_gemv_persistent_bulk_copies(ops, m, n, k):
     assert ops.gemv_tma_error() == 0
 
 
+@pytest.mark.parametrize("m, d, f, eps", [(8, 1024, 1536, 1e-5), (3, 4096, 2560, 1e-6),
+                                          (1, 2048, 4608, 1e-3), (5, 1536, 1024, 1e-5)])
+def test_gemv_hands_the_norm_over(ops, m, d, f, eps):
+    """The two halves of a deferred RMS norm around the residual stream.  A product that ends a
+    branch (f -> d) adds its output into the 32-bit stream, writes stream * gain and the
+    tokens' shares of squares; the product that starts the next branch (d -> f, plain and with
+    the fused activation) multiplies its outputs by rsqrt(mean(stream^2) + eps).  Together they
+    must give what add + norm + product give in the plain order (src/scratch_llm/model.py:
+    158-162, 430-435 of the reference)."""
+    x = rand(m, f, dtype=torch.bfloat16, seed=1)
+    w_end = rand(d, f, dtype=torch.bfloat16, seed=2, scale=0.05)
+    w_next = rand(2 * f, d, dtype=torch.bfloat16, seed=3, scale=0.05)
+    gain = rand(d, seed=4) * 0.2 + 1.0
+    resid0 = rand(m + 2, d, seed=5, scale=3.0)        # two rows more: they must stay untouched
+    # plain order
+    y = (x.float() @ w_end.float().T).to(torch.bfloat16).float()
+    stream = resid0[:m] + y
+    normed = P.rmsnorm(stream, gain, eps)
+    want_plain = normed @ w_next.float().T
+    g, u = want_plain[:, :f].to(torch.bfloat16).float(), want_plain[:, f:].to(torch.bfloat16).float()
+    want_act = g * torch.sigmoid(g) * u
+    # the engine's order
+    resid = resid0.cuda()
+    x_out = torch.full((m, d), float("nan"), dtype=torch.bfloat16, device="cuda")
+    shares = torch.full((-(-d // 8), 8), float("nan"), dtype=torch.float32, device="cuda")
+    ops.gemv_tma(x.cuda(), w_end.cuda(), None, sink=(resid[:m], gain.cuda(), x_out, shares))
+    # (the product's output is rounded to bfloat16 before it is added, as the unfused path
+    # does: a sum that lands on a tie may round the other way, one bfloat16 step of y)
+    torch.testing.assert_close(resid.cpu()[:m], stream, rtol=0, atol=2.0 ** -7 * float(y.abs().max()))
+    assert float((resid.cpu()[:m] - stream).abs().mean()) < 1e-5
+    assert torch.equal(resid.cpu()[m:], resid0[m:])
+    torch.testing.assert_close(x_out.cpu().float(), (stream * gain).to(torch.bfloat16).float(),
+                               rtol=1e-2, atol=1e-2)
+    torch.testing.assert_close(shares.cpu()[:, :m].sum(0), stream.pow(2).sum(-1), rtol=1e-4, atol=1e-3)
+    out = torch.full((m, 2 * f), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.gemv_tma(x_out, w_next.cuda(), out, scale=(shares, d, eps))
+    # (activations rounded to bfloat16 once, before the factor instead of after it: errors of
+    # a bfloat16 step of the inputs, measured against the largest output)
+    torch.testing.assert_close(out.cpu().float(), want_plain, rtol=1.6e-2,
+                               atol=1e-2 * float(want_plain.abs().max()))
+    act = torch.full((m, f), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.gemv_tma(x_out, w_next.cuda(), act, swiglu=True, scale=(shares, d, eps))
+    torch.testing.assert_close(act.cpu().float(), want_act, rtol=3e-2,
+                               atol=1e-2 * float(want_act.abs().max()))
+    # one token alone gives the bits it gave in the batch (sink and scale are per token)
+    resid1 = resid0[m - 1:m].clone().cuda()
+    x1 = torch.empty((1, d), dtype=torch.bfloat16, device="cuda")
+    s1 = torch.empty_like(shares)
+    ops.gemv_tma(x[m - 1:].cuda(), w_end.cuda(), None, sink=(resid1, gain.cuda(), x1, s1))
+    o1 = torch.empty((1, 2 * f), dtype=torch.bfloat16, device="cuda")
+    ops.gemv_tma(x1, w_next.cuda(), o1, scale=(s1, d, eps))
+    assert torch.equal(o1.cpu()[0], out.cpu()[m - 1])
+    assert ops.gemv_tma_error() == 0
+
+
 @pytest.mark.parametrize("m, n, k", [(128, 256, 64), (128, 256, 256), (256, 512, 192), (300, 600, 200),
                                      (5, 40, 72), (2048, 1024, 512), (130, 6144, 4096),
                                      (513, 2560, 1024)])

@@ -90,7 +90,10 @@ def test_replay_matches_plain(way, name, page, dtype, model_dirs, expected):
         ran = {k: v - before.get(k, 0) for k, v in ops.launch_counts.items()}
         if dtype == "bfloat16":
             # the kernels that the full-size models spend their time in all ran in this trace
-            for op in ("gemv_tma", "attention_mma_decode", "attention_tc", "gemm_tc"):
+            # (gemv_tma_sink: decode steps in which a product fed the residual stream itself
+            # and the norm after it was finished by the next product)
+            for op in ("gemv_tma", "gemv_tma_sink", "attention_mma_decode", "attention_tc",
+                       "gemm_tc"):
                 assert ran.get(op, 0) > 0, f"{op} never ran: {ran}"
 
 
