@@ -2,10 +2,10 @@
 """Puts the unmodified reference package under ``baseline/_ref`` for ``bench.py --impl
 reference``, without a network.
 
-    python baseline/install_reference.py <checkout of andreidhoang/scratch_llm>
+    python baseline/install_reference.py <checkout of andreidhoang/scratch_llm> [<wheelhouse>]
 
-First the offline pip install (from a copy of the checkout, since a build may write into its
-source tree).  The reference's build backend is hatchling; where the wheelhouse does not hold
+First the offline pip install (``--no-index --no-build-isolation --find-links <wheelhouse>``,
+from a copy of the checkout, since a build may write into its source tree).  The reference's build backend is hatchling; where the wheelhouse does not hold
 it, pip cannot build the wheel, and the package is placed by hand: it is pure Python, and the
 wheel that hatchling would build holds exactly the tree ``src/scratch_llm``
 (pyproject.toml: ``[tool.hatch.build.targets.wheel] packages = ["src/scratch_llm"]``), so that
@@ -26,10 +26,11 @@ TARGET = HERE / "_ref"
 
 
 def main() -> int:
-    if len(sys.argv) != 2:
+    if len(sys.argv) not in (2, 3):
         print(__doc__)
         return 2
     src = Path(sys.argv[1]).resolve()
+    links = ["--find-links", sys.argv[2]] if len(sys.argv) == 3 else []
     if not (src / "src" / "scratch_llm" / "model.py").is_file():
         print(f"{src} is not a checkout of the reference (no src/scratch_llm/model.py)")
         return 1
@@ -41,7 +42,7 @@ def main() -> int:
         copy = Path(tmp) / "reference"
         shutil.copytree(src, copy, ignore=shutil.ignore_patterns(".git", "artifacts", "assets"))
         cmd = [sys.executable, "-m", "pip", "install", "--no-index", "--no-build-isolation",
-               "--no-deps", "--find-links", "/opt/wheelhouse", "--target", str(TARGET), str(copy)]
+               "--no-deps", *links, "--target", str(TARGET), str(copy)]
         proc = subprocess.run(cmd, capture_output=True, text=True)
         notes.append("$ " + " ".join(cmd))
         notes.append(f"exit code {proc.returncode}")

@@ -34,8 +34,12 @@
 //     zero.  Nothing depends on timing or on M, so a token's result is bitwise the same at any
 //     batch size.  Several units are in flight in the combiners while the consumers go on.
 //
-// Waiting on CTAs of the same grid: the collecting CTA waits only for CTAs with smaller block
-// indices, which the hardware scheduled before it, and the grid is at most one CTA per SM.
+// Waiting on CTAs of the same grid: the collecting CTA polls words that CTAs with smaller block
+// indices write.  Those CTAs never wait for the collecting one, the grid has at most one CTA per
+// SM, and a CTA needs no more than an SM can give: so whatever order the hardware starts the
+// CTAs in (usually that of their indices, which keeps the wait short), and also when the
+// previous kernel of the stream still holds SMs at this grid's programmatic start, every CTA
+// gets its SM without anything of this grid having to finish first, and the wait ends.
 //
 // Every wait (mbarrier or flag) is bounded: after about two seconds the thread records a code
 // in `g_gemv_error` and goes on without waiting (the host reads the word and raises): 1 =
