@@ -114,6 +114,11 @@ struct AttnArgs {
     // projection as they are (q points at its first column): the kernel rotates q and the row's
     // new key itself and, if write_kv, stores the new key and value.
     const float* cos_t; const float* sin_t; int interleaved; int write_kv;
+    // attn_decode_cs_kernel with several splits, one query tile per row: a counter per (listed
+    // row, kv head), zero between launches.  The CTA that finishes last for a row and kv head
+    // (it sees the count n_splits - 1) merges the splits' partial results itself, so that no
+    // merge kernel follows; nobody waits for anybody.  nullptr: a merge kernel follows.
+    int* merge_count;
 };
 
 template <bool SPLIT>
@@ -753,6 +758,52 @@ __global__ void __launch_bounds__(THREADS, 3) attn_decode_cs_kernel(const AttnAr
                     l_tot > 0.f ? m_run[h] + log2f(l_tot) : -INFINITY;
         }
     }
+    if (n_splits > 1 && a.merge_count != nullptr) {
+        // The last CTA to arrive for this row and kv head merges (the arithmetic and the order
+        // of attn_merge_kernel: the result does not depend on which CTA that is).  The fence
+        // before the count makes this CTA's partial results visible to whoever counts later.
+        __shared__ int is_last;
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) {
+            int* count = a.merge_count + (size_t)blockIdx.y * a.G + g;
+            is_last = atomicAdd(count, 1) == n_splits - 1;
+            if (is_last) *count = 0;                 // zero again for the next launch
+        }
+        __syncthreads();
+        if (!is_last) return;
+        __threadfence();
+        for (int idx = tid; idx < n_packed * (HD / 4); idx += THREADS) {
+            const int p = idx / (HD / 4), d = (idx - p * (HD / 4)) * 4;
+            const int tok = p / GS, j = p - tok * GS;
+            if (t0 + tok >= a.part_tokens) continue;
+            const int64_t qh = (int64_t)(t0 + tok) * a.H + g * GS + j;
+            const float* lse = a.part_lse + qh * n_splits;
+            float mm = -INFINITY;
+            for (int sp = 0; sp < n_splits; ++sp) mm = fmaxf(mm, __ldcg(lse + sp));
+            float4 num = make_float4(0.f, 0.f, 0.f, 0.f);
+            float den = 0.f;
+            if (mm != -INFINITY) {
+                const float* po = a.part_o + qh * n_splits * HD + d;
+#pragma unroll 8
+                for (int sp = 0; sp < n_splits; ++sp) {
+                    const float f = exp2f(__ldcg(lse + sp) - mm);
+                    const float4 v = __ldcg(reinterpret_cast<const float4*>(po + (int64_t)sp * HD));
+                    num.x += f * v.x;
+                    num.y += f * v.y;
+                    num.z += f * v.z;
+                    num.w += f * v.w;
+                    den += f;
+                }
+            }
+            const bool some = den > 0.f;
+            bf16* dst = a.out + (int64_t)(t0 + tok) * a.out_stride + (int64_t)(g * GS + j) * HD + d;
+            *reinterpret_cast<__nv_bfloat162*>(dst) =
+                __floats2bfloat162_rn(some ? num.x / den : 0.f, some ? num.y / den : 0.f);
+            *reinterpret_cast<__nv_bfloat162*>(dst + 2) =
+                __floats2bfloat162_rn(some ? num.z / den : 0.f, some ? num.w / den : 0.f);
+        }
+    }
 }
 
 #endif  // SLLM_HEAD_DIM % 64 == 0
@@ -864,7 +915,7 @@ SLLM_EXPORT int sllm_attn_mma(const void* q, int64_t q_stride, const void* pages
     a.page_size = page_size; a.row_start = row_start; a.row_pos0 = row_pos0; a.row_list = row_list;
     a.out = (bf16*)out; a.out_stride = out_stride;
     a.part_o = nullptr; a.part_lse = nullptr; a.n_splits = 1;
-    a.part_tokens = n_tokens_total; a.part_error = nullptr;
+    a.part_tokens = n_tokens_total; a.part_error = nullptr; a.merge_count = nullptr;
     a.cos_t = nullptr; a.sin_t = nullptr; a.interleaved = 1; a.write_kv = 0;
     a.H = H; a.G = G; a.scale_log2 = scale * 1.4426950408889634f; a.window = window;
     const int GS = H / G;
@@ -918,7 +969,9 @@ SLLM_EXPORT int sllm_attn_mma_decode_fused_supported() { return 1; }
 // the step's fused projection [tokens, (H + 2 G) * HD] (q heads, k heads, v heads); the kernel
 // rotates q and the new key (adjacent pairs if `interleaved`, else the halves) and, if
 // `write_kv`, stores the rotated key and the value at the row's position in the cache.
-// `scratch` as in sllm_attn_mma for n_splits > 1 (a merge kernel follows).
+// `scratch` as in sllm_attn_mma for n_splits > 1.  `merge_count`: n_list * G counters that are
+// zero before the first launch (every launch leaves them zero): the CTA that finishes last for
+// a row and kv head merges the splits itself; nullptr: a merge kernel follows instead.
 SLLM_EXPORT int sllm_attn_mma_decode(const void* qkv, int64_t qkv_stride, void* pages,
                                      const int* block_table, int table_stride, int page_size,
                                      const int* row_start, const int* row_pos0,
@@ -926,7 +979,7 @@ SLLM_EXPORT int sllm_attn_mma_decode(const void* qkv, int64_t qkv_stride, void* 
                                      int64_t out_stride, int H, int G, float scale, int window,
                                      int n_splits, float* scratch, int64_t n_tokens_total,
                                      const float* cos_t, const float* sin_t, int interleaved,
-                                     int write_kv, cudaStream_t stream) {
+                                     int write_kv, int* merge_count, cudaStream_t stream) {
     if (n_list <= 0) return 0;
     if (H <= 0 || G <= 0 || H % G != 0 || page_size <= 0 || window < 0 || n_list > 65535 ||
         G > 65535 || (qkv_stride % 8) != 0 || (out_stride % 2) != 0 || n_splits < 1 || H / G > 16)
@@ -940,6 +993,7 @@ SLLM_EXPORT int sllm_attn_mma_decode(const void* qkv, int64_t qkv_stride, void* 
     a.out = (bf16*)out; a.out_stride = out_stride;
     a.part_o = nullptr; a.part_lse = nullptr; a.n_splits = n_splits;
     a.part_tokens = n_tokens_total; a.part_error = nullptr;
+    a.merge_count = n_splits > 1 ? merge_count : nullptr;
     a.H = H; a.G = G; a.scale_log2 = scale * 1.4426950408889634f; a.window = window;
     a.cos_t = cos_t; a.sin_t = sin_t; a.interleaved = interleaved; a.write_kv = write_kv;
     if (n_splits > 1) {
@@ -954,7 +1008,7 @@ SLLM_EXPORT int sllm_attn_mma_decode(const void* qkv, int64_t qkv_stride, void* 
     dim3 grid(n_splits, n_list, G);   // one tile of 16 packed queries per (row, kv head)
     e = sllm_launch_pdl(attn_decode_cs_kernel, grid, dim3(THREADS), smem, stream, a);
     if (e != cudaSuccess) return (int)e;
-    if (n_splits > 1) {
+    if (n_splits > 1 && a.merge_count == nullptr) {
         dim3 mgrid(n_list, (H + MERGE_WARPS - 1) / MERGE_WARPS);
         e = sllm_launch_pdl(attn_merge_kernel, mgrid, dim3(MERGE_WARPS * 32), 0, stream,
                             (const float*)a.part_o, (const float*)a.part_lse, n_splits, row_start,

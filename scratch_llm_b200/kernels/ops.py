@@ -527,19 +527,36 @@ def attention_decode_fused_supported(head_dim: int) -> bool:
     return bool(_load(*attention_mma_library(head_dim)).sllm_attn_mma_decode_fused_supported())
 
 
+#: counters of the decode attention's in-kernel merge, per device (zero between launches; a
+#: buffer that has been handed to a launch is never freed: a captured graph may hold its address)
+_merge_counters: dict[int, list[torch.Tensor]] = {}
+
+
+def _merge_counter(device: torch.device, n: int) -> torch.Tensor:
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    held = _merge_counters.setdefault(index, [])
+    if not held or held[-1].numel() < n:
+        held.append(torch.zeros(max(n, 4096), dtype=torch.int32, device=device))
+    return held[-1]
+
+
 def attention_mma_decode(qkv: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor,
                          page_size: int, row_start: torch.Tensor, row_pos0: torch.Tensor,
                          out: torch.Tensor, row_list: torch.Tensor | None, n_list: int,
                          n_heads: int, n_kv_heads: int, head_dim: int, scale: float,
                          window: int | None, cos: torch.Tensor, sin: torch.Tensor,
                          interleaved: bool, write: bool, n_splits: int = 1,
-                         scratch: torch.Tensor | None = None) -> torch.Tensor:
+                         scratch: torch.Tensor | None = None,
+                         merge_inside: bool = True) -> torch.Tensor:
     """Decode attention (rows of one new token) over the paged cache on the tensor cores, for
     head sizes that are multiples of 64, straight from the step's fused projection ``qkv``
     [tokens, (H + 2 G) * hd] as the product left it: the kernel rotates q and the new key itself
     (``cos``/``sin`` tables, adjacent pairs if ``interleaved``) and, if ``write``, stores the new
     key and value into ``pages``: no separate rotate-and-store kernel runs.  ``scratch`` as in
-    :func:`attention_mma` for several splits."""
+    :func:`attention_mma` for several splits; with ``merge_inside`` the CTA that finishes last for
+    a row and kv head merges the splits itself (same arithmetic, no merge kernel, nobody waits),
+    else a merge kernel follows.  Launches share the merge's counters per device and must be
+    ordered by their stream."""
     _need(qkv, torch.bfloat16, "qkv", contiguous=False)
     _need(pages, torch.bfloat16, "pages")
     _need(out, torch.bfloat16, "out", contiguous=False)
@@ -573,13 +590,15 @@ def attention_mma_decode(qkv: torch.Tensor, pages: torch.Tensor, block_table: to
             raise KernelError(f"attention scratch holds {scratch.numel()} floats, {need} needed")
     if block_table.stride(1) != 1:
         raise KernelError("block_table rows must be contiguous")
+    counters = _merge_counter(qkv.device, n_list * n_kv_heads) \
+        if merge_inside and n_splits > 1 else None
     _check(_load(*attention_mma_library(head_dim)).sllm_attn_mma_decode(
         _ptr(qkv), c_int64(qkv.stride(0)), _ptr(pages), _ptr(block_table),
         c_int(block_table.stride(0)), c_int(page_size), _ptr(row_start), _ptr(row_pos0),
         _ptr(row_list), c_int(n_list), _ptr(out), c_int64(out.stride(0)), c_int(n_heads),
         c_int(n_kv_heads), c_float(scale), c_int(window or 0), c_int(n_splits), _ptr(scratch),
         c_int64(n_tokens), _ptr(cos), _ptr(sin), c_int(int(interleaved)), c_int(int(write)),
-        _stream()), "attention_mma_decode")
+        _ptr(counters), _stream()), "attention_mma_decode")
     return out
 
 

@@ -437,6 +437,15 @@ def test_decode_attention_fused_with_rotation(ops, H, G, hd, page, window, n_spl
                              True, n_splits, scratch)
     assert torch.equal(out_b.cpu(), out_a.cpu())
     assert torch.equal(pages_b.cpu(), pages_a.cpu())
+    # (that was with the splits merged inside the kernel by the last CTA to arrive; a merge
+    # kernel after it gives the same bits, and so does a second launch on the same counters)
+    for inside in (False, True):
+        pages_d = pages.clone().cuda()
+        out_d = torch.full((n, H * hd), float("nan"), dtype=torch.bfloat16, device="cuda")
+        ops.attention_mma_decode(qkv.cuda(), pages_d, table.cuda(), page, row_start, row_pos0,
+                                 out_d, rows, n, H, G, hd, scale, window, cos.cuda(), sin.cuda(),
+                                 interleaved, True, n_splits, scratch, merge_inside=inside)
+        assert torch.equal(out_d.cpu(), out_a.cpu())
     # a layer that reads another layer's cache: nothing is stored
     pages_c = pages_a.clone()
     out_c = torch.full((n, H * hd), float("nan"), dtype=torch.bfloat16, device="cuda")
