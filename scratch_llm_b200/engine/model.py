@@ -71,6 +71,13 @@ class DecoderModel:
             block.cache_owner = next((built[r] for r, k in roles.items() if k == "mixer"), None)
             self.blocks.append(block)
         self._positions = list(positions.values())
+        # per run: the (norm, part) the NEXT run's block starts with, for blocks that ask
+        self._next_entry: list = []
+        for i, run in enumerate(spec.order):
+            block = self.blocks[run.layer]
+            nxt = self.blocks[spec.order[i + 1].layer] if i + 1 < len(spec.order) else None
+            entry = nxt.entry() if nxt is not None and hasattr(nxt, "entry") else None
+            self._next_entry.append(entry if getattr(block, "takes_next_entry", False) else None)
         self.final_norm = make(NORMS, "norm", spec.final_norm)
         self._named_parts.append((spec.final_norm_name, self.final_norm))
         self.embedding: torch.Tensor | None = None
@@ -149,12 +156,11 @@ class DecoderModel:
                              block_table=batch.block_tables[group] if group is not None else None,
                              page_size=cache.page_size, state=cache.states[run.cache])
             block = self.blocks[run.layer]
-            if getattr(block, "takes_next_entry", False):
+            if self._next_entry[i] is not None:
                 # what the next run starts with, so that this block's last product may prepare
                 # it (the final norm works on gathered rows: nothing is prepared for it)
-                nxt = self.blocks[s.order[i + 1].layer] if i + 1 < len(s.order) else None
-                entry = nxt.entry() if nxt is not None and hasattr(nxt, "entry") else None
-                pending = block.forward(resid, pending, batch, view, run.write, next_entry=entry)
+                pending = block.forward(resid, pending, batch, view, run.write,
+                                        next_entry=self._next_entry[i])
             else:
                 pending = block.forward(resid, pending, batch, view, run.write)
         if batch.n_out == 0:

@@ -39,6 +39,8 @@ class PreNormBlock(Block):
     def _sink(resid: torch.Tensor, producer, norm, consumer, n_tokens: int):
         """A sink for ``producer``'s output if it, the norm after it and the part after that
         all can hand the norm over (scratch_llm_b200.parts.stream), else None."""
+        if n_tokens > StreamSink.MAX_TOKENS:    # (first: larger steps should pay nothing here)
+            return None
         if norm is None or consumer is None or not getattr(producer, "accepts_sink", False) \
                 or not getattr(norm, "deferrable", False):
             return None

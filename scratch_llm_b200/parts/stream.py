@@ -49,6 +49,9 @@ class Normed:
 class StreamSink:
     """Where a branch's last product may put its output: into ``resid``, prepared for ``norm``."""
 
+    #: steps of more tokens never hand a norm over (the kernels that can are small-batch ones)
+    MAX_TOKENS = 8
+
     def __init__(self, resid: torch.Tensor, norm) -> None:
         self.resid, self.norm = resid, norm
 
