@@ -215,6 +215,32 @@ def test_cutting_does_not_change_bfloat16_logits_beyond_rounding(name, model_dir
             assert tokens == {int(ref.argmax())}, f"{key}: greedy tokens {tokens}"
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_norm_hand_over_where_only_some_products_can(dtype, tmp_path):
+    """A feed-forward width that the persistent small-batch product does not take (1,000 is no
+    multiple of 512): in decode steps the output projection still feeds the residual stream
+    itself and gate/up finishes the norm, while the down projection returns its output as
+    usual and the next layer's norm runs as a kernel.  Logits match the plain model."""
+    from scratch_llm_b200.config import config_from_dict
+    from scratch_llm_b200.kernels import ops
+    from scratch_llm_b200.weights import write_random_model
+    raw = {**CONFIGS["D"], "intermediate_size": 1000, "num_hidden_layers": 3}
+    d = write_random_model(config_from_dict(raw), tmp_path / "odd_ff", 6)
+    cfg, w = P.read_model_dir(d)
+    if dtype == "bfloat16":
+        w = {k: v.to(torch.bfloat16).float() for k, v in w.items()}
+    reqs = T.make_requests(cfg["vocab_size"], [40, 3, 70], seed=9)
+    want = {rid: P.forward(cfg, w, toks) for rid, toks in reqs.items()}
+    steps = T.mixed(reqs, seed=2)
+    runner = make_runner(d, dtype, 16, T.peak_tokens(steps), poison_free_pages=True)
+    before = dict(ops.launch_counts)
+    with torch.no_grad():
+        got = T.run_in_process(runner, steps)
+    compare(got, want, dtype)
+    sinks = ops.launch_counts.get("gemv_tma_sink", 0) - before.get("gemv_tma_sink", 0)
+    assert (sinks > 0) == (dtype == "bfloat16")
+
+
 def test_long_prompt_takes_the_fused_tensor_core_path(tmp_path):
     """A prompt of 1,000 tokens in one step runs gate/up + SwiGLU on the tcgen05 kernel
     (shorter ones use other kernels); its logits still match the plain implementation."""
