@@ -269,6 +269,11 @@ def _sm_count(device: torch.device | int | None = None) -> int:
     return _sm_counts[index]
 
 
+def sm_count(device: torch.device | int | None = None) -> int:
+    """SMs of ``device`` (the current one by default)."""
+    return _sm_count(device)
+
+
 def gemv_tma_supports(m: int, n: int, k: int, swiglu: bool = False) -> bool:
     """Whether :func:`gemv_tma` takes a product of these sizes (on the current device)."""
     return bool(_core("sllm_gemv_tma").sllm_gemv_tma_supports(

@@ -17,11 +17,21 @@ from .stream import Normed
 
 #: up to this many tokens the streaming small-batch kernel runs instead of the library product
 SMALL_BATCH = 8
-#: from this many tokens on, gate/up + SwiGLU run on the fused tcgen05 kernel (measured at
-#: 28672 x 4096: 99.5 against 104.9 us for the library product plus the activation kernel at 448
-#: tokens, 179 against 204 us at 1,024; below it the 256-token tiles of an SM pair leave too many
-#: of the 148 SMs idle: 97.8 against 80.0 us at 384)
+#: gate/up + SwiGLU run on the fused tcgen05 kernel (pairs of SMs, tiles of 256 tokens x 128
+#: features) from FUSED_GEMM_ALWAYS tokens on, and from FUSED_GEMM_MIN_TOKENS on where its tiles
+#: fill the SM pairs' rounds to at least FUSED_GEMM_MIN_FILL (0.85) and the reduction is long enough to
+#: carry a tile's start and end; else the library product plus the activation kernel.  Measured
+#: inside graph replays, fused against library + activation, in us:
+#:   28672 x 4096 (224 tiles up to 512 tokens: 3.03 rounds of 74 pairs, fill 0.76):
+#:       448 tokens 112.8 / 110.7, 512: 119.3 / 109.2, 1,024: 215.7 / 227.5, 2,048: 370 / 427
+#:   27648 x 5120 (216 tiles, 2.92 rounds, fill 0.97): 448: 114.6 / 120.5, 512: 124.8 / 132.9,
+#:       1,024: 235.5 / 233.4, 2,048: 446 / 461
+#:   16384 x 2048 (short reduction): 448: 37.5 / 32.6, 512: 35.8 / 32.4, 768: 46.9 / 46.3,
+#:       1,024: 61.8 / 62.8, 2,048: 105 / 142
 FUSED_GEMM_MIN_TOKENS = 448
+FUSED_GEMM_ALWAYS = 1024
+FUSED_GEMM_MIN_FILL = 0.85
+FUSED_GEMM_MIN_K = 4096
 
 
 class Linear:
@@ -81,6 +91,17 @@ class Linear:
             return torch.mm(x, w.t(), out_dtype=torch.float32)
         return torch.mm(x, w.t())
 
+    def _fused_pays(self, m: int, half: int) -> bool:
+        """Whether gate/up + SwiGLU of ``m`` tokens is faster on the fused tcgen05 kernel than
+        as library product + activation kernel (see FUSED_GEMM_MIN_TOKENS)."""
+        if m >= FUSED_GEMM_ALWAYS:
+            return True
+        if m < FUSED_GEMM_MIN_TOKENS or self.in_features < FUSED_GEMM_MIN_K:
+            return False
+        pairs = max(1, ops.sm_count(self.weight.device) // 2)
+        tiles = -(-m // 256) * -(-half // 128)
+        return tiles / (-(-tiles // pairs) * pairs) >= FUSED_GEMM_MIN_FILL
+
     def swiglu(self, x: torch.Tensor) -> torch.Tensor:
         """For a weight [gate rows; up rows]: silu(x gate^T) * (x up^T), fused where a kernel
         takes the shape."""
@@ -99,7 +120,7 @@ class Linear:
             if self._persistent_swiglu:
                 return ops.gemv_tma(x, w, out, swiglu=True)
             return ops.gemv_mma(x, w, out, swiglu=True)
-        if fits and x.shape[0] >= FUSED_GEMM_MIN_TOKENS and half % 8 == 0:
+        if fits and half % 8 == 0 and self._fused_pays(x.shape[0], half):
             # tcgen05 kernel with the activation in its epilogue: the [tokens, 2F] intermediate
             # is never written
             return ops.gemm_tc(x, w, out, swiglu=True)

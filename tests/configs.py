@@ -21,7 +21,7 @@ TINY_C = dict(architectures=["LlamaForCausalLM"], hidden_size=120, num_hidden_la
 TINY_D = dict(architectures=["LlamaForCausalLM"], hidden_size=1024, num_hidden_layers=2,
               num_attention_heads=8, num_key_value_heads=2, head_dim=128, intermediate_size=1536,
               vocab_size=1000, rope_theta=500000.0, rms_norm_eps=1e-5, tie_word_embeddings=False,
-              max_position_embeddings=1024, torch_dtype="float32")
+              max_position_embeddings=2048, torch_dtype="float32")
 PAGE_SIZE = {"A": 16, "B": 8, "C": 16, "D": 16}
 SEED = {"A": 0, "B": 1, "C": 2, "D": 3}
 CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}

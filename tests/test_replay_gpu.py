@@ -66,10 +66,15 @@ def compare(got, want_logits, dtype):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name, page", [("A", 16), ("B", 8), ("C", 16), ("D", 16), ("D", 64)])
 @pytest.mark.parametrize("way", ["whole", "tail", "portions", "mixed"])
-def test_replay_matches_plain(way, name, page, dtype, model_dirs, expected):
+def test_replay_matches_plain(way, name, page, dtype, model_dirs, expected, monkeypatch):
     """Free pages hold NaN (the pool at the start, and every page that is given back): a
     kernel that lets a place beyond a request's context reach a result fails here."""
     from scratch_llm_b200.kernels import ops
+    from scratch_llm_b200.parts import linear
+    if name == "D":
+        # the fused tcgen05 gate/up product would wait for 1,024 tokens at D's short reduction
+        # (a choice of speed): here it runs from 448 on, as it does at the full-size widths
+        monkeypatch.setattr(linear, "FUSED_GEMM_ALWAYS", linear.FUSED_GEMM_MIN_TOKENS)
     reqs, want = expected(name, dtype)
     steps = ways(name)[way](reqs)
     peak = T.peak_tokens(steps, round_to=max(64, page))
@@ -105,11 +110,13 @@ def is_large_mixed(step):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_large_mixed_steps(dtype, model_dirs):
+def test_large_mixed_steps(dtype, model_dirs, monkeypatch):
     """Steps of several hundred tokens that hold two or three long prompt portions beside
     decoded tokens of other requests, as a scheduler with a large token budget builds them all
     the time; pages are used again and free pages hold NaN."""
     from scratch_llm_b200.kernels import ops
+    from scratch_llm_b200.parts import linear
+    monkeypatch.setattr(linear, "FUSED_GEMM_ALWAYS", linear.FUSED_GEMM_MIN_TOKENS)
     cfg, w = P.read_model_dir(model_dirs["D"])
     if dtype == "bfloat16":
         w = {k: v.to(torch.bfloat16).float() for k, v in w.items()}
@@ -241,7 +248,7 @@ def test_norm_hand_over_where_only_some_products_can(dtype, tmp_path):
     assert (sinks > 0) == (dtype == "bfloat16")
 
 
-def test_long_prompt_takes_the_fused_tensor_core_path(tmp_path):
+def test_long_prompt_takes_the_fused_tensor_core_path(tmp_path, monkeypatch):
     """A prompt of 1,000 tokens in one step runs gate/up + SwiGLU on the tcgen05 kernel
     (shorter ones use other kernels); its logits still match the plain implementation."""
     from scratch_llm_b200.config import config_from_dict
@@ -253,7 +260,8 @@ def test_long_prompt_takes_the_fused_tensor_core_path(tmp_path):
     cfg, w = P.read_model_dir(d)
     w = {k: v.to(torch.bfloat16).float() for k, v in w.items()}
     reqs = T.make_requests(cfg["vocab_size"], [1000], seed=4)
-    assert 1000 >= linear.FUSED_GEMM_MIN_TOKENS
+    monkeypatch.setattr(linear, "FUSED_GEMM_ALWAYS", linear.FUSED_GEMM_MIN_TOKENS)
+    assert 1000 >= linear.FUSED_GEMM_ALWAYS
     want = {rid: P.forward(cfg, w, toks) for rid, toks in reqs.items()}
     steps = T.whole(reqs)
     for s in steps:   # logits at a few places only: the first, one in the middle, the last 40
