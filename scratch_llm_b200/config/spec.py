@@ -77,8 +77,16 @@ class ModelSpec:
     final_norm_name: str
     lm_head_name: str
     tie_embeddings: bool
+    #: the embedded tokens are multiplied by this before the first layer
+    embedding_multiplier: float = 1.0
+    #: the logits are multiplied by this, and then, if ``logit_softcap`` > 0, squashed to
+    #: ``logit_softcap * tanh(logits / logit_softcap)``
+    logit_scale: float = 1.0
+    logit_softcap: float = 0.0
 
     def __post_init__(self) -> None:
+        if self.logit_softcap < 0:
+            raise ValueError(f"logit_softcap must not be negative, got {self.logit_softcap}")
         seen_write: set[int] = set()
         for run in self.order:
             if not 0 <= run.layer < len(self.layers):

@@ -8,11 +8,12 @@
 
 namespace sllm {
 
-// out[n, :] = table[ids[n], :] as float.  One block per token.  An id -1 - j stands for
-// pending[j]: a token that an earlier kernel of the stream chose and the host has not read yet.
+// out[n, :] = table[ids[n], :] as float, times scale.  One block per token.  An id -1 - j stands
+// for pending[j]: a token that an earlier kernel of the stream chose and the host has not read yet.
 template <typename T>
 __global__ void embed_kernel(const int* __restrict__ ids, const int* __restrict__ pending,
-                             const T* __restrict__ table, float* __restrict__ out, int d) {
+                             const T* __restrict__ table, float* __restrict__ out, int d,
+                             float scale) {
     pdl_wait();
     pdl_trigger();
     const int64_t n = blockIdx.x;
@@ -20,7 +21,20 @@ __global__ void embed_kernel(const int* __restrict__ ids, const int* __restrict_
     if (id < 0) id = pending[-1 - id];
     const T* src = table + (int64_t)id * d;
     float* dst = out + n * d;
-    for (int i = threadIdx.x; i < d; i += blockDim.x) dst[i] = to_float(src[i]);
+    for (int i = threadIdx.x; i < d; i += blockDim.x) dst[i] = to_float(src[i]) * scale;
+}
+
+// x = cap * tanh(x * scale / cap) in place (cap > 0), or x * scale (cap == 0): what some
+// architectures do to their logits before sampling.
+__global__ void logit_cap_kernel(float* __restrict__ x, int64_t n, float scale, float cap) {
+    pdl_wait();
+    pdl_trigger();
+    const float inv = cap > 0.f ? 1.f / cap : 0.f;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const float v = x[i] * scale;
+        x[i] = cap > 0.f ? cap * tanhf(v * inv) : v;
+    }
 }
 
 // If delta != nullptr: resid[row] += delta[row] (stored back).  Then
@@ -207,17 +221,26 @@ static int norm_threads(int d) {
 
 // dtype: 0 = float32, 1 = bfloat16 (of table / delta / out / gu).
 // `pending` may be null if no id is negative.
+SLLM_EXPORT int sllm_logit_cap(float* x, int64_t n, float scale, float cap, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (cap < 0.f) return (int)cudaErrorInvalidValue;
+    const int blocks = (int)((n + 1023) / 1024 < 4096 ? (n + 1023) / 1024 : 4096);
+    logit_cap_kernel<<<blocks, 256, 0, stream>>>(x, n, scale, cap);
+    SLLM_LAUNCH_CHECK();
+    return 0;
+}
+
 SLLM_EXPORT int sllm_embed(const int* ids, const int* pending, const void* table, float* out,
-                           int n_tokens, int d, int dtype, cudaStream_t stream) {
+                           int n_tokens, int d, int dtype, float scale, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (d <= 0) return (int)cudaErrorInvalidValue;
     const int threads = norm_threads(d);
     if (dtype == 0)
         embed_kernel<float><<<n_tokens, threads, 0, stream>>>(ids, pending, (const float*)table, out,
-                                                              d);
+                                                              d, scale);
     else if (dtype == 1)
         embed_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(
-            ids, pending, (const __nv_bfloat16*)table, out, d);
+            ids, pending, (const __nv_bfloat16*)table, out, d, scale);
     else
         return (int)cudaErrorInvalidValue;
     SLLM_LAUNCH_CHECK();

@@ -148,7 +148,8 @@ class DecoderModel:
         s = self.spec
         resid = torch.empty((batch.n_tokens, s.hidden_size), dtype=torch.float32,
                             device=self.ctx.device)
-        ops.embed(batch.token_ids, self.embedding, resid, batch.pending_tokens)
+        ops.embed(batch.token_ids, self.embedding, resid, batch.pending_tokens,
+                  scale=s.embedding_multiplier)
         pending = None
         for i, run in enumerate(s.order):
             pages, group = cache.entry_pages(run.cache)
@@ -166,7 +167,10 @@ class DecoderModel:
         if batch.n_out == 0:
             return None
         h = self.final_norm.forward(resid, pending, out_rows=batch.logit_index)
-        return self.lm_head(h, out_dtype=torch.float32)
+        logits = self.lm_head(h, out_dtype=torch.float32)
+        if s.logit_scale != 1.0 or s.logit_softcap > 0:
+            ops.logit_cap(logits, s.logit_scale, s.logit_softcap)
+        return logits
 
 
 def build_model(config) -> DecoderModel:

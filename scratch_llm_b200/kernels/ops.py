@@ -147,8 +147,9 @@ def _code(dtype: torch.dtype) -> int:
 # ------------------------------------------------------------------------------ elementwise
 
 def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor,
-          pending: torch.Tensor | None = None) -> torch.Tensor:
-    """out[n] = table[ids[n]] widened to 32-bit.  ids int32 [N]; table [V, d]; out f32 [N, d].
+          pending: torch.Tensor | None = None, scale: float = 1.0) -> torch.Tensor:
+    """out[n] = table[ids[n]] widened to 32-bit, times ``scale`` (an architecture's embedding
+    multiplier).  ids int32 [N]; table [V, d]; out f32 [N, d].
     An id ``-1 - j`` stands for ``pending[j]`` (int32, on the device): a token that an earlier
     kernel of the stream chose and the host has not read yet."""
     _need(ids, torch.int32, "ids")
@@ -161,8 +162,22 @@ def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor,
         raise KernelError(f"out must be [{n}, {d}], got {list(out.shape)}")
     _check(_core("sllm_elementwise").sllm_embed(
         _ptr(ids), _ptr(pending) if pending is not None else c_void_p(0), _ptr(table), _ptr(out),
-        c_int(n), c_int(d), c_int(_code(table.dtype)), _stream()), "embed")
+        c_int(n), c_int(d), c_int(_code(table.dtype)), c_float(scale), _stream()), "embed")
     return out
+
+
+def logit_cap(logits: torch.Tensor, scale: float = 1.0, cap: float = 0.0) -> torch.Tensor:
+    """In place on 32-bit logits: ``cap * tanh(logits * scale / cap)``, or ``logits * scale``
+    when ``cap`` is 0."""
+    _need(logits, torch.float32, "logits")
+    if not logits.is_contiguous():
+        raise KernelError("logits must be contiguous")
+    if cap < 0:
+        raise KernelError(f"cap must not be negative, got {cap}")
+    _check(_core("sllm_elementwise").sllm_logit_cap(
+        _ptr(logits), c_int64(logits.numel()), c_float(scale), c_float(cap), _stream()),
+        "logit_cap")
+    return logits
 
 
 def add_rmsnorm(resid: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor,

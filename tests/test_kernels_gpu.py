@@ -47,6 +47,16 @@ def test_embed(ops, dtype):
     out = torch.empty(5, 200, dtype=torch.float32, device="cuda")
     ops.embed(ids.cuda(), table.cuda(), out)
     assert torch.equal(out.cpu(), P.embed(ids.long(), table).float())
+    ops.embed(ids.cuda(), table.cuda(), out, scale=200 ** 0.5)
+    assert torch.equal(out.cpu(), P.embed(ids.long(), table).float() * torch.tensor(200 ** 0.5))
+
+
+@pytest.mark.parametrize("scale, cap", [(1.0, 30.0), (0.25, 0.0), (3.0, 1.5)])
+def test_logit_cap(ops, scale, cap):
+    x = rand(7, 1001, seed=4) * 20
+    got = ops.logit_cap(x.cuda().clone(), scale, cap).cpu()
+    want = cap * torch.tanh(x * scale / cap) if cap else x * scale
+    torch.testing.assert_close(got, want, rtol=1e-5, atol=1e-5)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

@@ -691,3 +691,104 @@ def test_windowed_and_full_layers_share_a_model(dtype, tol, tmp_path):
                                        msg=lambda m: f"{way.__name__} {rid} {pos}: {m}")
         assert not runner.cache.requests and all(
             g.pool.n_free == g.pool.n_pages for g in runner.cache.groups)
+
+
+# --------------------------- the constants around the layers: embedding multiplier, logit cap
+
+def make_toy_scaled():
+    """An architecture of the framework's own parts that multiplies its embedded tokens, scales
+    its logits and squashes them: the three constants a :class:`ModelSpec` has beside its
+    layers."""
+    from scratch_llm_b200.config import register_architecture, ARCHITECTURES
+    from scratch_llm_b200.config.spec import ModelSpec, PartSpec, sequential_order, standard_layer
+
+    if "ToyScaledForCausalLM" not in ARCHITECTURES:
+        @dataclass(frozen=True)
+        class ToyScaledConfig:
+            width: int
+            n_vocab: int
+            multiplier: float
+            logit_scale: float
+            cap: float
+            architecture = "ToyScaledForCausalLM"
+
+            @classmethod
+            def from_dict(cls, raw):
+                return cls(raw["width"], raw["n_vocab"], raw["multiplier"], raw["logit_scale"],
+                           raw["cap"])
+
+            def to_dict(self):
+                return {"architectures": [self.architecture], "width": self.width,
+                        "n_vocab": self.n_vocab, "multiplier": self.multiplier,
+                        "logit_scale": self.logit_scale, "cap": self.cap}
+
+            def model_spec(self):
+                d = self.width
+                norm = PartSpec("rmsnorm", {"size": d, "eps": 1e-5})
+                att = PartSpec("gqa_attention", {"hidden_size": d, "n_heads": 4, "n_kv_heads": 2,
+                                                 "head_dim": 16, "scale": 0.25, "window": None})
+                ff = PartSpec("swiglu", {"hidden_size": d, "intermediate_size": 72})
+                rope = PartSpec("rotary", {"head_dim": 16, "theta": 1000.0, "max_position": 256})
+                names = {"mixer": "mixer", "feed_forward": "ff", "mixer_norm": "n1",
+                         "feed_forward_norm": "n2"}
+                layers = tuple(standard_layer(f"l{i}", "pre_norm", att, ff, norm, norm, rope, names)
+                               for i in range(2))
+                return ModelSpec(d, self.n_vocab, 256, layers, sequential_order(2), norm,
+                                 "emb.weight", "out_norm", "head.weight", tie_embeddings=False,
+                                 embedding_multiplier=self.multiplier,
+                                 logit_scale=self.logit_scale, logit_softcap=self.cap)
+
+        register_architecture("ToyScaledForCausalLM", ToyScaledConfig)
+    return ARCHITECTURES["ToyScaledForCausalLM"].config_cls
+
+
+def toy_scaled_plain(cfg, w, ids):
+    d, hd = cfg.width, 16
+    x = w["emb.weight"][torch.tensor(ids)] * cfg.multiplier
+    pos = torch.arange(len(ids))
+    cos, sin = P.rope_tables(hd, 256, 1000.0)
+    for i in range(2):
+        acfg = dict(num_attention_heads=4, num_key_value_heads=2, head_dim=hd, hidden_size=d,
+                    sliding_window=None)
+        a, _ = P.attention_layer(P.rmsnorm(x, w[f"l{i}.n1.weight"], 1e-5), pos, w, f"l{i}.mixer",
+                                 acfg, cos, sin)
+        x = x + a
+        x = x + P.swiglu(P.rmsnorm(x, w[f"l{i}.n2.weight"], 1e-5), w[f"l{i}.ff.gate_proj.weight"],
+                         w[f"l{i}.ff.up_proj.weight"], w[f"l{i}.ff.down_proj.weight"])
+    logits = P.rmsnorm(x, w["out_norm.weight"], 1e-5) @ w["head.weight"].T * cfg.logit_scale
+    return cfg.cap * torch.tanh(logits / cfg.cap) if cfg.cap > 0 else logits
+
+
+@pytest.mark.parametrize("cap", [0.0, 1.5])
+@pytest.mark.parametrize("dtype, tol", [("float32", dict(rtol=1e-4, atol=2e-5)),
+                                        ("bfloat16", dict(rtol=3e-2, atol=3e-2))])
+def test_embedding_multiplier_and_logit_cap(dtype, tol, cap, tmp_path):
+    """The constants a model has around its layers are the spec's, not the engine's: embedded
+    tokens times a multiplier, logits times a scale and squashed by a tanh (or not)."""
+    import trace_util as T
+    from scratch_llm_b200.engine import ModelRunner, load_model
+    from scratch_llm_b200.weights import write_random_model
+    Toy = make_toy_scaled()
+    cfg = Toy(width=48, n_vocab=80, multiplier=48 ** 0.5, logit_scale=3.0, cap=cap)
+    d = write_random_model(cfg, tmp_path / "toy_scaled", seed=21, std=0.08, dtype="float32")
+    _, w = P.read_model_dir(d)
+    if dtype == "bfloat16":
+        w = {k: (v if k.endswith(("n1.weight", "n2.weight", "out_norm.weight"))
+                 else v.to(torch.bfloat16).float()) for k, v in w.items()}
+    model = load_model(d, dtype, verbose=False)
+    reqs = T.make_requests(80, [40, 7, 70], seed=9)
+    want = {rid: toy_scaled_plain(cfg, w, toks) for rid, toks in reqs.items()}
+    # each constant matters: without it the logits move by far more than the tolerance
+    some = list(reqs)[0]
+    for other in (Toy(48, 80, 1.0, 3.0, cap), Toy(48, 80, 48 ** 0.5, 1.0, cap),
+                  Toy(48, 80, 48 ** 0.5, 3.0, 0.0 if cap else 1.5)):
+        assert float((toy_scaled_plain(other, w, reqs[some]) - want[some]).abs().max()) > 0.1
+    for way in (T.whole, T.tail_one_by_one, T.mixed):
+        steps = way(reqs)
+        runner = ModelRunner(model, 8, -(-T.peak_tokens(steps) // 8), 4)
+        runner.capture_padded_after = 2
+        with torch.no_grad():
+            got = T.run_in_process(runner, steps)
+        for (rid, pos), row in got.items():
+            torch.testing.assert_close(row, want[rid][pos], **tol,
+                                       msg=lambda m: f"{way.__name__} {rid} {pos}: {m}")
