@@ -103,8 +103,6 @@ class LLM:
         return Scheduler(self.runner.cache, self.runner.max_position, self.max_batch_tokens,
                          self.chunk_size, self.admission, self.runner.vocab_size, policy)
 
-    # ------------------------------------------------------------------------------ serve
-
     # ------------------------------------------------------------------- submit and step
 
     def submit(self, request: Request) -> None:
@@ -254,7 +252,6 @@ class LLM:
         if single:
             return toks[0], (lps[0] if lps else None)
         return toks, lps
-
 
     # ------------------------------------------------------------------------------ score
 
