@@ -78,11 +78,12 @@ class Linear:
             out = torch.empty((x.shape[0], self.out_features), dtype=torch.float32,
                               device=x.device)
             return ops.gemm_simt(x, w, out)
-        # every CTA of the streaming kernel re-reads all activations, which costs as much as the
-        # weights once the output is very wide and several tokens are in flight
         if self._persistent and x.shape[0] <= SMALL_BATCH and x.stride(0) % 8 == 0:
             out = torch.empty((x.shape[0], self.out_features), dtype=out_dtype, device=x.device)
             return ops.gemv_tma(x, w, out)
+        # shapes the persistent kernel does not take: every CTA of the older streaming kernel
+        # re-reads all activations, which costs as much as the weights once the output is very
+        # wide and several tokens are in flight
         streams = x.shape[0] <= SMALL_BATCH and (x.shape[0] <= 2 or self.out_features <= 65536)
         if streams and self.in_features % 8 == 0 and x.stride(0) % 8 == 0:
             out = torch.empty((x.shape[0], self.out_features), dtype=out_dtype, device=x.device)
