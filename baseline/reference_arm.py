@@ -164,14 +164,14 @@ class _Arm:
         wall = time.perf_counter() - t0
         return wall * 1e3 / steps, batch * 8, batch * 8
 
-    def time_prefill(self, tokens: int, reps: int = 5):
+    def time_prefill(self, tokens: int, reps: int = 9):
         torch = self.torch
         from scratch_llm.model import PagedKVCache, PrefillView
 
         prompt = torch.tensor(_prompts(1, tokens, self.cfg.vocab_size, 7), dtype=torch.long,
                               device=self.device)
         times = []
-        for r in range(reps + 2):
+        for r in range(reps + 3):
             cache = PagedKVCache(n_layers=self.cfg.n_layers, n_slots=1,
                                  n_kv_heads=self.cfg.kv_heads, max_ctx=self.cfg.context_length,
                                  head_dim=self.cfg.head_dim,
@@ -185,7 +185,7 @@ class _Arm:
                 logits[0, tokens - 1].argmax()
             e1.record()
             torch.cuda.synchronize()
-            if r >= 2:
+            if r >= 3:
                 times.append(e0.elapsed_time(e1))
             del logits, cache
         return times

@@ -180,8 +180,8 @@ def time_decode_e2e(llm, cfg, batch: int, context: int, steps: int, warmup: int)
     return wall * 1e3 / steps, h2d, d2h
 
 
-def time_prefill(llm, cfg, tokens: int, reps: int = 5):
-    """Times of `reps` prompt steps of `tokens` tokens (after two untimed ones), each from an
+def time_prefill(llm, cfg, tokens: int, reps: int = 9):
+    """Times of `reps` prompt steps of `tokens` tokens (after three untimed ones), each from an
     empty cache."""
     import torch
 
@@ -190,7 +190,7 @@ def time_prefill(llm, cfg, tokens: int, reps: int = 5):
     runner = llm.runner
     prompt = random_prompts(1, tokens, cfg.vocab_size, seed=7)[0]
     times = []
-    for r in range(reps + 2):
+    for r in range(reps + 3):
         assert runner.admit("prefill")
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
@@ -198,7 +198,7 @@ def time_prefill(llm, cfg, tokens: int, reps: int = 5):
         runner.step([RowInput("prefill", prompt, [tokens - 1])])
         e1.record()
         torch.cuda.synchronize()
-        if r >= 2:
+        if r >= 3:
             times.append(e0.elapsed_time(e1))
         runner.release("prefill")
     return times
