@@ -41,18 +41,21 @@ constexpr size_t TC_SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /
 // Writes 32 consecutive outputs of one row; `n_valid` of them exist.
 __device__ __forceinline__ void store_row32(bf16* dst, const float (&o)[32], int n_valid,
                                             bool aligned) {
-    if (n_valid >= 32 && aligned) {
+    // whole groups of 8 as 16-byte stores, the rest one by one
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < 4; ++i) {
+        if (aligned && n_valid >= 8 * (i + 1)) {
             uint4 q;
             q.x = pack2(o[8 * i + 0], o[8 * i + 1]);
             q.y = pack2(o[8 * i + 2], o[8 * i + 3]);
             q.z = pack2(o[8 * i + 4], o[8 * i + 5]);
             q.w = pack2(o[8 * i + 6], o[8 * i + 7]);
             reinterpret_cast<uint4*>(dst)[i] = q;
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (8 * i + j < n_valid) dst[8 * i + j] = __float2bfloat16_rn(o[8 * i + j]);
         }
-    } else {
-        for (int i = 0; i < 32 && i < n_valid; ++i) dst[i] = __float2bfloat16_rn(o[i]);
     }
 }
 
@@ -178,12 +181,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                     }
                 }
             } else {
-                const int f0 = n_blk * 128;
+                constexpr int bn = 128;     // features per tile of this kernel
+                const int f0 = n_blk * bn;
 #pragma unroll 1
-                for (int c = 0; c < 4; ++c) {
+                for (int c = 0; c * 32 < bn; ++c) {
                     uint32_t gv[32], uv[32];
                     tmem_ld32(lane_addr + c * 32, gv);
-                    tmem_ld32(lane_addr + 128 + c * 32, uv);
+                    tmem_ld32(lane_addr + bn + c * 32, uv);
                     tmem_ld_wait();
                     const int col = f0 + c * 32;
                     if (row < M && col < n_half) {
@@ -277,11 +281,15 @@ __device__ __forceinline__ void cluster_barrier_all() {
 }
 
 // tiles_m counts blocks of 256 tokens here.  gridDim.x = 2 * number of clusters.
+// `bn`: rows of W that each CTA of the pair contributes to a tile (the instruction's N is
+// 2 * bn; map_w's box has bn rows).  Plain products use 128.  With SWIGLU a tile is bn features
+// (CTA 0 brings their gate rows, CTA 1 their up rows), and bn may be any multiple of 16 up to
+// 128: the launcher picks the one whose tiles fill the pairs' rounds best.
 template <bool SWIGLU>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                 bf16* __restrict__ Y, int M, int N, int K, int64_t ldy, int n_half, int tiles_m,
-                int tiles_n) {
+                int tiles_n, int bn) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(
         ((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -328,14 +336,14 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             bool ok = true;
             for (int tile = cluster; tile < total_tiles && ok; tile += n_clusters) {
                 const int m0 = (tile % tiles_m) * (2 * TM) + (int)rank * TM, n_blk = tile / tiles_m;
-                const int w_row = SWIGLU ? (rank == 0 ? n_blk * 128 : n_half + n_blk * 128)
+                const int w_row = SWIGLU ? (rank == 0 ? n_blk * bn : n_half + n_blk * bn)
                                          : n_blk * TN + (int)rank * 128;
                 for (int kb = 0; kb < k_blocks; ++kb, ++it) {
                     const int s = it % STAGES2;
                     ok = mbar_wait(&empty[s], ((it / STAGES2) & 1) ^ 1, 1);
                     if (!ok) break;
                     // CTA 0 announces the bytes of both CTAs
-                    if (rank == 0) mbar_expect_tx(&full[s], 2 * STAGE2_BYTES);
+                    if (rank == 0) mbar_expect_tx(&full[s], 2 * (A_BYTES + bn * TK * 2));
                     tma_load_2d_pair(a_stage + s * A_BYTES, &map_x, leader_addr(&full[s]), kb * TK, m0);
                     tma_load_2d_pair(b_stage + s * B_HALF_BYTES, &map_w, leader_addr(&full[s]), kb * TK,
                                      w_row);
@@ -344,7 +352,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         }
     } else if (warp == 1) {
         if (lane == 0 && rank == 0) {
-            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TN >> 3) << 17) |
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) |
+                                   ((uint32_t)((2 * bn) >> 3) << 17) |
                                    ((uint32_t)((2 * TM) >> 4) << 24);
             uint32_t it = 0, local = 0;
             bool ok = true;
@@ -396,12 +405,14 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                     }
                 }
             } else {
-                const int f0 = n_blk * 128;
+                // gate at columns 0..bn-1 of the buffer, up at bn..2 bn - 1 (a last chunk of 16
+                // features reads 16 columns more than it keeps)
+                const int f0 = n_blk * bn;
 #pragma unroll 1
-                for (int c = 0; c < 4; ++c) {
+                for (int c = 0; c * 32 < bn; ++c) {
                     uint32_t gv[32], uv[32];
                     tmem_ld32(lane_addr + c * 32, gv);
-                    tmem_ld32(lane_addr + 128 + c * 32, uv);
+                    tmem_ld32(lane_addr + bn + c * 32, uv);
                     tmem_ld_wait();
                     const int col = f0 + c * 32;
                     if (row < M && col < n_half) {
@@ -413,7 +424,9 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                             const float u = __bfloat162float(__float2bfloat16_rn(__uint_as_float(uv[i])));
                             o[i] = g / (1.0f + __expf(-g)) * u;
                         }
-                        store_row32(Y + (int64_t)row * ldy + col, o, n_half - col, aligned);
+                        const int keep = bn - c * 32;    // features of this tile left from col on
+                        store_row32(Y + (int64_t)row * ldy + col, o,
+                                    n_half - col < keep ? n_half - col : keep, aligned);
                     }
                 }
             }
@@ -450,13 +463,15 @@ static EncodeTiledFn encode_fn() {
     return fn;
 }
 
-// A [rows, K] bfloat16 matrix with row stride ld, boxes of 128 rows x 64 columns, 128-byte swizzle.
-static bool make_map(CUtensorMap* map, const void* base, int rows, int K, int64_t ld) {
+// A [rows, K] bfloat16 matrix with row stride ld, boxes of box_rows rows x 64 columns, 128-byte
+// swizzle.
+static bool make_map(CUtensorMap* map, const void* base, int rows, int K, int64_t ld,
+                     int box_rows = 128) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return false;
     cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
     cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    cuuint32_t box[2] = {(cuuint32_t)TK, 128u};
+    cuuint32_t box[2] = {(cuuint32_t)TK, (cuuint32_t)box_rows};
     cuuint32_t elem[2] = {1u, 1u};
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
               elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -468,6 +483,31 @@ static bool make_map(CUtensorMap* map, const void* base, int rows, int K, int64_
 using namespace sllm;
 
 static int g_gemm_pairs = 1;
+static int g_gemm_tile = 0;
+// Features per tile of the pair kernel's fused gate/up product: 0 (default) lets the launcher
+// choose, else a multiple of 16 from 16 to 128.
+SLLM_EXPORT void sllm_gemm_tc_set_tile(int features) {
+    g_gemm_tile = (features >= 16 && features <= 128 && features % 16 == 0) ? features : 0;
+}
+
+// The tile width (features) the pair kernel uses for gate/up + SwiGLU of M tokens and n_half
+// features on n_pairs SM pairs.  A tile is 256 tokens x bn features and every pair works
+// through ceil(tiles / pairs) tiles.  112 instead of 128 is taken where it needs no more
+// rounds: every round is then an eighth shorter.  Measured (us, 128 / 112): 14336 features x
+// 4096 at 1,024 tokens, 7 rounds either way, 204 / 178; at 512 tokens 120 / 116; 8192 x 2048 at
+// 448 tokens 40.7 / 38.0.  Where 112 needs a round more it loses although the rounds are
+// shorter (2,048 tokens: 13 rounds of 128 take 329, 14 rounds of 112 take 366), because full
+// rounds are bound by what the SMs fetch, and narrower tiles fetch the activations more often;
+// widths below 112 lost everywhere.
+SLLM_EXPORT int sllm_gemm_tc_swiglu_tile(int M, int n_half, int n_pairs) {
+    if (g_gemm_tile) return g_gemm_tile;
+    if (M <= 0 || n_half <= 0 || n_pairs <= 0) return 128;
+    const int64_t tiles_m = (M + 2 * TM - 1) / (2 * TM);
+    const int64_t rounds128 = (tiles_m * ((n_half + 127) / 128) + n_pairs - 1) / n_pairs;
+    const int64_t rounds112 = (tiles_m * ((n_half + 111) / 112) + n_pairs - 1) / n_pairs;
+    return rounds112 <= rounds128 ? 112 : 128;
+}
+
 // 1 (default): tiles of 256 tokens on pairs of SMs (cta_group::2); 0: tiles of 128 tokens on
 // single SMs.
 SLLM_EXPORT void sllm_gemm_tc_set_pairs(int on) { g_gemm_pairs = on ? 1 : 0; }
@@ -493,13 +533,6 @@ SLLM_EXPORT int sllm_gemm_tc(const void* X, const void* W, void* Y, int M, int N
         return (int)cudaErrorInvalidValue;
     if (((uintptr_t)X & 15) || ((uintptr_t)W & 15) || ((uintptr_t)Y & 1))
         return (int)cudaErrorInvalidValue;
-    CUtensorMap map_x, map_w;
-    if (!make_map(&map_x, X, M, K, ldx) || !make_map(&map_w, W, N, K, ldw))
-        return (int)cudaErrorNotSupported;
-    const int n_half = N / 2;
-    const int tiles_n = swiglu ? (n_half + 127) / 128 : (N + TN - 1) / TN;
-    const int tiles_m = (M + TM - 1) / TM;
-    if ((int64_t)tiles_m * tiles_n > 0x7fffffff) return (int)cudaErrorInvalidValue;
     static int n_sm = 0;
     if (!n_sm) {
         int dev = 0;
@@ -507,7 +540,17 @@ SLLM_EXPORT int sllm_gemm_tc(const void* X, const void* W, void* Y, int M, int N
             cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
             return (int)cudaErrorUnknown;
     }
-    if (g_gemm_pairs && n_sm >= 2) {
+    const bool pairs = g_gemm_pairs && n_sm >= 2;
+    const int n_half = N / 2;
+    // rows of W per CTA and tile: 128, or the fused gate/up product's chosen width on pairs
+    const int bn = (swiglu && pairs) ? sllm_gemm_tc_swiglu_tile(M, n_half, n_sm / 2) : 128;
+    CUtensorMap map_x, map_w;
+    if (!make_map(&map_x, X, M, K, ldx) || !make_map(&map_w, W, N, K, ldw, bn))
+        return (int)cudaErrorNotSupported;
+    const int tiles_n = swiglu ? (n_half + bn - 1) / bn : (N + TN - 1) / TN;
+    const int tiles_m = (M + TM - 1) / TM;
+    if ((int64_t)tiles_m * tiles_n > 0x7fffffff) return (int)cudaErrorInvalidValue;
+    if (pairs) {
         // pairs of SMs: tiles of 256 tokens
         const int tiles_m2 = (M + 2 * TM - 1) / (2 * TM);
         const int total2 = tiles_m2 * tiles_n;
@@ -531,13 +574,13 @@ SLLM_EXPORT int sllm_gemm_tc(const void* X, const void* W, void* Y, int M, int N
                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC2_SMEM);
             if (e2 != cudaSuccess) return (int)e2;
             e2 = cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<true>, map_x, map_w, (bf16*)Y, M, N, K, ldy,
-                                    n_half, tiles_m2, tiles_n);
+                                    n_half, tiles_m2, tiles_n, bn);
         } else {
             e2 = cudaFuncSetAttribute(gemm_tc2_kernel<false>,
                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC2_SMEM);
             if (e2 != cudaSuccess) return (int)e2;
             e2 = cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<false>, map_x, map_w, (bf16*)Y, M, N, K, ldy,
-                                    n_half, tiles_m2, tiles_n);
+                                    n_half, tiles_m2, tiles_n, 128);
         }
         return (int)e2;
     }

@@ -404,6 +404,20 @@ def gemm_tc_set_pairs(on: bool) -> None:
     _core("sllm_gemm_tcgen05").sllm_gemm_tc_set_pairs(c_int(int(on)))
 
 
+def gemm_tc_set_tile(features: int | None) -> None:
+    """Features per tile of the pair kernel's fused gate/up product: None lets the launcher
+    choose (the width whose tiles fill the SM pairs' rounds best), else a multiple of 16 from 16
+    to 128."""
+    _core("sllm_gemm_tcgen05").sllm_gemm_tc_set_tile(c_int(int(features or 0)))
+
+
+def gemm_tc_swiglu_tile(m: int, half: int, pairs: int) -> int:
+    """The tile width the pair kernel uses for gate/up + SwiGLU of ``m`` tokens and ``half``
+    features on ``pairs`` SM pairs."""
+    return int(_core("sllm_gemm_tcgen05").sllm_gemm_tc_swiglu_tile(c_int(m), c_int(half),
+                                                                   c_int(pairs)))
+
+
 def gemm_tc_error() -> int:
     """The first error a bounded wait inside gemm_tc recorded since the last call (0 = none).
     Synchronises the device."""

@@ -18,7 +18,7 @@ from .stream import Normed
 #: up to this many tokens the streaming small-batch kernel runs instead of the library product
 SMALL_BATCH = 8
 #: gate/up + SwiGLU run on the fused tcgen05 kernel (pairs of SMs, tiles of 256 tokens x 128
-#: features) from FUSED_GEMM_ALWAYS tokens on, and from FUSED_GEMM_MIN_TOKENS on where its tiles
+#: features, or x 112 where that needs no more rounds of tiles) from FUSED_GEMM_ALWAYS tokens on, and from FUSED_GEMM_MIN_TOKENS on where its tiles
 #: fill the SM pairs' rounds to at least FUSED_GEMM_MIN_FILL (0.85) and the reduction is long enough to
 #: carry a tile's start and end; else the library product plus the activation kernel.  Measured
 #: inside graph replays, fused against library + activation, in us:

@@ -273,6 +273,32 @@ def test_gemm_tcgen05(ops, m, n, k, pairs):
         ops.gemm_tc_set_pairs(True)
 
 
+@pytest.mark.parametrize("tile", [128, 112, 96, 80, 64, 48, 16])
+@pytest.mark.parametrize("m, n, k", [(300, 600, 200), (256, 2 * 112 * 3, 256), (513, 2560, 1024),
+                                     (40, 2 * 1000, 136)])
+def test_gemm_tcgen05_gate_up_tile_widths(ops, m, n, k, tile):
+    """The fused gate/up product on SM pairs with tiles of every width (features per tile): the
+    gate and up halves of a tile sit side by side in tensor memory at the tile's width, a last
+    chunk may hold 16 features, the last tile of a row of tiles may be cut by the matrix."""
+    ops.gemm_tc_set_tile(tile)
+    try:
+        assert ops.gemm_tc_swiglu_tile(m, n // 2, 74) == tile
+        _gemm_tcgen05_case(ops, m, n, k)
+    finally:
+        ops.gemm_tc_set_tile(None)
+
+
+def test_gemm_tcgen05_tile_choice(ops):
+    """The launcher's choice of a tile width: 112 features where that needs no more rounds of
+    tiles than 128."""
+    pick = ops.gemm_tc_swiglu_tile
+    assert pick(1024, 14336, 74) == 112      # 448 or 512 tiles on 74 pairs: 7 rounds either way
+    assert pick(2048, 14336, 74) == 128      # 13 rounds of 128, 14 of 112
+    assert pick(2048, 8192, 74) == 128       # 7 rounds of 128, 8 of 112
+    assert pick(448, 8192, 74) == 112        # 2 rounds either way
+    assert pick(512, 13824, 74) == 128       # 3 rounds of 128, 4 of 112
+
+
 def _gemm_tcgen05_case(ops, m, n, k):
     g = torch.Generator().manual_seed(m + n + k)
     if k <= 256:   # small integers: every product and sum is exact, also in bfloat16
