@@ -229,14 +229,18 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = a.row_list ? a.row_list[blockIdx.y] : blockIdx.y;
-    const int g = blockIdx.z;
+    const int g = blockIdx.x;
     const int GS = a.H / a.G;
     const int t0 = a.row_start[r];
     const int n_new = a.row_start[r + 1] - t0;
     const int pos0 = a.row_pos0[r];
     const int n_packed = n_new * GS;
-    // heavy (late) query tiles first
-    const int q_tile = (int)gridDim.x - 1 - (int)blockIdx.x;
+    // Heavy (late) query tiles first, over ALL rows and kv heads: CTAs start in the order of
+    // blockIdx.x (kv head), then y (row), then z, so z carries the query tile.  (With the tile
+    // in x every kv head's heavy tiles came after the light tiles of the head before, and the
+    // last head's heaviest tile, started late, set the end: 64 us instead of 55 at 2,048
+    // tokens.)
+    const int q_tile = (int)gridDim.z - 1 - (int)blockIdx.z;
     const int q0 = q_tile * TQ;
     if (q0 >= n_packed) return;
     const int tok_first = q0 / GS;
@@ -570,14 +574,14 @@ attn_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = a.row_list ? a.row_list[blockIdx.y] : blockIdx.y;
-    const int g = blockIdx.z;
+    const int g = blockIdx.x;
     const int GS = a.H / a.G;
     const int t0 = a.row_start[r];
     const int n_new = a.row_start[r + 1] - t0;
     const int pos0 = a.row_pos0[r];
     const int n_packed = n_new * GS;
-    // heavy (late) query tiles first
-    const int pair = (int)gridDim.x - 1 - (int)blockIdx.x;
+    // heavy (late) query tiles first, over all rows and kv heads (see attn_tc_kernel)
+    const int pair = (int)gridDim.z - 1 - (int)blockIdx.z;
     const int q0 = pair * 2 * TQ;
     if (q0 >= n_packed) return;
     // per tile: does it exist, its last position, its key tiles
@@ -911,8 +915,10 @@ using namespace sllm;
 SLLM_EXPORT int sllm_attn_tc_head_dim() { return HD; }
 
 // Which kernel head sizes up to 128 run.  1 (the default): two query tiles per CTA when the
-// launch has at least five rounds of such CTAs, else one tile per CTA; 2: always two tiles;
-// 0: always one (head sizes above 128 have that kernel only).
+// launch has at least as many such CTAs as the device has SMs, else one tile per CTA (measured
+// at 32 query heads over 8 kv heads, one / two tiles in us: 1,024 tokens = 128 such CTAs 21.9 /
+// 27.0, 1,280 tokens = 160 CTAs 31.8 / 31.5, 2,048 tokens 58.2 / 51.8, 4,096 tokens 175 / 159);
+// 2: always two tiles; 0: always one (head sizes above 128 have that kernel only).
 static int g_atc_two_tiles = 1;
 SLLM_EXPORT void sllm_attn_tc_set_two_tiles(int mode) {
     g_atc_two_tiles = mode < 0 ? 0 : (mode > 2 ? 2 : mode);
@@ -947,6 +953,8 @@ SLLM_EXPORT int sllm_attn_tc(const void* q, int64_t q_stride, int64_t n_tokens, 
         return (int)cudaErrorInvalidValue;
     if (n_pages * 2 * G * page_size > 0x7fffffffLL || n_tokens > 0x7fffffffLL)
         return (int)cudaErrorInvalidValue;
+    // the query tiles of a row are the grid's z: at most 65,535 of them
+    if (((int64_t)max_new * (H / G) + TQ - 1) / TQ > 65535) return (int)cudaErrorInvalidValue;
     AtcEncodeFn fn = atc_encode_fn();
     if (!fn) return (int)cudaErrorNotSupported;
     const int GS = H / G;
@@ -990,11 +998,11 @@ SLLM_EXPORT int sllm_attn_tc(const void* q, int64_t q_stride, int64_t n_tokens, 
             n_sm = 148;
     }
     const int64_t pair_ctas = (((int64_t)max_new * GS + 2 * TQ - 1) / (2 * TQ)) * n_list * G;
-    if (g_atc_two_tiles == 1 ? pair_ctas >= 5 * (int64_t)n_sm : g_atc_two_tiles == 2) {
+    if (g_atc_two_tiles == 1 ? pair_ctas >= (int64_t)n_sm : g_atc_two_tiles == 2) {
         e = cudaFuncSetAttribute(attn_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)ATC2_SMEM);
         if (e != cudaSuccess) return (int)e;
-        dim3 grid2(((int64_t)max_new * GS + 2 * TQ - 1) / (2 * TQ), n_list, G);
+        dim3 grid2(G, n_list, ((int64_t)max_new * GS + 2 * TQ - 1) / (2 * TQ));
         attn_tc2_kernel<<<grid2, ATC2_THREADS, ATC2_SMEM, stream>>>(map_q, map_kv, a);
         SLLM_LAUNCH_CHECK();
         return 0;
@@ -1003,7 +1011,7 @@ SLLM_EXPORT int sllm_attn_tc(const void* q, int64_t q_stride, int64_t n_tokens, 
     e = cudaFuncSetAttribute(attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)ATC_SMEM);
     if (e != cudaSuccess) return (int)e;
-    dim3 grid(((int64_t)max_new * GS + TQ - 1) / TQ, n_list, G);
+    dim3 grid(G, n_list, ((int64_t)max_new * GS + TQ - 1) / TQ);
     attn_tc_kernel<<<grid, ATC_THREADS, ATC_SMEM, stream>>>(map_q, map_kv, a);
     SLLM_LAUNCH_CHECK();
     return 0;

@@ -671,8 +671,8 @@ def attention_tc(q: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor
 
 def attention_tc_set_two_tiles(head_dim: int, mode: int | bool | None) -> None:
     """Choose the tcgen05 attention kernel for head sizes up to 128.  None (the default):
-    two query tiles per CTA, which share every key/value tile, when the launch is large enough
-    to fill the device several times over, else one; True: always two; False: always one."""
+    two query tiles per CTA, which share every key/value tile, when the launch has at least as
+    many such CTAs as the device has SMs, else one; True: always two; False: always one."""
     code = 1 if mode is None else (2 if mode else 0)
     _load(*attention_tc_library(head_dim)).sllm_attn_tc_set_two_tiles(c_int(code))
 
