@@ -133,12 +133,16 @@ __global__ void __launch_bounds__(THREADS, SPLIT ? 3 : 2) attn_mma_kernel(const 
     pdl_trigger();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n_splits = SPLIT ? a.n_splits : 1;
-    // query tiles in descending order: under the causal mask the last tile of a row has the
-    // most keys to walk, and the longest jobs should start first
-    const int q_tile = (int)(gridDim.x / n_splits) - 1 - (int)(blockIdx.x / n_splits);
-    const int split = blockIdx.x % n_splits;
+    // Query tiles in descending order: under the causal mask the last tile of a row has the
+    // most keys to walk, and the longest jobs should start first.  CTAs start in the order of
+    // blockIdx.x, then y, then z: the wide kernel (many tiles per row) therefore carries the
+    // tile in z and the kv head in x, so that ALL heads' heaviest tiles start first; the split
+    // kernel (one or a few tiles per row) keeps tiles and splits in x.
+    const int q_tile = SPLIT ? (int)(gridDim.x / n_splits) - 1 - (int)(blockIdx.x / n_splits)
+                             : (int)gridDim.z - 1 - (int)blockIdx.z;
+    const int split = SPLIT ? blockIdx.x % n_splits : 0;
     const int r = a.row_list ? a.row_list[blockIdx.y] : blockIdx.y;
-    const int g = blockIdx.z;
+    const int g = SPLIT ? blockIdx.z : blockIdx.x;
     const int GS = a.H / a.G;
     const int t0 = a.row_start[r];
     const int n_new = a.row_start[r + 1] - t0;
@@ -925,7 +929,9 @@ SLLM_EXPORT int sllm_attn_mma(const void* q, int64_t q_stride, const void* pages
         e = cudaFuncSetAttribute(attn_mma_kernel<false>,
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
-        dim3 grid(((int64_t)max_new * GS + 63) / 64, n_list, G);
+        const int64_t q_tiles = ((int64_t)max_new * GS + 63) / 64;
+        if (q_tiles > 65535) return (int)cudaErrorInvalidValue;   // the tiles are the grid's z
+        dim3 grid(G, n_list, (unsigned)q_tiles);
         return (int)sllm_launch_pdl(attn_mma_kernel<false>, grid, dim3(THREADS), smem, stream, a);
     }
     if (n_splits < 1) return (int)cudaErrorInvalidValue;
