@@ -31,6 +31,8 @@
 // and 0 x NaN would be NaN.  Every mbarrier wait is bounded; errors land in g_attn_tc_error.
 #include <cuda.h>
 
+#include <type_traits>
+
 #include "common.cuh"
 
 #ifndef SLLM_HEAD_DIM
@@ -353,6 +355,15 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             const uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) |
                                       ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(TQ >> 4) << 24);
             bool ok = atc_wait(q_full, 0, 2);
+            // the descriptors are built once, so that a product costs this thread an addition
+            // (see attn_tc2_kernel)
+            uint64_t dq[HD / 16];
+#pragma unroll
+            for (int kk = 0; kk < HD / 16; ++kk)
+                dq[kk] = atc_desc(atc_u32(q_s) + (kk / 4) * SUB_BYTES, 16, 1024) + 2 * (kk % 4);
+            const uint64_t dk0 = atc_desc(atc_u32(kv_s), 16, 1024);                    // stage 0
+            const uint64_t dv0 = atc_desc(atc_u32(kv_s) + KV_BYTES, SUB_BYTES, 1024);
+            constexpr uint64_t STAGE_STEP = (2 * KV_BYTES) >> 4;
             // S(t) = Q K(t)^T into the tile's buffer, which the P before it (two tiles back with
             // two buffers, one tile back with one) has left once its P V is done.  A wait on
             // pv_done names the phase by its parity, so the waiter must know that the phase before
@@ -363,15 +374,11 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 const int back = EARLY_QK ? 2 : 1;
                 if (t >= back && !atc_wait(pv_done, (t - back) & 1, 8)) return false;
                 atc_fence_after();
-                const uint32_t k_addr = atc_u32(kv_s + (size_t)s * 2 * KV_BYTES);
+                const uint64_t dk = dk0 + (uint64_t)s * STAGE_STEP;
 #pragma unroll
-                for (int kk = 0; kk < HD / 16; ++kk) {
-                    const uint64_t dq = atc_desc(atc_u32(q_s) + (kk / 4) * SUB_BYTES, 16, 1024) +
-                                        2 * (kk % 4);
-                    const uint64_t dk = atc_desc(k_addr + (kk / 4) * SUB_BYTES, 16, 1024) +
-                                        2 * (kk % 4);
-                    atc_mma_ss(tmem + SP_COLS * atc_buf(t), dq, dk, idesc_qk, kk > 0);
-                }
+                for (int kk = 0; kk < HD / 16; ++kk)
+                    atc_mma_ss(tmem + SP_COLS * atc_buf(t), dq[kk],
+                               dk + (((kk / 4) * SUB_BYTES) >> 4) + 2 * (kk % 4), idesc_qk, kk > 0);
                 atc_commit(&s_full[atc_buf(t)]);
                 return true;
             };
@@ -393,15 +400,14 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                     if (!ok) break;
                 }
                 atc_fence_after();
-                const uint32_t v_addr = atc_u32(kv_s + (size_t)s * 2 * KV_BYTES) + KV_BYTES;
+                // V: rows = keys (128 bytes = 64 dims each), 8-key groups 1024 bytes apart,
+                // 64-dim blocks SUB_BYTES apart; 16 keys further = 2048 bytes
+                const uint64_t dv = dv0 + (uint64_t)s * STAGE_STEP;
+                atc_mma_ts(tmem + O_COL, tmem + SP_COLS * atc_buf(t), dv, idesc_pv, t != 0);
 #pragma unroll
-                for (int kk = 0; kk < TKV / 16; ++kk) {
-                    // V: rows = keys (128 bytes = 64 dims each), 8-key groups 1024 bytes apart,
-                    // 64-dim blocks SUB_BYTES apart; 16 keys further = 2048 bytes
-                    const uint64_t dv = atc_desc(v_addr + kk * 2048, SUB_BYTES, 1024);
-                    atc_mma_ts(tmem + O_COL, tmem + SP_COLS * atc_buf(t) + kk * 8, dv, idesc_pv,
-                               (t | kk) != 0);
-                }
+                for (int kk = 1; kk < TKV / 16; ++kk)
+                    atc_mma_ts(tmem + O_COL, tmem + SP_COLS * atc_buf(t) + kk * 8,
+                               dv + kk * (2048 >> 4), idesc_pv, 1);
                 atc_commit(&kv_empty[s]);
                 atc_commit(pv_done);
                 if (!EARLY_QK && t + 1 < n_tiles) ok = issue_qk(t + 1);
@@ -693,60 +699,77 @@ attn_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
             const uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) |
                                       ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(TQ >> 4) << 24);
             bool ok = atc_wait(q_full, 0, 2);
-            // S_x(t) = Q_x K(t)^T (the stage's keys must have landed: the caller has waited)
-            auto issue_qk = [&](int x, int t) {
-                const int s = t % KV_STAGES2;
-                const uint32_t k_addr = atc_u32(kv_s + (size_t)s * 2 * KV_BYTES);
-                const uint32_t q_addr = atc_u32(q_s + x * Q_BYTES);
+            // This one thread feeds the tensor pipe, and a product of 128 x 128 x 16 keeps the
+            // pipe busy for about 70 cycles only: whatever the thread computes between two
+            // products is time the pipe stands still (with a descriptor built per product the
+            // pipe was busy 46 % of the time).  So the descriptors are built once: a product
+            // then costs the thread an addition.  (A descriptor's low 14 bits are the
+            // shared-memory address / 16, and every address used here lies inside this CTA's
+            // allocation, so offsets can be added to the descriptor itself.)
+            uint64_t dq[2][HD / 16];
 #pragma unroll
-                for (int kk = 0; kk < HD / 16; ++kk) {
-                    const uint64_t dq = atc_desc(q_addr + (kk / 4) * SUB_BYTES, 16, 1024) + 2 * (kk % 4);
-                    const uint64_t dk = atc_desc(k_addr + (kk / 4) * SUB_BYTES, 16, 1024) + 2 * (kk % 4);
-                    atc_mma_ss(tmem + SP_COLS * x, dq, dk, idesc_qk, kk > 0);
-                }
+            for (int x = 0; x < 2; ++x)
+#pragma unroll
+                for (int kk = 0; kk < HD / 16; ++kk)
+                    dq[x][kk] = atc_desc(atc_u32(q_s + x * Q_BYTES) + (kk / 4) * SUB_BYTES, 16, 1024) +
+                                2 * (kk % 4);
+            const uint64_t dk0 = atc_desc(atc_u32(kv_s), 16, 1024);                    // stage 0
+            const uint64_t dv0 = atc_desc(atc_u32(kv_s) + KV_BYTES, SUB_BYTES, 1024);
+            constexpr uint64_t STAGE_STEP = (2 * KV_BYTES) >> 4;
+            // S_x(t) = Q_x K(t)^T (the stage's keys must have landed: the caller has waited)
+            auto issue_qk = [&](auto xc, int t) {
+                constexpr int x = decltype(xc)::value;
+                const uint64_t dk = dk0 + (uint64_t)(t % KV_STAGES2) * STAGE_STEP;
+#pragma unroll
+                for (int kk = 0; kk < HD / 16; ++kk)
+                    atc_mma_ss(tmem + SP_COLS * x, dq[x][kk],
+                               dk + (((kk / 4) * SUB_BYTES) >> 4) + 2 * (kk % 4), idesc_qk, kk > 0);
                 atc_commit(&s_full[x]);
             };
             // O_x += P_x(t) V(t)
-            auto issue_pv = [&](int x, int t) {
-                const int s = t % KV_STAGES2;
-                const uint32_t v_addr = atc_u32(kv_s + (size_t)s * 2 * KV_BYTES) + KV_BYTES;
+            auto issue_pv = [&](auto xc, int t) {
+                constexpr int x = decltype(xc)::value;
+                const uint64_t dv = dv0 + (uint64_t)(t % KV_STAGES2) * STAGE_STEP;
+                atc_mma_ts(tmem + O_COL + HD * x, tmem + SP_COLS * x, dv, idesc_pv, t != 0);
 #pragma unroll
-                for (int kk = 0; kk < TKV / 16; ++kk) {
-                    const uint64_t dv = atc_desc(v_addr + kk * 2048, SUB_BYTES, 1024);
-                    atc_mma_ts(tmem + O_COL + HD * x, tmem + SP_COLS * x + kk * 8, dv, idesc_pv,
-                               (t | kk) != 0);
-                }
+                for (int kk = 1; kk < TKV / 16; ++kk)
+                    atc_mma_ts(tmem + O_COL + HD * x, tmem + SP_COLS * x + kk * 8, dv + kk * (2048 >> 4),
+                               idesc_pv, 1);
                 atc_commit(&pv_done[x]);
             };
             if (ok) ok = atc_wait(&kv_full[0], 0, 3);
             if (ok) {
                 atc_fence_after();
-                for (int x = 0; x < 2; ++x)
-                    if (n_tiles_x[x] > 0) issue_qk(x, 0);
+                if (n_tiles_x[0] > 0) issue_qk(std::integral_constant<int, 0>{}, 0);
+                if (n_tiles_x[1] > 0) issue_qk(std::integral_constant<int, 1>{}, 0);
             }
             for (int t = 0; t < n_tiles && ok; ++t) {
                 const int s = t % KV_STAGES2;
                 bool next_ready = false;
-                for (int x = 0; x < 2 && ok; ++x) {
-                    if (t >= n_tiles_x[x]) continue;
+                // one query tile's part of step t: P_x(t) V(t), then Q_x K(t+1)^T
+                auto tile_step = [&](auto xc) {
+                    constexpr int x = decltype(xc)::value;
+                    if (t >= n_tiles_x[x]) return;
                     ok = atc_wait(&p_full[x], t & 1, 4);
-                    if (!ok) break;
+                    if (!ok) return;
                     if (t == n_tiles - 1) {   // the producer has zeroed the stale rows of V
                         ok = atc_wait(v_clean, 0, 10);
-                        if (!ok) break;
+                        if (!ok) return;
                     }
                     atc_fence_after();
-                    issue_pv(x, t);
+                    issue_pv(xc, t);
                     if (t + 1 < n_tiles_x[x]) {
                         if (!next_ready) {
                             ok = atc_wait(&kv_full[(t + 1) % KV_STAGES2], ((t + 1) / KV_STAGES2) & 1, 3);
-                            if (!ok) break;
+                            if (!ok) return;
                             atc_fence_after();
                             next_ready = true;
                         }
-                        issue_qk(x, t + 1);
+                        issue_qk(xc, t + 1);
                     }
-                }
+                };
+                tile_step(std::integral_constant<int, 0>{});
+                if (ok) tile_step(std::integral_constant<int, 1>{});
                 if (!ok) break;
                 // every product that reads this stage's keys and values has been issued
                 atc_commit(&kv_empty[s]);
@@ -888,6 +911,7 @@ attn_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
                      ::"r"(tmem), "r"(512u) : "memory");
     }
 }
+
 
 #endif  // SLLM_HEAD_DIM <= 128
 
