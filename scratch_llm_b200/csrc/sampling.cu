@@ -14,6 +14,8 @@
 // The nucleus needs no sort: token k is kept iff the mass of all strictly more probable
 // tokens is <= top_p, which is monotone in p_k, so the smallest kept probability is found by
 // bisection over float bit patterns (31 passes over the row, which stays in L2).
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 
 namespace sllm {
@@ -196,6 +198,248 @@ sample_kernel(const float* __restrict__ logits, int64_t ld, int V,
     }
 }
 
+// The same choice for large vocabularies: a thread-block cluster of SC_RANKS CTAs per row.
+// With one CTA per row every pass over the row streams it from L2 into one SM with one load in
+// flight per thread, and the nucleus needs up to 33 passes: 0.96 ms for a row of 128,256 logits,
+// whatever the number of rows.  Here each CTA of the cluster keeps an eighth of the row in its
+// shared memory (the logits, then the probabilities in their place), a pass is a
+// walk over shared memory, and the CTAs add their partial results through distributed shared
+// memory: every CTA writes its partial into a slot of every CTA, the cluster meets at its
+// barrier, and each adds the eight slots in rank order, so that all hold the same bits and take
+// the same branches.  (Two sets of slots take turns: a CTA can be one round ahead of another,
+// never two.)  The bisection stops as soon as no probability lies strictly between its bounds:
+// the threshold can then only be the upper one (22 rounds instead of 31 for 128,256 random
+// logits; eight ways per round instead of two took 8 rounds but as long, a round's arithmetic
+// growing as its number fell).  Arithmetic and rules are those of
+// sample_kernel; only the order of the sums differs.
+constexpr int SC_RANKS = 8;
+constexpr int SC_MAX_SLICE = 24576;     // values a CTA keeps in shared memory (two CTAs share an SM)
+constexpr int SC_MIN_VOCAB = 8192;      // below, one CTA per row has the row in L1 anyway
+
+struct ScSlots {
+    float f[2][SC_RANKS][2];
+    ArgMax a[2][SC_RANKS];
+    int i[2][SC_RANKS];
+};
+
+namespace cg = cooperative_groups;
+
+// every CTA's (x, y) summed over the cluster, the same bits in every CTA
+__device__ __forceinline__ float2 sc_all_sum(cg::cluster_group& cluster, ScSlots* slots, int& round,
+                                             float x, float y) {
+    const int set = round & 1;
+    ++round;
+    if (threadIdx.x < SC_RANKS) {
+        ScSlots* peer = cluster.map_shared_rank(slots, threadIdx.x);
+        peer->f[set][cluster.block_rank()][0] = x;
+        peer->f[set][cluster.block_rank()][1] = y;
+    }
+    cluster.sync();
+    float2 total = make_float2(0.f, 0.f);
+#pragma unroll
+    for (int r = 0; r < SC_RANKS; ++r) {
+        total.x += slots->f[set][r][0];
+        total.y += slots->f[set][r][1];
+    }
+    return total;
+}
+
+
+// N values per CTA summed over the block and then over the cluster (in v, the same bits in every
+// thread of every CTA).  scratch: [32][N] floats.
+template <int N>
+__device__ __forceinline__ void sc_all_sum_n(cg::cluster_group& cluster, ScSlots* slots, int& round,
+                                             float (&v)[N], float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int k = 0; k < N; ++k) v[k] = warp_sum(v[k]);
+    __syncthreads();        // scratch may still be read from the round before
+    if (lane == 0) {
+#pragma unroll
+        for (int k = 0; k < N; ++k) scratch[warp * N + k] = v[k];
+    }
+    __syncthreads();
+    const int set = round & 1;
+    ++round;
+    if (threadIdx.x < SC_RANKS * N) {
+        // thread (peer, k): the block's sum of value k, in warp order, into the peer's slot
+        const int peer = threadIdx.x / N, k = threadIdx.x % N;
+        float t = 0.f;
+        for (int w = 0; w < SAMPLE_THREADS / 32; ++w) t += scratch[w * N + k];
+        cluster.map_shared_rank(slots, peer)->f[set][cluster.block_rank()][k] = t;
+    }
+    cluster.sync();
+#pragma unroll
+    for (int k = 0; k < N; ++k) {
+        float t = 0.f;
+#pragma unroll
+        for (int r = 0; r < SC_RANKS; ++r) t += slots->f[set][r][k];
+        v[k] = t;
+    }
+}
+
+// NUCLEUS = false: no row has a top_p below 1 (top_p is not read); the kernel then needs few
+// registers and two CTAs share an SM.
+template <bool NUCLEUS>
+__global__ void __cluster_dims__(SC_RANKS, 1, 1) __launch_bounds__(SAMPLE_THREADS, 2)
+sample_cluster_kernel(const float* __restrict__ logits, int64_t ld, int V, int slice,
+                      const float* __restrict__ temperature, const float* __restrict__ top_p,
+                      const unsigned long long* __restrict__ seed,
+                      const unsigned long long* __restrict__ counter, int* __restrict__ out,
+                      float* __restrict__ logprob_out, float* __restrict__ probs_out) {
+    extern __shared__ float sc_values[];       // [slice] logits, later their probabilities
+    __shared__ float fscratch[33];
+    __shared__ ArgMax ascratch[33];
+    __shared__ float chunk_sum[32];
+    __shared__ float nscratch[NUCLEUS ? 32 * 2 : 1];
+    __shared__ int chosen;
+    __shared__ ScSlots slots;
+    cg::cluster_group cluster = cg::this_cluster();
+    const int rank = (int)cluster.block_rank();
+    const int row = blockIdx.x / SC_RANKS, tid = threadIdx.x;
+    const float* z = logits + (int64_t)row * ld;
+    const float T = temperature ? temperature[row] : 0.f;
+    const int begin = min(V, rank * slice), n = min(V, begin + slice) - begin;
+    float* zs = sc_values;      // the slice's logits until the probabilities take their place
+    float* ps = sc_values;
+    int round = 0;
+
+    ArgMax best{0.f, -1};
+    for (int i = tid; i < n; i += SAMPLE_THREADS) {
+        const float v = z[begin + i];
+        zs[i] = v;
+        best = better(best, ArgMax{v, begin + i});
+    }
+    best = block_argmax(best, ascratch);
+    {   // the row's first maximum: every CTA's candidate to every CTA
+        const int set = round & 1;
+        ++round;
+        if (tid < SC_RANKS) cluster.map_shared_rank(&slots, tid)->a[set][rank] = best;
+        cluster.sync();
+        best = ArgMax{0.f, -1};
+#pragma unroll
+        for (int r = 0; r < SC_RANKS; ++r) best = better(best, slots.a[set][r]);
+    }
+    const float zmax = best.v;
+
+    int token = best.i;
+    if (T > 0.f) {     // (the same in every CTA of the cluster: they serve one row)
+        const float inv_t = 1.0f / T;
+        const float mt = zmax * inv_t;
+        float part = 0.f;
+        for (int i = tid; i < n; i += SAMPLE_THREADS) {
+            const float e = expf(zs[i] * inv_t - mt);
+            ps[i] = e;
+            part += e;
+        }
+        const float Z = sc_all_sum(cluster, &slots, round, block_sum(part, fscratch), 0.f).x;
+        const float inv_z = 1.0f / Z;
+        for (int i = tid; i < n; i += SAMPLE_THREADS) ps[i] *= inv_z;
+        __syncthreads();
+        float thresh = 0.f;  // keep p >= thresh
+        const float tp = NUCLEUS && top_p ? top_p[row] : 1.f;
+        if (NUCLEUS && tp < 1.0f) {
+            // f(t) = sum of p_i > t.  lo: f(lo) > tp.  hi: f(hi) <= tp.  p_max = 1 / Z.
+            unsigned lo = 0u, hi = __float_as_uint(inv_z);
+            while (hi - lo > 1u) {
+                const unsigned mid = lo + (hi - lo) / 2u;
+                const float t = __uint_as_float(mid);
+                float v[2] = {0.f, 0.f};       // f(mid); how many probabilities lie inside
+                for (int i = tid; i < n; i += SAMPLE_THREADS) {
+                    const float p = ps[i];
+                    v[0] += p > t ? p : 0.f;
+                    const unsigned bits = __float_as_uint(p);
+                    v[1] += (bits > lo && bits < hi && bits != mid) ? 1.f : 0.f;
+                }
+                sc_all_sum_n<2>(cluster, &slots, round, v, nscratch);
+                if (v[0] <= tp) hi = mid; else lo = mid;
+                // no probability strictly inside the bounds (mid has just become one of them):
+                // f is constant on [lo, hi), so the search can only end at this hi
+                if (v[1] == 0.f) break;
+            }
+            thresh = __uint_as_float(hi);
+        }
+        // contiguous chunk per thread, in index order; the CTAs' slices follow one another
+        const int per = (n + SAMPLE_THREADS - 1) / SAMPLE_THREADS;
+        const int c0 = min(n, tid * per), c1 = min(n, c0 + per);
+        float mine = 0.f;
+        for (int i = c0; i < c1; ++i) {
+            const float p = ps[i];
+            mine += p >= thresh ? p : 0.f;
+        }
+        const float my_total = block_sum(mine, fscratch);
+        const int set = round & 1;
+        const float kept = sc_all_sum(cluster, &slots, round, my_total, 0.f).x;
+        float before_cta = 0.f;
+        for (int r = 0; r < rank; ++r) before_cta += slots.f[set][r][0];
+        if (probs_out) {
+            float* po = probs_out + (int64_t)row * V + begin;
+            for (int i = tid; i < n; i += SAMPLE_THREADS) {
+                const float p = ps[i];
+                po[i] = p >= thresh ? p / kept : 0.f;
+            }
+        }
+        if (tid == 0) chosen = -1;
+        __syncthreads();
+        const float u = philox_uniform(seed ? seed[row] : 0ull, counter ? counter[row] : 0ull);
+        const float target = u * kept;
+        // exclusive prefix of the chunk sums: the warps before this one (their totals, in warp
+        // order), then the lanes before this one
+        float before = before_cta;
+        {
+            const int lane = tid & 31, warp = tid >> 5;
+            float incl = mine;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const float up = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += up;
+            }
+            if (lane == 31) chunk_sum[warp] = incl;      // (chunk_sum is free: totals of the warps)
+            __syncthreads();
+            for (int w = 0; w < warp; ++w) before += chunk_sum[w];
+            before += incl - mine;
+        }
+        if (mine > 0.f && target >= before && target < before + mine) {
+            float run = before;
+            int pick = -1, last_kept = -1;
+            for (int i = c0; i < c1; ++i) {
+                const float p = ps[i];
+                if (p >= thresh) {
+                    last_kept = begin + i;
+                    run += p;
+                    if (pick < 0 && target < run) pick = begin + i;
+                }
+            }
+            atomicMax(&chosen, pick >= 0 ? pick : last_kept);
+        }
+        __syncthreads();
+        {   // the CTA whose slice holds the target has chosen; all learn the token
+            const int cset = round & 1;
+            ++round;
+            if (tid < SC_RANKS) cluster.map_shared_rank(&slots, tid)->i[cset][rank] = chosen;
+            cluster.sync();
+            int c = -1;
+#pragma unroll
+            for (int r = 0; r < SC_RANKS; ++r) c = max(c, slots.i[cset][r]);
+            // rounding can leave the target past every chunk's end: take the most probable token
+            token = c >= 0 ? c : best.i;
+        }
+    }
+    if (rank == 0 && tid == 0) out[row] = token;
+    if (logprob_out) {
+        float part = 0.f;
+        if (T > 0.f) {      // the logits have left shared memory
+            for (int i = tid; i < n; i += SAMPLE_THREADS) part += expf(z[begin + i] - zmax);
+        } else {
+            for (int i = tid; i < n; i += SAMPLE_THREADS) part += expf(zs[i] - zmax);
+        }
+        const float Z1 = sc_all_sum(cluster, &slots, round, block_sum(part, fscratch), 0.f).x;
+        if (rank == 0 && tid == 0) logprob_out[row] = z[token] - zmax - logf(Z1);
+    }
+    // nobody leaves while a peer may still write into its slots
+    cluster.sync();
+}
+
 // Greedy choice for many rows at once: grid (ARGMAX_CHUNKS, rows).  Each block finds the
 // argmax of its slice of the row; the block that finishes last for a row (a ticket from an
 // atomic counter, no waiting) combines the slices.  `partial` holds ARGMAX_CHUNKS (value,
@@ -308,6 +552,19 @@ SLLM_EXPORT int sllm_sample(const float* logits, int64_t ld, int n_rows, int V,
                             cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (V <= 0 || ld < V) return (int)cudaErrorInvalidValue;
+    // large vocabularies: a cluster of CTAs per row, each with its slice in shared memory
+    const int slice = ((V + SC_RANKS - 1) / SC_RANKS + 3) / 4 * 4;
+    if (V >= SC_MIN_VOCAB && slice <= SC_MAX_SLICE) {
+        const size_t smem = (size_t)slice * sizeof(float);
+        auto kernel = top_p ? sample_cluster_kernel<true> : sample_cluster_kernel<false>;
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        kernel<<<n_rows * SC_RANKS, SAMPLE_THREADS, smem, stream>>>(
+            logits, ld, V, slice, temperature, top_p, seed, counter, out, logprob_out, probs_out);
+        SLLM_LAUNCH_CHECK();
+        return 0;
+    }
     sample_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(logits, ld, V, temperature, top_p, seed,
                                                          counter, out, logprob_out, probs_out);
     SLLM_LAUNCH_CHECK();

@@ -86,7 +86,9 @@ class Sampler:
             i = np.array([[s & 0x7FFFFFFFFFFFFFFF for s in seeds], list(counters)], dtype=np.int64)
             fd = torch.from_numpy(f).to(self.device, non_blocking=True)
             idv = torch.from_numpy(i).to(self.device, non_blocking=True)
-            ops.sample(logits, out, fd[0], fd[1], idv[0], idv[1], logprob_out=lp)
+            # (no top_p below 1: the kernel is told so, and need not look for a nucleus)
+            nucleus = fd[1] if any(p.top_p < 1.0 for p in params) else None
+            ops.sample(logits, out, fd[0], nucleus, idv[0], idv[1], logprob_out=lp)
         host_tokens, host_lp, event = self._host_buffers(n)
         host_tokens[:n].copy_(out, non_blocking=True)
         if lp is not None:

@@ -595,7 +595,7 @@ def test_argmax_many_blocks_per_row(ops, n, V):
         assert out.cpu().tolist() == want.tolist()
 
 
-@pytest.mark.parametrize("V", [331, 50000])
+@pytest.mark.parametrize("V", [331, 50000, 128256, 9001])
 def test_sampling_distribution_and_draws(ops, V):
     logits = rand(3, V, seed=6, scale=2.0)
     temps = torch.tensor([0.7, 1.0, 1.3])
@@ -614,6 +614,12 @@ def test_sampling_distribution_and_draws(ops, V):
         if not differ.any():
             torch.testing.assert_close(got, want, rtol=1e-4, atol=1e-7)
         assert got[out[r].item()] > 0
+    # without a nucleus (no top_p given): the whole distribution at the row's temperature
+    whole = torch.empty(3, V, dtype=torch.float32, device="cuda")
+    ops.sample(logits.cuda(), out.clone(), temps.cuda(), None, seed, ctr, probs_out=whole)
+    for r in range(3):
+        torch.testing.assert_close(whole[r].cpu(), P.sampling_distribution(logits[r], float(temps[r]), 1.0),
+                                   rtol=1e-4, atol=1e-7)
     # the same (seed, counter) draws the same token; counters walk through the distribution
     again = torch.empty(3, dtype=torch.int32, device="cuda")
     ops.sample(logits.cuda(), again, temps.cuda(), tops.cuda(), seed, ctr)
