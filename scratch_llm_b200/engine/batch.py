@@ -61,9 +61,12 @@ def pad_plan(n_tokens: int, n_single: int, n_multi: int, n_out: int) -> PadPlan:
     """Tokens go up to a multiple of 16 (of 64 above 128), single rows to a multiple of 8,
     multi rows to a power of two, wanted places to a power of two up to 8 and to a multiple of
     16 above; nothing wanted stays nothing wanted.  A decode step (every row one token, its
-    logits wanted) only goes up to the next multiple of 8 in all three."""
+    logits wanted) only goes up to the next multiple of 8 (of 16 above 32 rows, of 32 above 64)
+    in all three."""
     if n_multi == 0 and n_tokens == n_single == n_out:
-        n = _round_up(n_tokens, 8)
+        # (rows of padding cost a decode step next to nothing, a shape that has not come before
+        # costs a capture: the steps get coarser as the batch grows)
+        n = _round_up(n_tokens, 8 if n_tokens <= 32 else 16 if n_tokens <= 64 else 32)
         return PadPlan(n, n, 0, n)
     tokens = _round_up(n_tokens, 16) if n_tokens <= 128 else _round_up(n_tokens, 64)
     out = 0 if n_out == 0 else _next_power_of_two(n_out) if n_out <= 8 else _round_up(n_out, 16)

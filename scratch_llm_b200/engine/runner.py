@@ -54,7 +54,9 @@ DECODE_EXACT_ROWS = 8
 PAD_MAX_WANTED = 64
 #: captured graphs a runner keeps; the one used longest ago goes first
 MAX_CAPTURED_STEPS = 192
-#: a decode shape is captured at its second use: every later step has it again.  A padded
+#: a decode shape is captured at its second use: every later step has it again (capturing at
+#: the first use costs more than a plain step and a capture after it, 28 against 10 + 11 ms at
+#: Llama-3-8B sizes: what a first use sets up is cheaper outside a capture).  A padded
 #: shape is captured once it has come this often: a capture costs as much as the launches of
 #: some ten plain steps and saves a tenth of a step each time, and many shapes come only a few times
 CAPTURE_PADDED_AFTER = 24
