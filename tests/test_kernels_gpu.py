@@ -595,6 +595,46 @@ def test_argmax_many_blocks_per_row(ops, n, V):
         assert out.cpu().tolist() == want.tolist()
 
 
+@pytest.mark.parametrize("V", [8191, 8192, 8193, 70001])
+def test_sampling_edges_of_the_cluster_kernel(ops, V):
+    """Vocabularies around the size from which a cluster of CTAs serves a row (and one that no
+    CTA's slice divides), many rows, a nucleus of almost nothing and of everything, a high and a
+    low temperature, peaked rows, and the log-probability of the drawn token."""
+    n = 150
+    g = torch.Generator().manual_seed(V)
+    logits = torch.randn(n, V, generator=g) * 2.0
+    logits[3] = -50.0
+    logits[3, V - 1] = 10.0                    # all mass on the last token
+    logits[4, : V // 2] += 30.0                # half the row far above the other half
+    temps = torch.tensor([0.05, 0.3, 1.0, 1.0, 2.0, 5.0] * (n // 6))
+    tops = torch.tensor([0.01, 0.5, 0.999, 1.0, 0.9, 0.2] * (n // 6))
+    seed = torch.arange(n, dtype=torch.int64).cuda()
+    ctr = torch.full((n,), 7, dtype=torch.int64).cuda()
+    probs = torch.empty(n, V, dtype=torch.float32, device="cuda")
+    out = torch.empty(n, dtype=torch.int32, device="cuda")
+    lp = torch.empty(n, dtype=torch.float32, device="cuda")
+    ops.sample(logits.cuda(), out, temps.cuda(), tops.cuda(), seed, ctr, logprob_out=lp,
+               probs_out=probs)
+    got_all, tok = probs.cpu(), out.cpu().long()
+    assert int(tok[3]) == V - 1
+    want_lp = torch.log_softmax(logits, -1)[torch.arange(n), tok]
+    torch.testing.assert_close(lp.cpu(), want_lp, rtol=1e-4, atol=1e-4)
+    for r in range(0, n, 7):
+        want = P.sampling_distribution(logits[r], float(temps[r]), float(tops[r]))
+        got = got_all[r]
+        differ = (got > 0) != (want > 0)
+        assert differ.sum() <= 1, (r, int(differ.sum()))
+        if not differ.any():
+            torch.testing.assert_close(got, want, rtol=1e-4, atol=1e-7)
+        assert got[tok[r]] > 0 and abs(float(got.sum()) - 1.0) < 1e-4
+    # a row's draw does not depend on its neighbours or on their number
+    alone = torch.empty(1, dtype=torch.int32, device="cuda")
+    for r in (0, 5, n - 1):
+        ops.sample(logits[r:r + 1].cuda(), alone, temps[r:r + 1].cuda(), tops[r:r + 1].cuda(),
+                   seed[r:r + 1], ctr[r:r + 1])
+        assert int(alone) == int(tok[r])
+
+
 @pytest.mark.parametrize("V", [331, 50000, 128256, 9001])
 def test_sampling_distribution_and_draws(ops, V):
     logits = rand(3, V, seed=6, scale=2.0)
