@@ -5,6 +5,7 @@ exists, at sizes given on the command line.
         [--k 4096] [--swiglu]
     python -m scratch_llm_b200.kernels.microbench attn_prefill --tokens 2048 4096 [--page 64]
     python -m scratch_llm_b200.kernels.microbench attn_decode --batch 8 64 [--context 1024]
+    python -m scratch_llm_b200.kernels.microbench sample --rows 1 8 64 [--vocab 128256]
 
 Method: ``--inner`` launches (16 by default) are recorded into a CUDA graph, so that no
 launch waits for the host; after warm-up each replay is timed by an event pair on the
@@ -192,6 +193,32 @@ def bench_attn_decode(args) -> list[dict]:
     return out
 
 
+def bench_sample(args) -> list[dict]:
+    """The choice of the next token over a vocabulary of ``--vocab`` entries: greedy (the argmax
+    kernel), a draw at a temperature, a draw from a nucleus, and the latter with the drawn
+    token's log-probability."""
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    out = []
+    for n in args.rows:
+        logits = torch.randn(n, args.vocab, device="cuda", generator=gen) * 3
+        tok = torch.empty(n, dtype=torch.int32, device="cuda")
+        temp = torch.full((n,), 0.8, device="cuda")
+        top = torch.full((n,), 0.9, device="cuda")
+        seed = torch.arange(n, dtype=torch.int64, device="cuda")
+        ctr = torch.zeros(n, dtype=torch.int64, device="cuda")
+        lp = torch.empty(n, device="cuda")
+        scratch = torch.zeros(ops.argmax_scratch_bytes(n), dtype=torch.uint8, device="cuda")
+        out.append({
+            "kernel": "sample", "rows": n, "vocab": args.vocab,
+            "argmax": time_us(lambda i: ops.argmax(logits, tok, scratch, n), args.reps),
+            "temperature": time_us(lambda i: ops.sample(logits, tok, temp, None, seed, ctr),
+                                   args.reps),
+            "nucleus": time_us(lambda i: ops.sample(logits, tok, temp, top, seed, ctr), args.reps),
+            "nucleus_logprob": time_us(lambda i: ops.sample(logits, tok, temp, top, seed, ctr, lp),
+                                       args.reps)})
+    return out
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
     sub = ap.add_subparsers(dest="what", required=True)
@@ -206,6 +233,9 @@ def main(argv=None) -> int:
     p = sub.add_parser("attn_decode")
     p.add_argument("--batch", type=int, nargs="+", default=[8, 64])
     p.add_argument("--context", type=int, default=1024)
+    p = sub.add_parser("sample")
+    p.add_argument("--rows", type=int, nargs="+", default=[1, 8, 64])
+    p.add_argument("--vocab", type=int, default=128256)
     for name in ("attn_prefill", "attn_decode"):
         q = sub.choices[name]
         q.add_argument("--heads", type=int, default=32)
@@ -223,7 +253,7 @@ def main(argv=None) -> int:
     ops.prepare([], verbose=False)
     with torch.no_grad():
         rows = {"linear": bench_linear, "attn_prefill": bench_attn_prefill,
-                "attn_decode": bench_attn_decode}[args.what](args)
+                "attn_decode": bench_attn_decode, "sample": bench_sample}[args.what](args)
     for r in rows:
         print(json.dumps(r))
     ops.check_kernel_errors()
