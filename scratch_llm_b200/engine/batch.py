@@ -112,6 +112,9 @@ class StepBatch:
     max_new_multi: int = 0
     max_context_single: int = 0
     context_bucket: int = 0   # max_context_single rounded up to a power of two (at least 256)
+    #: the logits of every token are wanted, in the tokens' order (a decode step: the gather of
+    #: the wanted rows before the final norm is then the identity)
+    wants_every_token: bool = False
     # host copies, for parts that plan their launches from them
     host_row_new: list[int] = field(default_factory=list)
     host_row_pos0: list[int] = field(default_factory=list)
@@ -295,6 +298,7 @@ def build_batch(cache, stager: BatchStager, rows: Sequence[RowInput], vocab_size
         multi_rows=dev[8], block_tables=dev[9:], n_single=len(single), n_multi=len(multi),
         max_new_multi=max((lens[i] for i in multi), default=0),
         max_context_single=ctx_single, context_bucket=context_bucket(ctx_single),
+        wants_every_token=bool(li.size == n_tokens and (li == np.arange(n_tokens)).all()),
         host_row_new=lens, host_row_pos0=row_pos0.tolist(), n_real_tokens=n_tokens,
         n_real_out=len(logit_index))
 

@@ -18,6 +18,7 @@ from ..kernels import ops
 from ..parts import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS, BuildContext,
                      CacheView, KVSpec, StateSpec, make)
 from ..parts.linear import Linear
+from ..parts.stream import Normed
 from ..weights.loader import ParamSpec
 
 
@@ -28,6 +29,18 @@ def _spec_key(spec: PartSpec):
 #: kind of part (a value of a block's ``ROLES``) -> (registry, name used in error messages)
 PART_KINDS = {"mixer": (MIXERS, "mixer"), "feed_forward": (FEED_FORWARDS, "feed-forward"),
               "norm": (NORMS, "norm"), "position": (POSITION_ENCODINGS, "position encoding")}
+
+
+class _HeadEntry:
+    """The output matrix as the part that follows the final norm: it can finish a norm handed
+    over to it where its product can (see :mod:`scratch_llm_b200.parts.stream`)."""
+
+    def __init__(self, model: "DecoderModel") -> None:
+        self.model = model
+
+    def accepts_normed(self, n_tokens: int) -> bool:
+        head = self.model.lm_head
+        return head is not None and head.takes_normed(n_tokens)
 
 
 class DecoderModel:
@@ -80,6 +93,11 @@ class DecoderModel:
             self._next_entry.append(entry if getattr(block, "takes_next_entry", False) else None)
         self.final_norm = make(NORMS, "norm", spec.final_norm)
         self._named_parts.append((spec.final_norm_name, self.final_norm))
+        # the last run may prepare the final norm for the output matrix in steps that want the
+        # logits of every token in order (decode steps), where no rows are gathered in between
+        last = self.blocks[spec.order[-1].layer] if spec.order else None
+        self._final_entry = ((self.final_norm, _HeadEntry(self))
+                             if getattr(last, "takes_next_entry", False) else None)
         self.embedding: torch.Tensor | None = None
         self.lm_head: Linear | None = None
 
@@ -157,7 +175,10 @@ class DecoderModel:
                              block_table=batch.block_tables[group] if group is not None else None,
                              page_size=cache.page_size, state=cache.states[run.cache])
             block = self.blocks[run.layer]
-            if self._next_entry[i] is not None:
+            if i == len(s.order) - 1 and self._final_entry is not None and batch.wants_every_token:
+                pending = block.forward(resid, pending, batch, view, run.write,
+                                        next_entry=self._final_entry)
+            elif self._next_entry[i] is not None:
                 # what the next run starts with, so that this block's last product may prepare
                 # it (the final norm works on gathered rows: nothing is prepared for it)
                 pending = block.forward(resid, pending, batch, view, run.write,
@@ -166,7 +187,10 @@ class DecoderModel:
                 pending = block.forward(resid, pending, batch, view, run.write)
         if batch.n_out == 0:
             return None
-        h = self.final_norm.forward(resid, pending, out_rows=batch.logit_index)
+        if isinstance(pending, Normed):      # prepared by the last run: every row, in order
+            h = self.final_norm.forward(resid, pending)
+        else:
+            h = self.final_norm.forward(resid, pending, out_rows=batch.logit_index)
         logits = self.lm_head(h, out_dtype=torch.float32)
         if s.logit_scale != 1.0 or s.logit_softcap > 0:
             ops.logit_cap(logits, s.logit_scale, s.logit_softcap)
