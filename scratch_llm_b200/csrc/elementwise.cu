@@ -24,6 +24,39 @@ __global__ void embed_kernel(const int* __restrict__ ids, const int* __restrict_
     for (int i = threadIdx.x; i < d; i += blockDim.x) dst[i] = to_float(src[i]) * scale;
 }
 
+// The embedding with the first norm prepared for the product after it (up to 8 tokens, bfloat16
+// table): out[n, :] as embed_kernel, x_out[n, i] = bfloat16(out[n, i] * gain[i]), and
+// shares[i / 8][n] = sum of out[n, i]^2 over the 8 features of group i / 8: the product that
+// follows multiplies its outputs by rsqrt(sum of the shares / d + eps).  One block per token,
+// d a multiple of 8.
+__global__ void embed_prepare_kernel(const int* __restrict__ ids, const int* __restrict__ pending,
+                                     const __nv_bfloat16* __restrict__ table, float* __restrict__ out,
+                                     int d, float scale, const float* __restrict__ gain,
+                                     __nv_bfloat16* __restrict__ x_out, int64_t ld_xout,
+                                     float* __restrict__ shares) {
+    pdl_wait();
+    pdl_trigger();
+    const int n = blockIdx.x;
+    int id = ids[n];
+    if (id < 0) id = pending[-1 - id];
+    const __nv_bfloat16* src = table + (int64_t)id * d;
+    float* dst = out + (int64_t)n * d;
+    __nv_bfloat16* xo = x_out + (int64_t)n * ld_xout;
+    for (int g = threadIdx.x; g < d / 8; g += blockDim.x) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(src + g * 8);
+        const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&raw);
+        float sq = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float v = __bfloat162float(e[j]) * scale;
+            dst[g * 8 + j] = v;
+            xo[g * 8 + j] = __float2bfloat16_rn(v * gain[g * 8 + j]);
+            sq += v * v;
+        }
+        shares[(int64_t)g * 8 + n] = sq;
+    }
+}
+
 // x = cap * tanh(x * scale / cap) in place (cap > 0), or x * scale (cap == 0): what some
 // architectures do to their logits before sampling.
 __global__ void logit_cap_kernel(float* __restrict__ x, int64_t n, float scale, float cap) {
@@ -221,6 +254,22 @@ static int norm_threads(int d) {
 
 // dtype: 0 = float32, 1 = bfloat16 (of table / delta / out / gu).
 // `pending` may be null if no id is negative.
+// See embed_prepare_kernel.  n_tokens <= 8; d a multiple of 8; table rows and x_out rows 16-byte
+// aligned; shares [d / 8][8].
+SLLM_EXPORT int sllm_embed_prepare(const int* ids, const int* pending, const void* table, float* out,
+                                   int n_tokens, int d, float scale, const float* gain, void* x_out,
+                                   int64_t ld_xout, float* shares, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (n_tokens > 8 || d <= 0 || (d % 8) || ((uintptr_t)table & 15)) return (int)cudaErrorInvalidValue;
+    int threads = 32;
+    while (threads < 1024 && threads * 8 < d) threads <<= 1;
+    embed_prepare_kernel<<<n_tokens, threads, 0, stream>>>(
+        ids, pending, (const __nv_bfloat16*)table, out, d, scale, gain, (__nv_bfloat16*)x_out,
+        ld_xout, shares);
+    SLLM_LAUNCH_CHECK();
+    return 0;
+}
+
 SLLM_EXPORT int sllm_logit_cap(float* x, int64_t n, float scale, float cap, cudaStream_t stream) {
     if (n <= 0) return 0;
     if (cap < 0.f) return (int)cudaErrorInvalidValue;

@@ -18,7 +18,7 @@ from ..kernels import ops
 from ..parts import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS, BuildContext,
                      CacheView, KVSpec, StateSpec, make)
 from ..parts.linear import Linear
-from ..parts.stream import Normed
+from ..parts.stream import Normed, StreamSink
 from ..weights.loader import ParamSpec
 
 
@@ -93,6 +93,12 @@ class DecoderModel:
             self._next_entry.append(entry if getattr(block, "takes_next_entry", False) else None)
         self.final_norm = make(NORMS, "norm", spec.final_norm)
         self._named_parts.append((spec.final_norm_name, self.final_norm))
+        # what the first run starts with, for the embedding (if that block says, its norm's
+        # factor is one number per token and its gain a vector `weight`)
+        first = self.blocks[spec.order[0].layer] if spec.order else None
+        entry = first.entry() if first is not None and hasattr(first, "entry") else None
+        self._first_entry = entry if (entry is not None and getattr(entry[0], "deferrable", False)
+                                      and hasattr(entry[1], "accepts_normed")) else None
         # the last run may prepare the final norm for the output matrix in steps that want the
         # logits of every token in order (decode steps), where no rows are gathered in between
         last = self.blocks[spec.order[-1].layer] if spec.order else None
@@ -160,15 +166,32 @@ class DecoderModel:
 
     # --------------------------------------------------------------------------- forward
 
+    def _embed(self, batch, resid: torch.Tensor):
+        """The tokens' embeddings into the stream.  In steps of a few tokens the first run's
+        norm is prepared for the product after it on the way (returned as what is pending),
+        where that norm and that product can (scratch_llm_b200.parts.stream)."""
+        s = self.spec
+        n, d = batch.n_tokens, s.hidden_size
+        entry = self._first_entry
+        if (entry is not None and n <= StreamSink.MAX_TOKENS and d % 8 == 0
+                and self.embedding.dtype == torch.bfloat16 and entry[1].accepts_normed(n)):
+            norm = entry[0]
+            x_out = torch.empty((n, d), dtype=torch.bfloat16, device=resid.device)
+            shares = torch.empty((d // 8, 8), dtype=torch.float32, device=resid.device)
+            ops.embed_prepare(batch.token_ids, self.embedding, resid, batch.pending_tokens,
+                              s.embedding_multiplier, norm.weight, x_out, shares)
+            return Normed(x_out, shares, d, norm.eps, norm)
+        ops.embed(batch.token_ids, self.embedding, resid, batch.pending_tokens,
+                  scale=s.embedding_multiplier)
+        return None
+
     def forward(self, batch, cache) -> torch.Tensor | None:
         """Run the batch's tokens from the cache; returns logits [n_out, vocab] in 32-bit, or
         None when no logits are wanted."""
         s = self.spec
         resid = torch.empty((batch.n_tokens, s.hidden_size), dtype=torch.float32,
                             device=self.ctx.device)
-        ops.embed(batch.token_ids, self.embedding, resid, batch.pending_tokens,
-                  scale=s.embedding_multiplier)
-        pending = None
+        pending = self._embed(batch, resid)
         for i, run in enumerate(s.order):
             pages, group = cache.entry_pages(run.cache)
             view = CacheView(pages=pages,

@@ -166,6 +166,30 @@ def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor,
     return out
 
 
+def embed_prepare(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor,
+                  pending: torch.Tensor | None, scale: float, gain: torch.Tensor,
+                  x_out: torch.Tensor, shares: torch.Tensor) -> None:
+    """:func:`embed` for up to 8 tokens of a bfloat16 table, with the norm after it prepared for
+    the product that follows: ``x_out`` [N, d] = bfloat16(out * gain), ``shares`` [d / 8, 8] the
+    tokens' sums of squares in groups of 8 features (see scratch_llm_b200.parts.stream)."""
+    _need(ids, torch.int32, "ids")
+    if pending is not None:
+        _need(pending, torch.int32, "pending")
+    _need(table, torch.bfloat16, "table")
+    _need(out, torch.float32, "out")
+    _need(gain, torch.float32, "gain")
+    _need(x_out, torch.bfloat16, "x_out", contiguous=False)
+    _need(shares, torch.float32, "shares")
+    n, d = ids.numel(), table.shape[1]
+    if n > 8 or d % 8 or out.shape != (n, d) or x_out.shape != (n, d) or gain.numel() != d \
+            or shares.shape != (d // 8, 8) or x_out.stride(1) != 1:
+        raise KernelError("embed_prepare shapes")
+    _check(_core("sllm_elementwise").sllm_embed_prepare(
+        _ptr(ids), _ptr(pending) if pending is not None else c_void_p(0), _ptr(table), _ptr(out),
+        c_int(n), c_int(d), c_float(scale), _ptr(gain), _ptr(x_out), c_int64(x_out.stride(0)),
+        _ptr(shares), _stream()), "embed_prepare")
+
+
 def logit_cap(logits: torch.Tensor, scale: float = 1.0, cap: float = 0.0) -> torch.Tensor:
     """In place on 32-bit logits: ``cap * tanh(logits * scale / cap)``, or ``logits * scale``
     when ``cap`` is 0."""

@@ -51,6 +51,28 @@ def test_embed(ops, dtype):
     assert torch.equal(out.cpu(), P.embed(ids.long(), table).float() * torch.tensor(200 ** 0.5))
 
 
+@pytest.mark.parametrize("n, d, scale", [(8, 1024, 1.0), (3, 200, 2.5), (1, 4096, 1.0)])
+def test_embed_prepares_the_first_norm(ops, n, d, scale):
+    """The embedding for a few tokens that also writes the first norm's input for the product
+    after it (stream * gain in bfloat16) and the tokens' sums of squares in groups of 8."""
+    table = rand(500, d, dtype=torch.bfloat16, seed=1)
+    gain = rand(d, seed=2) * 0.2 + 1.0
+    ids = torch.tensor([499, 0, 7, 7, 123, -1, 42, 3][:n], dtype=torch.int32)
+    pending = torch.tensor([321, 5], dtype=torch.int32)
+    real = ids.clone().long()
+    real[ids < 0] = 321
+    out = torch.full((n, d), float("nan"), dtype=torch.float32, device="cuda")
+    x_out = torch.full((n, d), float("nan"), dtype=torch.bfloat16, device="cuda")
+    shares = torch.full((d // 8, 8), float("nan"), dtype=torch.float32, device="cuda")
+    ops.embed_prepare(ids.cuda(), table.cuda(), out, pending.cuda(), scale, gain.cuda(), x_out, shares)
+    want = table[real].float() * scale
+    assert torch.equal(out.cpu(), want)
+    assert torch.equal(x_out.cpu(), (want * gain).to(torch.bfloat16))
+    torch.testing.assert_close(shares.cpu()[:, :n].sum(0), want.pow(2).sum(-1), rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(shares.cpu()[:, :n].T.reshape(n, d // 8),
+                               want.pow(2).reshape(n, d // 8, 8).sum(-1), rtol=1e-6, atol=1e-6)
+
+
 @pytest.mark.parametrize("scale, cap", [(1.0, 30.0), (0.25, 0.0), (3.0, 1.5)])
 def test_logit_cap(ops, scale, cap):
     x = rand(7, 1001, seed=4) * 20
